@@ -1,0 +1,201 @@
+/*
+ * jetlong_b200 — C ABI of the B200 (sm_100a) bifocal-RoPE attention kernels.
+ *
+ * This is the native boundary a Jet-Long maintainer binds instead of the reference's
+ * JIT-compiled pybind module and CuTe-DSL launchers.  Plain pointers, sizes and strides only;
+ * no torch types.  Every tensor is caller-owned device memory; the library never allocates.
+ * All work is enqueued on the stream passed in; no call synchronises or reads device memory
+ * on the host, so calls are CUDA-graph capturable.
+ *
+ * Element type of q/k/v/out is bf16 (JL_BF16) unless noted; lse is fp32.  Strides are in ELEMENTS.
+ * The innermost (head_dim) dimension is always contiguous and head_dim must be 128.
+ *
+ * Reference interfaces replaced (paths inside the Jet-Long repository):
+ *   jl_merge          jetlm/kernels/csrc/merge_fused.cpp:32-54  (merge2_bshd / merge2_bshd_out),
+ *                     jetlm/kernels/csrc/merge_fused.cu:135-168, and the torch N-way merge
+ *                     jetlm/kernels/cute_decode_sm90.py:199-240
+ *   jl_prefill        jetlm/kernels/cute_prefill_sm90.py:114-230 (fa4_cute_prefill_sm90_jetlong_fused:
+ *                     pack to 2S + block-sparse FA4 call + merge2_bshd + logaddexp)
+ *   jl_decode         jetlm/kernels/cute_decode_sm90.py:2748-2799 (fa4_cute_decode_sm90_jetlong_fused)
+ *                     and its launcher :2454-2745
+ *   jl_decode_workspace_bytes   the module-level split-K workspace cache, cute_decode_sm90.py:165-196
+ *   jl_rotate         the torch elementwise RoPE / regroup passes,
+ *                     jetlm/modeling/jetlong_fused/modeling_qwen3_jetlong_fused.py:171-176, :209-226
+ */
+#ifndef JETLONG_B200_H_
+#define JETLONG_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define JL_MAX_CLASSES 3
+#define JL_MAX_SEGMENTS 4
+#define JL_MAX_PARTS 16
+
+/* Status codes returned by every entry point. */
+enum {
+  JL_OK = 0,
+  JL_ERR_BAD_ARG = 1,        /* null pointer, negative size, misaligned pointer or stride        */
+  JL_ERR_UNSUPPORTED = 2,    /* valid request outside what the kernels implement (e.g. head_dim) */
+  JL_ERR_LAUNCH = 3,         /* the CUDA runtime refused the launch                              */
+  JL_ERR_ARCH = 4,           /* current device is not sm_100                                     */
+  JL_ERR_WORKSPACE = 5       /* workspace missing or smaller than jl_*_workspace_bytes           */
+};
+
+/* Library version (major*10000 + minor*100 + patch). */
+int jl_version(void);
+/* Static description of a status code. */
+const char* jl_status_string(int status);
+/* Detail message of the last failing call on this host thread ("" if none). */
+const char* jl_last_error(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * Position map: which (query operand, key operand) pair scores a (query, key) position pair.
+ *
+ * JL_MAP_BAND  (jetlong, self-extend): class 0 iff 0 <= pq - pk <= near_span, class 1 iff
+ *              pq - pk > near_span.  jetlong: near_span = w_0 (w_0 + 1 near keys);
+ *              self-extend: near_span = window_size - 1.
+ * JL_MAP_CHUNK (dual chunk attention): class = min(pq / chunk - pk / chunk, 2)
+ *              (0 intra, 1 successive, 2 inter).
+ * Pairs with pk > pq are masked (causal).  Class c is scored as q[c] . k[c]; operands of
+ * different classes may alias (DCA uses one key tensor for all three classes).
+ * ------------------------------------------------------------------------------------------- */
+enum { JL_MAP_BAND = 0, JL_MAP_CHUNK = 1 };
+
+typedef struct {
+  int32_t kind;        /* JL_MAP_BAND or JL_MAP_CHUNK */
+  int32_t n_classes;   /* 2 for BAND, 3 for CHUNK     */
+  int64_t near_span;   /* BAND                        */
+  int64_t chunk;       /* CHUNK                       */
+} jl_posmap;
+
+/* ---------------------------------------------------------------------------------------------
+ * jl_prefill — single-pass position-mapped causal attention for a block of Sq query tokens
+ * against Skv keys.  One online softmax spans all classes; no packed 2S tensors, no separate
+ * merge.  Query row i has absolute position q_pos0 + i.  Key row j has absolute position
+ * k_pos0 + (j / k_block) * k_block_stride + (j % k_block): a contiguous cache uses
+ * k_block >= Skv; a block-cyclic shard of a sequence-parallel cache uses its stripe geometry.
+ *
+ * q[c]: (B, Sq, H, D)   k[c], v: (B, Skv, Hk, D)   out: (B, Sq, H, D)   lse: (B, H, Sq) fp32.
+ * lse may be NULL.  Rows that see no key produce a zero output row and lse = -inf.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* q[JL_MAX_CLASSES];
+  const void* k[JL_MAX_CLASSES];
+  const void* v;
+  void* out;
+  float* lse;
+  int64_t q_stride_b, q_stride_s, q_stride_h;
+  int64_t k_stride_b, k_stride_s, k_stride_h;
+  int64_t v_stride_b, v_stride_s, v_stride_h;
+  int64_t o_stride_b, o_stride_s, o_stride_h;
+  int32_t batch, seqlen_q, seqlen_k, heads, kv_heads, head_dim;
+  int64_t q_pos0;
+  int64_t k_pos0;
+  int64_t k_block;          /* <= 0 means contiguous */
+  int64_t k_block_stride;
+  float softmax_scale;
+  jl_posmap map;
+  int32_t impl;             /* 0 = default kernel; 1 = legacy mma.sync kernel kept as GPU cross-check */
+} jl_prefill_args;
+
+int jl_prefill(const jl_prefill_args* args, void* cuda_stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * jl_decode — split-KV attention of ONE query token per sequence over up to JL_MAX_SEGMENTS key
+ * segments read in place (no slicing, padding or regrouping copies).  Segment s is scored with
+ * query operand q[seg[s].q_class].  If seg[s].rotate != 0 the keys of that segment are rotated
+ * in-kernel by (floor(p / group_size) - p) * inv_freq, p = seg[s].pos0 + row, i.e. the far class
+ * of the jetlong map is formed on the fly from a base-rotated cache.
+ *
+ * q[c]: (B, 1, H, D)   seg[s].k / .v: (B, len, Hk, D)   out: (B, 1, H, D)   lse: (B, H) fp32.
+ * seg[s].len_dev, if not NULL, is an int32 device array (B,) of per-sequence valid lengths
+ * (<= len).  workspace holds the fp32 split partials; size it with jl_decode_workspace_bytes.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* k;
+  const void* v;
+  int64_t k_stride_b, k_stride_s, k_stride_h;
+  int64_t v_stride_b, v_stride_s, v_stride_h;
+  const int32_t* len_dev;
+  int64_t pos0;
+  int32_t len;
+  int32_t q_class;
+  int32_t rotate;
+  int32_t reserved;
+} jl_kv_segment;
+
+typedef struct {
+  const void* q[JL_MAX_CLASSES];
+  int64_t q_stride_b, q_stride_h;
+  jl_kv_segment seg[JL_MAX_SEGMENTS];
+  int32_t n_segments;
+  int32_t batch, heads, kv_heads, head_dim;
+  int32_t num_splits;       /* <= 0: chosen by the library to fill the GPU */
+  float softmax_scale;
+  const float* inv_freq;    /* (head_dim/2,) fp32 device array; needed only when a segment rotates */
+  int32_t group_size;
+  int32_t reserved;
+  void* out;
+  float* lse;               /* may be NULL */
+  int64_t o_stride_b, o_stride_h;
+  void* workspace;
+  size_t workspace_bytes;
+} jl_decode_args;
+
+/* Bytes of workspace jl_decode needs for (batch, heads, head_dim) with at most max_splits splits
+ * (max_splits <= 0: the library's own upper bound for automatic splitting). */
+size_t jl_decode_workspace_bytes(int32_t batch, int32_t heads, int32_t head_dim, int32_t max_splits);
+/* Number of splits jl_decode would pick for num_splits <= 0. */
+int32_t jl_decode_auto_splits(int32_t batch, int32_t kv_heads, int64_t total_keys);
+int jl_decode(const jl_decode_args* args, void* cuda_stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * jl_merge — N-way (O, LSE) merge of partial attention results over disjoint key sets:
+ *   out = sum_p O_p e^{lse_p - m} / sum_p e^{lse_p - m},  lse = m + log sum_p e^{lse_p - m}.
+ * o[p]: (B, S, H, D) contiguous, lse[p]: (B, H, S) fp32 contiguous.  lse_out may be NULL.
+ * round_like_reference != 0 (n_parts == 2 only) reproduces the storage-dtype rounding after every
+ * arithmetic step of the reference kernel (merge_fused.cu:100-111), including its 1e-7 clamp.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* o[JL_MAX_PARTS];
+  const float* lse[JL_MAX_PARTS];
+  int32_t n_parts;
+  int32_t batch, seqlen, heads, head_dim;
+  int32_t round_like_reference;
+  void* out;
+  float* lse_out;
+} jl_merge_args;
+
+int jl_merge(const jl_merge_args* args, void* cuda_stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * jl_rotate — rotate-half RoPE of x by an integer position function, fp32 math, one rounding:
+ *   t(p)  = min((p / div) * div_mul + (p % mod) * mod_mul + add, t_max),  p = pos0 + row
+ *   theta = fp32(t) * inv_freq[d]            (one fp32 rounding, as the reference forms it)
+ *   out[d], out[d+D/2] = x[d] cos - x[d+D/2] sin, x[d+D/2] cos + x[d] sin
+ * Covers base RoPE (t = p), the jetlong regroup of base-rotated tensors (t = p/G - p),
+ * self-extend's grouped positions (t = p/Gs + shift) and DCA's mod / clamped / constant positions.
+ * x, out: (B, S, Hx, D) with element strides; out may alias x or point into a KV cache.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* x;
+  void* out;
+  int64_t x_stride_b, x_stride_s, x_stride_h;
+  int64_t o_stride_b, o_stride_s, o_stride_h;
+  int32_t batch, seqlen, heads, head_dim;
+  int64_t pos0;
+  int64_t div, div_mul, mod, mod_mul, add, t_max;
+  const float* inv_freq;    /* (head_dim/2,) fp32 device array */
+} jl_rotate_args;
+
+int jl_rotate(const jl_rotate_args* args, void* cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* JETLONG_B200_H_ */

@@ -1,0 +1,417 @@
+// Split-KV single-token decode attention with GQA head packing — an HBM-streaming kernel.
+//
+// Grid (split, kv_head, batch); 4 warps per CTA.  The keys of all segments form one virtual
+// sequence that is cut into `num_splits` contiguous ranges.  Each warp streams its own 16-row
+// slices of 64-key K/V tiles through a private 3-stage cp.async pipeline (128-bit loads, rows read
+// in place through the caller's strides, XOR-swizzled in shared memory), so warps never wait on
+// one another.  The H/Hk query heads that share a kv head are packed into the M dimension of
+// m16n8k16 tensor-core MMAs (rows past H/Hk are zero), scores go through a base-2 online softmax,
+// and P.V accumulates in registers.  Far-class keys of a base-rotated cache can be regrouped on the
+// fly (rotation by (floor(p/G) - p) * inv_freq in registers) so the cache is read exactly once.
+// Each CTA writes one normalised fp32 partial (O, LSE) per query head; a small second kernel
+// merges the splits.
+#include "jl_common.cuh"
+
+namespace jl {
+
+constexpr int kDecWarps = 4;
+constexpr int kDecTile = 64;                 // keys per tile (16 per warp)
+constexpr int kDecStages = 3;
+constexpr int kDecMaxSplits = 296;           // 2 resident CTAs on each of 148 SMs
+constexpr int kStageBytes = kDecTile * 256;  // one K or V tile
+
+struct DecSeg {
+  const __nv_bfloat16* k;
+  const __nv_bfloat16* v;
+  int64_t ks_b, ks_s, ks_h, vs_b, vs_s, vs_h;
+  const int32_t* len_dev;
+  int64_t pos0;
+  int len, q_class, rotate;
+};
+
+struct DecParams {
+  const __nv_bfloat16* q[JL_MAX_CLASSES];
+  int64_t qs_b, qs_h;
+  DecSeg seg[JL_MAX_SEGMENTS];
+  int n_seg, batch, heads, kv_heads, num_splits, group_size;
+  float scale_log2;
+  const float* inv_freq;
+  float* part_o;     // (B, H, splits, 128)
+  float* part_lse;   // (B, H, splits)
+};
+
+struct DecSmem {
+  uint8_t kv[kDecStages][2][kStageBytes];          // [stage][K/V][64 rows x 256 B]; reused for the warp merge
+  uint8_t q[JL_MAX_CLASSES][16 * 256];
+  float inv_freq[64];
+};
+
+// sin/cos of an fp32 angle of any magnitude reached by RoPE positions: exact reduction by 2*pi in
+// fp64 (one DFMA), then the SFU approximations on [-pi, pi].
+__device__ __forceinline__ void sincos_reduced(float theta, float* s, float* c) {
+  const float k = rintf(theta * 0.15915494309189535f);
+  const float r = static_cast<float>(fma(-static_cast<double>(k), 6.283185307179586, static_cast<double>(theta)));
+  *s = __sinf(r);
+  *c = __cosf(r);
+}
+
+__global__ void __launch_bounds__(kDecWarps * 32, 2) decode_kernel(const DecParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  DecSmem& sm = *reinterpret_cast<DecSmem*>(smem_raw);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int rep = p.heads / p.kv_heads;            // query heads per kv head (<= 16)
+
+  // ---- stage the packed query rows of every class (rows >= rep are zero) ----
+  for (int i = threadIdx.x; i < JL_MAX_CLASSES * 16 * 16; i += blockDim.x) {
+    const int c = i / 256, row = (i / 16) % 16, chunk = i % 16;
+    uint4 val = make_uint4(0, 0, 0, 0);
+    if (p.q[c] != nullptr && row < rep)
+      val = *reinterpret_cast<const uint4*>(p.q[c] + b * p.qs_b + (kvh * rep + row) * p.qs_h + chunk * 8);
+    *reinterpret_cast<uint4*>(&sm.q[c][swz256(row, chunk)]) = val;
+  }
+  if (threadIdx.x < 64) sm.inv_freq[threadIdx.x] = p.inv_freq != nullptr ? p.inv_freq[threadIdx.x] : 0.f;
+
+  // ---- this CTA's key range in the virtual concatenation of the segments ----
+  int seg_len[JL_MAX_SEGMENTS];
+  int64_t total = 0;
+#pragma unroll
+  for (int s = 0; s < JL_MAX_SEGMENTS; ++s) {
+    int len = 0;
+    if (s < p.n_seg) {
+      len = p.seg[s].len;
+      if (p.seg[s].len_dev != nullptr) len = min(len, max(p.seg[s].len_dev[b], 0));
+    }
+    seg_len[s] = len;
+    total += len;
+  }
+  int64_t per = (total + p.num_splits - 1) / p.num_splits;
+  per = (per + kDecTile - 1) / kDecTile * kDecTile;
+  const int64_t range_lo = min(static_cast<int64_t>(split) * per, total);
+  const int64_t range_hi = min(range_lo + per, total);
+
+  int seg_lo[JL_MAX_SEGMENTS], seg_tiles[JL_MAX_SEGMENTS], seg_hi[JL_MAX_SEGMENTS];
+  int n_tiles = 0;
+  {
+    int64_t base = 0;
+#pragma unroll
+    for (int s = 0; s < JL_MAX_SEGMENTS; ++s) {
+      const int64_t lo = max(range_lo, base) - base, hi = min(range_hi, base + seg_len[s]) - base;
+      seg_lo[s] = static_cast<int>(lo);
+      seg_hi[s] = static_cast<int>(hi);
+      seg_tiles[s] = hi > lo ? static_cast<int>((hi - lo + kDecTile - 1) / kDecTile) : 0;
+      n_tiles += seg_tiles[s];
+      base += seg_len[s];
+    }
+  }
+  __syncthreads();
+
+  auto locate = [&](int t, int& s_out, int& row0, int& valid) {
+    int s = 0;
+#pragma unroll
+    for (int i = 0; i < JL_MAX_SEGMENTS - 1; ++i)
+      if (s == i && t >= seg_tiles[i]) { t -= seg_tiles[i]; s = i + 1; }
+    s_out = s;
+    row0 = seg_lo[s] + t * kDecTile;
+    valid = min(kDecTile, seg_hi[s] - row0);
+  };
+
+  // Each warp copies rows [16*warp, 16*warp+16) of a tile: lane -> (row = lane/16 + 2*j, chunk = lane%16).
+  auto issue = [&](int t) {
+    if (t < n_tiles) {
+      int s, row0, valid;
+      locate(t, s, row0, valid);
+      const DecSeg& sg = p.seg[s];
+      const int stage = t % kDecStages;
+      const __nv_bfloat16* kb = sg.k + b * sg.ks_b + kvh * sg.ks_h;
+      const __nv_bfloat16* vb = sg.v + b * sg.vs_b + kvh * sg.vs_h;
+      const uint32_t ks = smem_u32(sm.kv[stage][0]), vs = smem_u32(sm.kv[stage][1]);
+      const int chunk = lane & 15;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int r = warp * 16 + (lane >> 4) + 2 * j;
+        const bool ok = r < valid;
+        const int64_t grow = ok ? row0 + r : row0;      // keep the address in range when zero-filling
+        cp_async_16(ks + swz256(r, chunk), kb + grow * sg.ks_s + chunk * 8, ok);
+        cp_async_16(vs + swz256(r, chunk), vb + grow * sg.vs_s + chunk * 8, ok);
+      }
+    }
+    cp_async_commit();
+  };
+
+  float o[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+#pragma unroll
+  for (int t = 0; t < kDecStages - 1; ++t) issue(t);
+
+  for (int t = 0; t < n_tiles; ++t) {
+    cp_async_wait<kDecStages - 2>();
+    __syncwarp();
+    issue(t + kDecStages - 1);     // refills the stage consumed in the previous iteration (warp-private rows)
+
+    int s, row0, valid;
+    locate(t, s, row0, valid);
+    const DecSeg& sg = p.seg[s];
+    const int stage = t % kDecStages;
+    const uint32_t ks = smem_u32(sm.kv[stage][0]), vs = smem_u32(sm.kv[stage][1]);
+    const uint32_t qs = smem_u32(sm.q[sg.q_class]);
+    const int wvalid = valid - warp * 16;           // valid keys among this warp's 16
+    if (wvalid <= 0) continue;                      // warp-uniform
+
+    // ---- K fragments for the warp's 16 keys: kf[kk] = {nblk0 k-lo, nblk0 k-hi, nblk1 k-lo, nblk1 k-hi} ----
+    uint32_t kf[8][4];
+    {
+      const int r = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) ldmatrix_x4(kf[kk], ks + swz256(r, 2 * kk + ((lane >> 3) & 1)));
+    }
+    if (sg.rotate) {
+      // element (key n, dim d) of kf[kk][i]: n = 8*(i/2) + lane/4, d = 16*kk + 8*(i%2) + 2*(lane%4) + {0,1};
+      // its rotation partner d + 64 sits in kf[kk + 4][i].
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int64_t pos = sg.pos0 + row0 + warp * 16 + half * 8 + (lane >> 2);
+        const float tf = static_cast<float>(pos / p.group_size - pos);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int i = half * 2 + e;
+            const int d = 16 * kk + 8 * e + 2 * (lane & 3);
+            float s0, c0, s1, c1;
+            sincos_reduced(__fmul_rn(tf, sm.inv_freq[d]), &s0, &c0);
+            sincos_reduced(__fmul_rn(tf, sm.inv_freq[d + 1]), &s1, &c1);
+            const float2 lo = unpack_bf16x2(kf[kk][i]), hi = unpack_bf16x2(kf[kk + 4][i]);
+            kf[kk][i] = pack_bf16x2(lo.x * c0 - hi.x * s0, lo.y * c1 - hi.y * s1);
+            kf[kk + 4][i] = pack_bf16x2(hi.x * c0 + lo.x * s0, hi.y * c1 + lo.y * s1);
+          }
+        }
+      }
+    }
+
+    // ---- S = Q K^T for 16 (packed head) rows x 16 keys ----
+    float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      uint32_t a[4];
+      ldmatrix_x4(a, qs + swz256(lane & 15, 2 * kk + (lane >> 4)));
+      mma_bf16_16816(sc[0], a, kf[kk][0], kf[kk][1]);
+      mma_bf16_16816(sc[1], a, kf[kk][2], kf[kk][3]);
+    }
+
+    // ---- online softmax (base 2); thread holds rows g = lane/4 (regs 0,1) and g + 8 (regs 2,3) ----
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = nb * 8 + 2 * (lane & 3) + (e & 1);
+        const float v = key < wvalid ? sc[nb][e] * p.scale_log2 : -INFINITY;
+        sc[nb][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+    }
+    float alpha[2], m_use[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      const float m_new = fmaxf(m_run[h], mx[h]);
+      m_use[h] = m_new == -INFINITY ? 0.f : m_new;
+      alpha[h] = fast_exp2(m_run[h] - m_use[h]);
+      m_run[h] = m_new;
+    }
+    float rs[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float pv = fast_exp2(sc[nb][e] - m_use[e >> 1]);
+        sc[nb][e] = pv;
+        rs[e >> 1] += pv;
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      rs[h] += __shfl_xor_sync(0xffffffffu, rs[h], 1);
+      rs[h] += __shfl_xor_sync(0xffffffffu, rs[h], 2);
+      l_run[h] = l_run[h] * alpha[h] + rs[h];
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+      o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+    }
+
+    // ---- O += P V ----
+    uint32_t pa[4];
+    pa[0] = pack_bf16x2(sc[0][0], sc[0][1]);
+    pa[1] = pack_bf16x2(sc[0][2], sc[0][3]);
+    pa[2] = pack_bf16x2(sc[1][0], sc[1][1]);
+    pa[3] = pack_bf16x2(sc[1][2], sc[1][3]);
+    {
+      const int r = warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        uint32_t vf[4];
+        ldmatrix_x4_trans(vf, vs + swz256(r, 2 * j + (lane >> 4)));
+        mma_bf16_16816(o[2 * j], pa, vf[0], vf[1]);
+        mma_bf16_16816(o[2 * j + 1], pa, vf[2], vf[3]);
+      }
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // ---- merge the 4 warps' states through shared memory (reusing the K/V stages) ----
+  float* mo = reinterpret_cast<float*>(&sm.kv[0][0][0]);        // [warp][16 rows][128]
+  float* mm = mo + kDecWarps * 16 * 128;                        // [warp][16]
+  float* ml = mm + kDecWarps * 16;                              // [warp][16]
+  {
+    const int g = lane >> 2, tq = lane & 3;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float* dst = mo + (warp * 16 + g) * 128 + i * 8 + 2 * tq;
+      dst[0] = o[i][0]; dst[1] = o[i][1];
+      dst[8 * 128] = o[i][2]; dst[8 * 128 + 1] = o[i][3];
+    }
+    if (tq == 0) {
+      mm[warp * 16 + g] = m_run[0]; mm[warp * 16 + g + 8] = m_run[1];
+      ml[warp * 16 + g] = l_run[0]; ml[warp * 16 + g + 8] = l_run[1];
+    }
+  }
+  __syncthreads();
+  for (int row = 0; row < rep; ++row) {
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kDecWarps; ++w) M = fmaxf(M, mm[w * 16 + row]);
+    const float Ms = M == -INFINITY ? 0.f : M;
+    float L = 0.f, acc = 0.f;
+    const int d = threadIdx.x;                                   // 128 threads == 128 dims
+#pragma unroll
+    for (int w = 0; w < kDecWarps; ++w) {
+      const float f = fast_exp2(mm[w * 16 + row] - Ms);
+      L += ml[w * 16 + row] * f;
+      acc += mo[(w * 16 + row) * 128 + d] * f;
+    }
+    const int head = kvh * rep + row;
+    const int64_t pidx = (static_cast<int64_t>(b) * p.heads + head) * p.num_splits + split;
+    p.part_o[pidx * 128 + d] = L > 0.f ? acc / L : 0.f;
+    if (d == 0) p.part_lse[pidx] = L > 0.f ? (Ms + log2f(L)) * kLn2 : -INFINITY;
+  }
+}
+
+// Merge the split partials of one (batch, head): 128 threads, one per output dim.
+__global__ void __launch_bounds__(128) decode_combine_kernel(const float* __restrict__ part_o,
+                                                             const float* __restrict__ part_lse, int num_splits,
+                                                             int heads, __nv_bfloat16* out, int64_t os_b, int64_t os_h,
+                                                             float* lse_out) {
+  const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  const int64_t base = (static_cast<int64_t>(b) * heads + h) * num_splits;
+  float m = -INFINITY;
+  for (int s = 0; s < num_splits; ++s) m = fmaxf(m, part_lse[base + s]);
+  const float ms = m == -INFINITY ? 0.f : m;
+  float wsum = 0.f, acc = 0.f;
+  for (int s = 0; s < num_splits; ++s) {
+    const float w = exp2f((part_lse[base + s] - ms) * kLog2e);
+    wsum += w;
+    acc = fmaf(w, part_o[(base + s) * 128 + d], acc);
+  }
+  out[b * os_b + h * os_h + d] = __float2bfloat16(wsum > 0.f ? acc / wsum : 0.f);
+  if (lse_out != nullptr && d == 0) lse_out[static_cast<int64_t>(b) * heads + h] = wsum > 0.f ? ms + logf(wsum) : -INFINITY;
+}
+
+int32_t decode_auto_splits(int32_t batch, int32_t kv_heads, int64_t total_keys) {
+  const int64_t ctas = static_cast<int64_t>(batch > 0 ? batch : 1) * (kv_heads > 0 ? kv_heads : 1);
+  int64_t s = kDecMaxSplits / ctas;
+  const int64_t tiles = (total_keys + kDecTile - 1) / kDecTile;
+  if (s > tiles) s = tiles;
+  if (s < 1) s = 1;
+  return static_cast<int32_t>(s);
+}
+
+size_t decode_workspace_bytes(int32_t batch, int32_t heads, int32_t head_dim, int32_t max_splits) {
+  if (batch <= 0 || heads <= 0 || head_dim <= 0) return 0;
+  const size_t splits = max_splits > 0 ? static_cast<size_t>(max_splits) : static_cast<size_t>(kDecMaxSplits);
+  return static_cast<size_t>(batch) * heads * splits * (static_cast<size_t>(head_dim) + 1) * sizeof(float);
+}
+
+int launch_decode(const jl_decode_args* a, cudaStream_t stream) {
+  if (a->head_dim != kHeadDim) return fail(JL_ERR_UNSUPPORTED, "jl_decode: head_dim must be 128, got %d", a->head_dim);
+  if (a->batch <= 0 || a->heads <= 0 || a->kv_heads <= 0) return fail(JL_ERR_BAD_ARG, "jl_decode: batch/heads/kv_heads must be positive");
+  if (a->heads % a->kv_heads != 0) return fail(JL_ERR_BAD_ARG, "jl_decode: heads must be divisible by kv_heads");
+  if (a->heads / a->kv_heads > 16) return fail(JL_ERR_UNSUPPORTED, "jl_decode: at most 16 query heads per kv head");
+  if (a->n_segments < 1 || a->n_segments > JL_MAX_SEGMENTS) return fail(JL_ERR_BAD_ARG, "jl_decode: n_segments must be in [1, %d]", JL_MAX_SEGMENTS);
+  if (a->out == nullptr) return fail(JL_ERR_BAD_ARG, "jl_decode: out is NULL");
+  if (a->q_stride_b % 8 || a->q_stride_h % 8) return fail(JL_ERR_BAD_ARG, "jl_decode: q strides must be multiples of 8 elements");
+  DecParams p{};
+  int64_t total = 0;
+  bool any_rotate = false;
+  for (int c = 0; c < JL_MAX_CLASSES; ++c) {
+    if (reinterpret_cast<uintptr_t>(a->q[c]) & 15) return fail(JL_ERR_BAD_ARG, "jl_decode: q[%d] is not 16-byte aligned", c);
+    p.q[c] = static_cast<const __nv_bfloat16*>(a->q[c]);
+  }
+  for (int s = 0; s < a->n_segments; ++s) {
+    const jl_kv_segment& g = a->seg[s];
+    if (g.len < 0) return fail(JL_ERR_BAD_ARG, "jl_decode: segment %d has negative length", s);
+    if (g.q_class < 0 || g.q_class >= JL_MAX_CLASSES || a->q[g.q_class] == nullptr)
+      return fail(JL_ERR_BAD_ARG, "jl_decode: segment %d names a missing query operand", s);
+    if (g.len > 0 && (g.k == nullptr || g.v == nullptr)) return fail(JL_ERR_BAD_ARG, "jl_decode: segment %d has NULL k/v", s);
+    if ((reinterpret_cast<uintptr_t>(g.k) | reinterpret_cast<uintptr_t>(g.v)) & 15)
+      return fail(JL_ERR_BAD_ARG, "jl_decode: segment %d k/v not 16-byte aligned", s);
+    const int64_t st[] = {g.k_stride_b, g.k_stride_s, g.k_stride_h, g.v_stride_b, g.v_stride_s, g.v_stride_h};
+    for (int64_t x : st)
+      if (x % 8 != 0) return fail(JL_ERR_BAD_ARG, "jl_decode: segment %d strides must be multiples of 8 elements", s);
+    DecSeg& d = p.seg[s];
+    d.k = static_cast<const __nv_bfloat16*>(g.k);
+    d.v = static_cast<const __nv_bfloat16*>(g.v);
+    d.ks_b = g.k_stride_b; d.ks_s = g.k_stride_s; d.ks_h = g.k_stride_h;
+    d.vs_b = g.v_stride_b; d.vs_s = g.v_stride_s; d.vs_h = g.v_stride_h;
+    d.len_dev = g.len_dev;
+    d.pos0 = g.pos0;
+    d.len = g.len;
+    d.q_class = g.q_class;
+    d.rotate = g.rotate != 0;
+    any_rotate |= g.rotate != 0;
+    total += g.len;
+  }
+  if (any_rotate && (a->inv_freq == nullptr || a->group_size < 1))
+    return fail(JL_ERR_BAD_ARG, "jl_decode: rotating segments need inv_freq and group_size >= 1");
+  int splits = a->num_splits > 0 ? a->num_splits : decode_auto_splits(a->batch, a->kv_heads, total);
+  const int64_t tiles = (total + kDecTile - 1) / kDecTile;
+  if (splits > tiles) splits = static_cast<int>(tiles > 0 ? tiles : 1);
+  const size_t need = decode_workspace_bytes(a->batch, a->heads, a->head_dim, splits);
+  if (a->workspace == nullptr || a->workspace_bytes < need)
+    return fail(JL_ERR_WORKSPACE, "jl_decode: workspace of %zu bytes needed, %zu given", need, a->workspace_bytes);
+  if (reinterpret_cast<uintptr_t>(a->workspace) & 15) return fail(JL_ERR_BAD_ARG, "jl_decode: workspace not 16-byte aligned");
+  p.qs_b = a->q_stride_b; p.qs_h = a->q_stride_h;
+  p.n_seg = a->n_segments; p.batch = a->batch; p.heads = a->heads; p.kv_heads = a->kv_heads;
+  p.num_splits = splits;
+  p.group_size = a->group_size > 0 ? a->group_size : 1;
+  p.scale_log2 = a->softmax_scale * kLog2e;
+  p.inv_freq = a->inv_freq;
+  p.part_o = static_cast<float*>(a->workspace);
+  p.part_lse = p.part_o + static_cast<size_t>(a->batch) * a->heads * splits * kHeadDim;
+
+  static bool attr_set = false;
+  const int smem = static_cast<int>(sizeof(DecSmem));
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return check_launch("jl_decode (shared memory opt-in)");
+    attr_set = true;
+  }
+  dim3 grid(splits, a->kv_heads, a->batch);
+  decode_kernel<<<grid, kDecWarps * 32, smem, stream>>>(p);
+  int rc = check_launch("jl_decode");
+  if (rc != JL_OK) return rc;
+  dim3 cgrid(a->heads, a->batch);
+  decode_combine_kernel<<<cgrid, 128, 0, stream>>>(p.part_o, p.part_lse, splits, a->heads,
+                                                   static_cast<__nv_bfloat16*>(a->out), a->o_stride_b, a->o_stride_h,
+                                                   a->lse);
+  return check_launch("jl_decode (combine)");
+}
+
+}  // namespace jl

@@ -1,0 +1,91 @@
+// Shared device/host helpers for the jetlong_b200 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/jetlong_b200.h"
+
+namespace jl {
+
+constexpr int kHeadDim = 128;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+// Host-side error reporting (thread-local detail string behind jl_last_error()).
+void set_error(const char* fmt, ...);
+int fail(int status, const char* fmt, ...);
+int check_launch(const char* what);
+int check_device_arch();
+
+// ---------------------------------------------------------------------------------------------
+// Small device helpers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ float2 unpack_bf16x2(uint32_t u) {
+  // bf16 -> fp32 is a 16-bit left shift
+  float2 r;
+  r.x = __uint_as_float(u << 16);
+  r.y = __uint_as_float(u & 0xffff0000u);
+  return r;
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// 16-byte async copy global -> shared; src_bytes == 0 zero-fills (used for rows past the end).
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
+  int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+// D(16x8, fp32) += A(16x16, bf16, row) * B(16x8, bf16, col)
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Byte offset of 16-byte chunk `chunk` (0..15) of row `row` in a [rows][128 bf16] tile whose rows
+// are 256 bytes; the chunk index is XOR-swizzled with the row so that 8 consecutive rows of one
+// logical chunk land in 8 different bank groups (conflict-free ldmatrix).
+__device__ __forceinline__ uint32_t swz256(int row, int chunk) {
+  return static_cast<uint32_t>(row * 256 + ((chunk ^ (row & 7)) << 4));
+}
+
+// Absolute position of key row j of a (possibly block-cyclic) key tensor.
+__device__ __host__ __forceinline__ int64_t key_position(int64_t j, int64_t pos0, int64_t block, int64_t block_stride) {
+  if (block <= 0) return pos0 + j;
+  return pos0 + (j / block) * block_stride + (j % block);
+}
+
+}  // namespace jl

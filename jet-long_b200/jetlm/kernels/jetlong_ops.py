@@ -1,0 +1,486 @@
+"""Kernel-level Python operators over the C ABI (tensor contracts of the reference's level-2 API).
+
+Reference counterparts (paths inside the Jet-Long repository):
+  jetlong_prefill   jetlm/kernels/cute_prefill_sm90.py:114-230   fa4_cute_prefill_sm90_jetlong_fused
+  jetlong_decode    jetlm/kernels/cute_decode_sm90.py:2748-2799  fa4_cute_decode_sm90_jetlong_fused
+  merge_partials    jetlm/kernels/cute_decode_sm90.py:199-240 and jetlm/kernels/merge_fused.py:76-93
+  rope_rotate       jetlm/modeling/jetlong_fused/modeling_qwen3_jetlong_fused.py:171-176, :209-226
+
+All tensors are (B, S, H, D) *views*: any strides are accepted as long as head_dim is contiguous and
+every stride is a multiple of 8 elements, so (B, H, S, D) cache tensors are passed as
+`.transpose(1, 2)` without a copy.  Kernels run on the current torch CUDA stream.  Nothing here
+computes attention in PyTorch: a missing extension or a failing call raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import torch
+
+from . import _native as N
+
+_SUPPORTED_DTYPES = (torch.bfloat16,)
+
+
+# ----------------------------------------------------------------------------------------------
+# plumbing
+# ----------------------------------------------------------------------------------------------
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require_arch(op: str, device: torch.device) -> None:
+    major, _ = torch.cuda.get_device_capability(device)
+    if major != 10:
+        raise RuntimeError(f"{op} requires sm_100 (B200)")
+
+
+def _require_contiguous(op: str, name: str, t: torch.Tensor) -> None:
+    if not t.is_contiguous():
+        raise ValueError(f"{op}: {name} must be contiguous; call {name}.contiguous() before invoking the kernel")
+
+
+def _check_view(op: str, name: str, t: torch.Tensor) -> None:
+    if t.dim() != 4:
+        raise ValueError(f"{op} expects rank-4 BSHD tensors")
+    if t.shape[-1] > 1 and t.stride(-1) != 1:
+        raise ValueError(f"{op}: {name} must have a contiguous head_dim; call {name}.contiguous()")
+    # size-1 dims may carry arbitrary strides; they are never multiplied by a non-zero index
+    if any(t.shape[i] > 1 and t.stride(i) % 8 for i in range(3)):
+        raise ValueError(f"{op}: {name} strides must be multiples of 8 elements")
+    if t.data_ptr() % 16:
+        raise ValueError(f"{op}: {name} must be 16-byte aligned")
+
+
+def _st(t: torch.Tensor, i: int) -> int:
+    return t.stride(i) if t.shape[i] > 1 else 0
+
+
+_WORKSPACES: dict[tuple, torch.Tensor] = {}
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Split-KV scratch, cached per (device, stream) so concurrent streams never share it."""
+    key = (device.index, _stream())
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = ws
+    return ws
+
+
+@dataclass(frozen=True)
+class PositionMap:
+    """Which (q operand, k operand) pair scores a (query, key) position pair (see jl_posmap)."""
+    kind: int
+    n_classes: int
+    near_span: int = 0
+    chunk: int = 1
+
+    @staticmethod
+    def jetlong(w_0: int) -> "PositionMap":
+        return PositionMap(N.JL_MAP_BAND, 2, near_span=int(w_0))
+
+    @staticmethod
+    def selfext(window_size: int) -> "PositionMap":
+        return PositionMap(N.JL_MAP_BAND, 2, near_span=int(window_size) - 1)
+
+    @staticmethod
+    def dca(chunk_size: int) -> "PositionMap":
+        return PositionMap(N.JL_MAP_CHUNK, 3, chunk=int(chunk_size))
+
+    def c_struct(self) -> N.PosMap:
+        return N.PosMap(self.kind, self.n_classes, self.near_span, self.chunk)
+
+
+# ----------------------------------------------------------------------------------------------
+# rotate
+# ----------------------------------------------------------------------------------------------
+
+_BIG = (1 << 62)
+
+
+def rope_rotate(x: torch.Tensor, inv_freq: torch.Tensor, *, pos0: int = 0, div: int = 1, div_mul: int = 1,
+                mod: int = _BIG, mod_mul: int = 0, add: int = 0, t_max: int = _BIG,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = rotate-half RoPE of x (B,S,H,D view) at t(p) = min((p//div)*div_mul + (p%mod)*mod_mul + add, t_max),
+    p = pos0 + row.  fp32 math on the angles fp32(t)*inv_freq, one rounding to bf16."""
+    op = "rope_rotate"
+    _check_view(op, "x", x)
+    if x.dtype not in _SUPPORTED_DTYPES:
+        raise ValueError(f"{op}: x must be torch.bfloat16, got {x.dtype}")
+    _require_arch(op, x.device)
+    if out is None:
+        out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    _check_view(op, "out", out)
+    if out.shape != x.shape:
+        raise ValueError(f"{op}: out must have shape {tuple(x.shape)}")
+    inv_freq = inv_freq.to(device=x.device, dtype=torch.float32).contiguous()
+    if inv_freq.numel() < x.shape[-1] // 2:
+        raise ValueError(f"{op}: inv_freq must have shape ({x.shape[-1] // 2},) or larger")
+    B, S, H, D = x.shape
+    a = N.RotateArgs(x.data_ptr(), out.data_ptr(), _st(x, 0), _st(x, 1), _st(x, 2), _st(out, 0), _st(out, 1), _st(out, 2),
+                     B, S, H, D, int(pos0), int(div), int(div_mul), int(mod), int(mod_mul), int(add), int(t_max),
+                     inv_freq.data_ptr())
+    with torch.cuda.device(x.device):
+        N.check("jl_rotate", N.lib().jl_rotate(C.byref(a), _stream()))
+    return out
+
+
+def rope_base(x, inv_freq, *, pos0=0, out=None):
+    """Base RoPE: t = p."""
+    return rope_rotate(x, inv_freq, pos0=pos0, out=out)
+
+
+def rope_regroup(x_base, inv_freq, *, group_size: int, pos0=0, out=None):
+    """jetlong far-class operand from a base-rotated tensor: extra rotation by floor(p/G) - p."""
+    return rope_rotate(x_base, inv_freq, pos0=pos0, div=int(group_size), div_mul=1, mod=_BIG, mod_mul=-1, out=out)
+
+
+# ----------------------------------------------------------------------------------------------
+# merge
+# ----------------------------------------------------------------------------------------------
+
+def merge_partials(o_parts: Sequence[torch.Tensor], lse_parts: Sequence[torch.Tensor], *,
+                   out: Optional[torch.Tensor] = None, lse_out: Optional[torch.Tensor] = None,
+                   return_lse: bool = True, round_like_reference: bool = False):
+    """N-way (O, LSE) merge.  o_parts[i]: (B,S,H,D) contiguous bf16; lse_parts[i]: (B,H,S) fp32 contiguous.
+    A stacked (N,B,S,H,D) / (N,B,H,S) pair is accepted too.  Returns out or (out, lse)."""
+    op = "merge_partials"
+    if isinstance(o_parts, torch.Tensor):
+        o_parts = list(o_parts.unbind(0))
+    if isinstance(lse_parts, torch.Tensor):
+        lse_parts = list(lse_parts.unbind(0))
+    n = len(o_parts)
+    if n < 1 or n > N.JL_MAX_PARTS or len(lse_parts) != n:
+        raise ValueError(f"{op}: need between 1 and {N.JL_MAX_PARTS} (out, lse) pairs")
+    o0 = o_parts[0]
+    if o0.dim() != 4 or lse_parts[0].dim() != 3:
+        raise ValueError("expected out=(B,S,H,D) and lse=(B,H,S)")
+    if not o0.is_cuda:
+        raise ValueError("fused merge requires CUDA tensors")
+    if o0.dtype not in _SUPPORTED_DTYPES:
+        raise ValueError(f"{op}: partial outputs must be torch.bfloat16, got {o0.dtype}")
+    _require_arch(op, o0.device)
+    B, S, H, D = o0.shape
+    for i, (o, l) in enumerate(zip(o_parts, lse_parts)):
+        if o.shape != o0.shape or o.dtype != o0.dtype or o.device != o0.device:
+            raise ValueError(f"{op}: part {i} shape/dtype/device mismatch")
+        if tuple(l.shape) != (B, H, S) or l.dtype != torch.float32 or l.device != o0.device:
+            raise ValueError(f"{op}: lse of part {i} must be float32 with shape {(B, H, S)}")
+        _require_contiguous(op, f"o_parts[{i}]", o)
+        _require_contiguous(op, f"lse_parts[{i}]", l)
+    if out is None:
+        out = torch.empty_like(o0)
+    else:
+        if out.shape != o0.shape or out.dtype != o0.dtype or out.device != o0.device:
+            raise ValueError(f"{op}: out shape/dtype/device mismatch")
+        _require_contiguous(op, "out", out)
+    if lse_out is None and return_lse:
+        lse_out = torch.empty(B, H, S, dtype=torch.float32, device=o0.device)
+    if lse_out is not None:
+        if tuple(lse_out.shape) != (B, H, S) or lse_out.dtype != torch.float32:
+            raise ValueError(f"{op}: lse_out must be float32 with shape {(B, H, S)}")
+        _require_contiguous(op, "lse_out", lse_out)
+    a = N.MergeArgs()
+    for i in range(n):
+        a.o[i] = o_parts[i].data_ptr()
+        a.lse[i] = lse_parts[i].data_ptr()
+    a.n_parts, a.batch, a.seqlen, a.heads, a.head_dim = n, B, S, H, D
+    a.round_like_reference = int(bool(round_like_reference))
+    a.out = out.data_ptr()
+    a.lse_out = lse_out.data_ptr() if lse_out is not None else None
+    with torch.cuda.device(o0.device):
+        N.check("jl_merge", N.lib().jl_merge(C.byref(a), _stream()))
+    return (out, lse_out) if return_lse else out
+
+
+# ----------------------------------------------------------------------------------------------
+# prefill
+# ----------------------------------------------------------------------------------------------
+
+def posmap_prefill(q_ops: Sequence[torch.Tensor], k_ops: Sequence[torch.Tensor], v: torch.Tensor, *,
+                   pmap: PositionMap, q_pos0: int, k_pos0: int = 0, softmax_scale: Optional[float] = None,
+                   k_block: int = 0, k_block_stride: int = 0, out: Optional[torch.Tensor] = None,
+                   lse: Optional[torch.Tensor] = None, return_lse: bool = True, impl: int = 0):
+    """Single-pass position-mapped causal attention (see jl_prefill).  q_ops[c]: (B,Sq,H,D) views sharing
+    strides; k_ops[c], v: (B,Skv,Hk,D) views (all k_ops share strides).  Returns (out, lse) or out."""
+    op = "posmap_prefill"
+    if len(q_ops) != pmap.n_classes or len(k_ops) != pmap.n_classes:
+        raise ValueError(f"{op}: the position map has {pmap.n_classes} classes; got {len(q_ops)} q and {len(k_ops)} k operands")
+    q0, k0 = q_ops[0], k_ops[0]
+    tensors = [(f"q[{i}]", t) for i, t in enumerate(q_ops)] + [(f"k[{i}]", t) for i, t in enumerate(k_ops)] + [("v", v)]
+    if not all(t.is_cuda for _, t in tensors):
+        raise ValueError(f"{op} requires CUDA tensors")
+    for name, t in tensors:
+        _check_view(op, name, t)
+    if q0.dtype not in _SUPPORTED_DTYPES:
+        raise ValueError(f"{op}: q must have dtype torch.bfloat16, got {q0.dtype}")
+    if not all(t.dtype == q0.dtype for _, t in tensors):
+        raise ValueError(f"{op}: Q/K/V tensors must share dtype")
+    if not all(t.device == q0.device for _, t in tensors):
+        raise ValueError(f"{op}: all tensors must be on the same CUDA device")
+    for t in q_ops[1:]:
+        if t.shape != q0.shape or [_st(t, i) for i in range(3)] != [_st(q0, i) for i in range(3)]:
+            raise ValueError(f"{op}: query operands must share shape and strides")
+    for t in k_ops[1:]:
+        if t.shape != k0.shape or [_st(t, i) for i in range(3)] != [_st(k0, i) for i in range(3)]:
+            raise ValueError(f"{op}: key operands must share shape and strides")
+    if k0.shape != v.shape:
+        raise ValueError(f"{op}: keys and value must share shape")
+    if q0.shape[0] != k0.shape[0] or q0.shape[3] != k0.shape[3]:
+        raise ValueError(f"{op}: Q/K batch and head-dim must match")
+    if q0.shape[2] % k0.shape[2] != 0:
+        raise ValueError(f"{op}: q heads must be divisible by kv heads")
+    _require_arch(op, q0.device)
+    B, Sq, H, D = q0.shape
+    Skv, Hk = k0.shape[1], k0.shape[2]
+    if out is None:
+        out = torch.empty(B, Sq, H, D, dtype=q0.dtype, device=q0.device)
+    else:
+        if tuple(out.shape) != (B, Sq, H, D) or out.dtype != q0.dtype or out.device != q0.device:
+            raise ValueError(f"{op}: out must be {q0.dtype} with shape {(B, Sq, H, D)}")
+        _check_view(op, "out", out)
+    if lse is None and return_lse:
+        lse = torch.empty(B, H, Sq, dtype=torch.float32, device=q0.device)
+    if lse is not None:
+        if tuple(lse.shape) != (B, H, Sq) or lse.dtype != torch.float32:
+            raise ValueError(f"{op}: lse must be float32 with shape {(B, H, Sq)}")
+        _require_contiguous(op, "lse", lse)
+    a = N.PrefillArgs()
+    for c in range(pmap.n_classes):
+        a.q[c] = q_ops[c].data_ptr()
+        a.k[c] = k_ops[c].data_ptr()
+    a.v, a.out = v.data_ptr(), out.data_ptr()
+    a.lse = lse.data_ptr() if lse is not None else None
+    a.q_stride_b, a.q_stride_s, a.q_stride_h = _st(q0, 0), _st(q0, 1), _st(q0, 2)
+    a.k_stride_b, a.k_stride_s, a.k_stride_h = _st(k0, 0), _st(k0, 1), _st(k0, 2)
+    a.v_stride_b, a.v_stride_s, a.v_stride_h = _st(v, 0), _st(v, 1), _st(v, 2)
+    a.o_stride_b, a.o_stride_s, a.o_stride_h = _st(out, 0), _st(out, 1), _st(out, 2)
+    a.batch, a.seqlen_q, a.seqlen_k, a.heads, a.kv_heads, a.head_dim = B, Sq, Skv, H, Hk, D
+    a.q_pos0, a.k_pos0, a.k_block, a.k_block_stride = int(q_pos0), int(k_pos0), int(k_block), int(k_block_stride)
+    a.softmax_scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
+    a.map = pmap.c_struct()
+    a.impl = int(impl)
+    with torch.cuda.device(q0.device):
+        N.check("jl_prefill", N.lib().jl_prefill(C.byref(a), _stream()))
+    return (out, lse) if return_lse else out
+
+
+def jetlong_prefill(q_base, q_group, k_base, k_group, value, *, seqstart_q: torch.Tensor,
+                    seqstart_q_scalar: Optional[int] = None, window_size_left: int,
+                    softmax_scale: Optional[float] = None, tile_m: int = 128, tile_n: int = 128,
+                    seqused_q=None, seqused_k=None, inv_freq=None, group_size=None, num_stages=None,
+                    deterministic: bool = False, out=None, impl: int = 0):
+    """Fused bifocal prefill with the tensor contract of the reference's level-2 entry point:
+    (B,S,H,D) base/group operands, int32 seqstart_q (B,), returns (out (B,S,H,D), lse (B,H,S))."""
+    op = "jetlong_prefill"
+    unsupported = {"seqused_q": seqused_q, "seqused_k": seqused_k, "inv_freq": inv_freq,
+                   "group_size": group_size, "num_stages": num_stages}
+    used = [n for n, val in unsupported.items() if val is not None]
+    if used:
+        raise ValueError(f"{op}: unsupported metadata arguments for the fused prefill: {', '.join(used)}")
+    if not all(t.is_cuda for t in (q_base, q_group, k_base, k_group, value, seqstart_q)):
+        raise ValueError(f"{op} requires CUDA tensors")
+    if not all(t.dim() == 4 for t in (q_base, q_group, k_base, k_group, value)):
+        raise ValueError(f"{op} expects rank-4 BSHD tensors")
+    if q_base.shape != q_group.shape:
+        raise ValueError(f"{op}: q_base and q_group must share shape")
+    if k_base.shape != k_group.shape or k_base.shape != value.shape:
+        raise ValueError(f"{op}: k_base, k_group, and value must share shape")
+    if seqstart_q.dtype != torch.int32 or seqstart_q.dim() != 1 or seqstart_q.shape[0] != q_base.shape[0]:
+        raise ValueError(f"{op}: seqstart_q must be int32 with shape (batch,)")
+    if tile_m <= 0 or tile_n <= 0:
+        raise ValueError(f"{op}: tile_m and tile_n must be positive")
+    if seqstart_q_scalar is None:
+        vals = set(int(x) for x in seqstart_q.detach().cpu().tolist())
+        if len(vals) != 1:
+            raise ValueError("prefill fastpath requires uniform seqstart_q across batch")
+        seqstart_q_scalar = vals.pop()
+    return posmap_prefill([q_base, q_group], [k_base, k_group], value, pmap=PositionMap.jetlong(window_size_left),
+                          q_pos0=int(seqstart_q_scalar), k_pos0=0, softmax_scale=softmax_scale, out=out, impl=impl)
+
+
+# ----------------------------------------------------------------------------------------------
+# decode
+# ----------------------------------------------------------------------------------------------
+
+@dataclass
+class KvSegment:
+    """One key/value range read in place by the decode kernel (see jl_kv_segment)."""
+    k: torch.Tensor            # (B, len, Hk, D) view
+    v: torch.Tensor
+    q_class: int               # index into the query operand list
+    rotate: bool = False       # regroup the keys in-kernel by (floor(p/G) - p) * inv_freq
+    pos0: int = 0              # absolute position of row 0 (used when rotate)
+    len_dev: Optional[torch.Tensor] = None   # optional int32 (B,) valid lengths
+
+
+def decode_segments(q_ops: Sequence[Optional[torch.Tensor]], segments: Sequence[KvSegment], *,
+                    softmax_scale: Optional[float] = None, inv_freq: Optional[torch.Tensor] = None,
+                    group_size: int = 1, num_splits: int = 0, out: Optional[torch.Tensor] = None,
+                    lse: Optional[torch.Tensor] = None, return_lse: bool = True,
+                    workspace: Optional[torch.Tensor] = None):
+    """Split-KV decode of one query token per sequence over in-place key segments (see jl_decode).
+    q_ops[c]: (B,1,H,D) views sharing strides (None for unused classes).  Returns (out (B,1,H,D), lse (B,H,1))."""
+    op = "decode_segments"
+    q0 = next(t for t in q_ops if t is not None)
+    if q0.dim() != 4:
+        raise ValueError(f"{op} expects rank-4 BSHD tensors")
+    if q0.shape[1] != 1:
+        raise ValueError(f"{op} requires seqlen_q == 1")
+    if q0.dtype not in _SUPPORTED_DTYPES:
+        raise ValueError(f"{op}: query must have dtype torch.bfloat16, got {q0.dtype}")
+    if not q0.is_cuda:
+        raise ValueError(f"{op} requires CUDA Q/K/V tensors")
+    if not 1 <= len(segments) <= N.JL_MAX_SEGMENTS:
+        raise ValueError(f"{op}: between 1 and {N.JL_MAX_SEGMENTS} segments")
+    _require_arch(op, q0.device)
+    B, _, H, D = q0.shape
+    a = N.DecodeArgs()
+    for c, t in enumerate(q_ops):
+        if t is None:
+            continue
+        if t.shape != q0.shape or t.dtype != q0.dtype or t.device != q0.device:
+            raise ValueError(f"{op}: query operands must share shape, dtype and device")
+        _check_view(op, f"q[{c}]", t)
+        if (_st(t, 0), _st(t, 2)) != (_st(q0, 0), _st(q0, 2)):
+            raise ValueError(f"{op}: query operands must share strides")
+        a.q[c] = t.data_ptr()
+    a.q_stride_b, a.q_stride_h = _st(q0, 0), _st(q0, 2)
+    Hk = segments[0].k.shape[2]
+    total = 0
+    keep = []
+    for i, s in enumerate(segments):
+        if s.k.dim() != 4 or s.v.dim() != 4:
+            raise ValueError(f"{op} expects rank-4 BSHD tensors")
+        if s.k.shape[:3] != s.v.shape[:3]:
+            raise ValueError(f"{op}: each K/V branch must share batch, sequence, and head dimensions")
+        if s.k.shape[0] != B:
+            raise ValueError(f"{op}: Q/K/V batch sizes must match")
+        if s.k.shape[2] != Hk:
+            raise ValueError(f"{op}: near and distant KV head counts must match")
+        if s.k.shape[-1] != D or s.v.shape[-1] != D:
+            raise ValueError(f"{op}: query and key head_dim must match")
+        if s.k.dtype != q0.dtype or s.v.dtype != q0.dtype:
+            raise ValueError(f"{op}: Q/K/V tensors must share dtype")
+        if s.k.device != q0.device or s.v.device != q0.device:
+            raise ValueError(f"{op}: Q/K/V tensors must be on the same CUDA device")
+        _check_view(op, f"segment[{i}].k", s.k)
+        _check_view(op, f"segment[{i}].v", s.v)
+        g = a.seg[i]
+        g.k, g.v = s.k.data_ptr(), s.v.data_ptr()
+        g.k_stride_b, g.k_stride_s, g.k_stride_h = _st(s.k, 0), _st(s.k, 1), _st(s.k, 2)
+        g.v_stride_b, g.v_stride_s, g.v_stride_h = _st(s.v, 0), _st(s.v, 1), _st(s.v, 2)
+        if s.len_dev is not None:
+            if tuple(s.len_dev.shape) != (B,) or s.len_dev.dtype != torch.int32 or s.len_dev.device != q0.device:
+                raise ValueError(f"{op}: segment lengths must be int32 with shape ({B},) on {q0.device}")
+            keep.append(s.len_dev.contiguous())
+            g.len_dev = keep[-1].data_ptr()
+        g.pos0, g.len, g.q_class, g.rotate = int(s.pos0), int(s.k.shape[1]), int(s.q_class), int(bool(s.rotate))
+        total += int(s.k.shape[1])
+    if H % Hk != 0:
+        raise ValueError(f"{op}: query heads must be divisible by kv heads")
+    a.n_segments, a.batch, a.heads, a.kv_heads, a.head_dim = len(segments), B, H, Hk, D
+    a.num_splits = int(num_splits)
+    a.softmax_scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
+    if inv_freq is not None:
+        inv_freq = inv_freq.to(device=q0.device, dtype=torch.float32).contiguous()
+        keep.append(inv_freq)
+        a.inv_freq = inv_freq.data_ptr()
+    a.group_size = int(group_size)
+    if out is None:
+        out = torch.empty(B, 1, H, D, dtype=q0.dtype, device=q0.device)
+    if lse is None and return_lse:
+        lse = torch.empty(B, H, 1, dtype=torch.float32, device=q0.device)
+    a.out = out.data_ptr()
+    a.lse = lse.data_ptr() if lse is not None else None
+    a.o_stride_b, a.o_stride_h = _st(out, 0), _st(out, 2)
+    lib = N.lib()
+    splits = num_splits if num_splits > 0 else lib.jl_decode_auto_splits(B, Hk, total)
+    need = lib.jl_decode_workspace_bytes(B, H, D, splits)
+    ws = workspace if workspace is not None else _workspace(q0.device, need)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel() * ws.element_size()
+    with torch.cuda.device(q0.device):
+        N.check("jl_decode", lib.jl_decode(C.byref(a), _stream()))
+    return (out, lse) if return_lse else out
+
+
+def _require_output(op, name, t, shape, dtype, device):
+    if t is None:
+        return
+    if tuple(t.shape) != shape:
+        raise ValueError(f"{op}: {name} must have shape {shape}, got {tuple(t.shape)}")
+    if t.dtype != dtype:
+        raise ValueError(f"{op}: {name} must have dtype {dtype}, got {t.dtype}")
+    if t.device != device:
+        raise ValueError(f"{op}: {name} must be on device {device}, got {t.device}")
+    _require_contiguous(op, name, t)
+
+
+def _require_metadata(op, name, t, shape, device):
+    if tuple(t.shape) != shape:
+        raise ValueError(f"{op}: {name} must have shape {shape}, got {tuple(t.shape)}")
+    if t.dtype != torch.int32:
+        raise ValueError(f"{op}: {name} must have dtype torch.int32, got {t.dtype}")
+    if t.device != device:
+        raise ValueError(f"{op}: {name} must be on device {device}, got {t.device}")
+
+
+def jetlong_decode(query_base, query_group, key_near, value_near, key_distant, value_distant, *,
+                   seqused_near: torch.Tensor, seqused_distant: torch.Tensor, jetlong_meta=None,
+                   inv_freq: torch.Tensor, group_size: int, out=None, lse=None, tile_m: int = 64,
+                   tile_n: int = 128, num_stages: int = 3, pack_gqa=None, k_mode: str = "consumer",
+                   num_splits: int = 0, active_splits=None, distant_k_grouped: bool = False,
+                   distant_pos0: int = 0):
+    """Fused bifocal decode with the tensor contract of the reference's level-2 entry point.
+
+    Near keys are scored with query_base, distant keys with query_group.  With
+    distant_k_grouped=False the distant keys are base-rotated and are regrouped in-kernel
+    (positions distant_pos0 + row).  Returns out, or (out, lse) when an lse tensor is passed."""
+    op = "jetlong_decode"
+    named = (("query_base", query_base), ("query_group", query_group), ("key_near", key_near),
+             ("value_near", value_near), ("key_distant", key_distant), ("value_distant", value_distant))
+    if not all(t.dim() == 4 for _, t in named):
+        raise ValueError(f"{op} expects rank-4 BSHD tensors")
+    if query_base.shape != query_group.shape:
+        raise ValueError(f"{op}: query_base and query_group must share shape")
+    if query_base.shape[1] != 1:
+        raise ValueError(f"{op} requires seqlen_q == 1")
+    if not all(t.is_cuda for _, t in named):
+        raise ValueError(f"{op} requires CUDA Q/K/V tensors")
+    if num_splits < 0:
+        raise ValueError(f"{op}: num_splits must be >= 0")
+    if inv_freq.device != query_base.device:
+        raise ValueError(f"{op}: inv_freq must be on device {query_base.device}, got {inv_freq.device}")
+    if inv_freq.dim() != 1 or inv_freq.numel() < query_base.shape[-1] // 2:
+        raise ValueError(f"{op}: inv_freq must have shape ({query_base.shape[-1] // 2},) or larger")
+    if not torch.is_floating_point(inv_freq):
+        raise ValueError(f"{op}: inv_freq must be a floating-point tensor, got {inv_freq.dtype}")
+    B, _, H, D = query_base.shape
+    dev = query_base.device
+    _require_metadata(op, "seqused_near", seqused_near, (B,), dev)
+    _require_metadata(op, "seqused_distant", seqused_distant, (B,), dev)
+    _require_output(op, "out", out, (B, 1, H, value_near.shape[-1]), query_base.dtype, dev)
+    _require_output(op, "lse", lse, (B, H, 1), torch.float32, dev)
+    if jetlong_meta is not None:
+        if jetlong_meta.dtype != torch.int32 or jetlong_meta.dim() != 2 or jetlong_meta.shape[1] < 3:
+            raise ValueError("jetlong_meta must be int32 with shape (B, >=3): [total_kv_len, boundary, group_size]")
+    if active_splits is not None:
+        _require_metadata(op, "active_splits", active_splits, (B,), dev)
+    return_lse = lse is not None
+    segs = [KvSegment(key_distant, value_distant, q_class=1, rotate=not distant_k_grouped, pos0=distant_pos0,
+                      len_dev=seqused_distant),
+            KvSegment(key_near, value_near, q_class=0, len_dev=seqused_near)]
+    res = decode_segments([query_base, query_group], segs, inv_freq=inv_freq, group_size=group_size,
+                          num_splits=num_splits, out=out, lse=lse, return_lse=return_lse)
+    return res
+
+
+# Names the reference's tests and benches import; same tensor contracts, B200 kernels underneath.
+fa4_cute_prefill_sm90_jetlong_fused = jetlong_prefill
+fa4_cute_decode_sm90_jetlong_fused = jetlong_decode
