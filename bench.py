@@ -1,0 +1,405 @@
+#!/usr/bin/env python
+"""Headline benchmark: Qwen3-8B `jetlong_fused` full-model prefill throughput (tok/s) at 131072
+tokens on B200, plus the decode-attention microbench at 131072 keys, with the roofline of the
+dominant kernel and the reference's CPU path timed beside it.
+
+    python bench.py --gpus 1 --steps 3 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference            # the reference's eager composition on the host cores
+
+One "step" is one prefill forward `model(input_ids, use_cache=True)` over a fresh 131072-token
+prompt (the reference's own protocol: scripts/throughput/bench_prefill_throughput.py:83-95 in the
+Jet-Long repository), random-init bf16 weights, uniform random token ids.  With N > 1 the key
+sequence of every attention call is sharded block-cyclically over the ranks and partial (O, LSE)
+pairs are combined after an NCCL all-gather (strong scaling: the prompt stays 131072 tokens).
+Rank 0 prints ONE JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path[:0] = [os.path.join(ROOT, "jet-long_b200")]
+
+import torch  # noqa: E402
+
+MODEL_DIMS = {
+    "qwen3-8b": dict(variant="Qwen3-8B-Base-jetlong_fused"),
+    "qwen3-4b": dict(variant="Qwen3-4B-Base-jetlong_fused"),
+    "qwen3-1.7b": dict(variant="Qwen3-1.7B-Base-jetlong_fused"),
+}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"], bf16_tflops_sustained=p["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+def model_config(name: str, w: int, w_0: int, layers: int | None):
+    from transformers.models.qwen3.configuration_qwen3 import Qwen3Config
+    with open(os.path.join(ROOT, "jet-long_b200", "model_configs", MODEL_DIMS[name]["variant"], "config.json")) as f:
+        d = json.load(f)
+    d.pop("auto_map", None)
+    d.pop("architectures", None)
+    d["jetlong"] = dict(d["jetlong"], w=w, w_0=w_0)
+    if layers:
+        d["num_hidden_layers"] = layers
+        d["max_window_layers"] = layers
+    cfg = Qwen3Config(**d)
+    cfg._attn_implementation = "sdpa"
+    return cfg
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        busy = sorted(sm)[len(sm) // 2:] if sm else []
+        return dict(sm_mhz=statistics.median(busy) if busy else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+# --------------------------------------------------------------------------------------------------
+# CPU baseline: the oracle (a restatement of the reference's eager composition) on the host cores
+# --------------------------------------------------------------------------------------------------
+
+def cpu_prefill_sample(S: int, dims: dict, w_0: int, G: int):
+    """Time a bounded sample of the prefill workload on the CPU and extrapolate to tokens/s.
+
+    Attention: the oracle's two-branch bifocal composition for two 128-row query blocks (rows
+    [S/2, S/2+128) and [S-128, S)) of 8 query heads (one per kv head) over the full key range,
+    scaled by (query heads / 8) x (all causal pairs / sampled pairs).  Dense layers: the fp32
+    projections + MLP of one layer on 256 tokens and a slice of the lm_head on 128 tokens, scaled to S tokens
+    and all layers."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import jetlong_oracle as orc
+    H, Hk, D, L = dims["heads"], dims["kv_heads"], 128, dims["layers"]
+    hidden, inter, vocab = dims["hidden"], dims["inter"], dims["vocab"]
+    torch.manual_seed(0)
+    inv = orc.default_inv_freq()
+    t_attn, pairs = 0.0, 0
+    for q0 in (S // 2, S - 128):
+        n_k = q0 + 128
+        k = torch.randn(1, n_k, Hk, D)
+        v = torch.randn(1, n_k, Hk, D)
+        q = torch.randn(1, 128, Hk, D)
+        t0 = time.perf_counter()
+        qp = (torch.arange(128) + q0).view(1, -1)
+        kp = torch.arange(n_k).view(1, -1)
+        qb, qg, kb, kg = orc.jetlong_operands(q, k, q_positions=qp, k_positions=kp, group_size=G, inv_freq=inv)
+        orc.jetlong_prefill(qb, qg, kb, kg, v, seqstart=q0, w0=w_0)
+        t_attn += time.perf_counter() - t0
+        pairs += 128 * q0 + 128 * 129 // 2
+    total_pairs = S * (S + 1) // 2
+    attn_layer = t_attn * (H / Hk) * (total_pairs / pairs)
+    x = torch.randn(256, hidden)
+    ws = [torch.randn(hidden, H * D), torch.randn(hidden, 2 * Hk * D), torch.randn(H * D, hidden),
+          torch.randn(hidden, 2 * inter), torch.randn(inter, hidden)]
+    t0 = time.perf_counter()
+    a = x @ ws[0]; _ = x @ ws[1]; _ = a @ ws[2]
+    u = x @ ws[3]
+    _ = (torch.nn.functional.silu(u[:, :inter]) * u[:, inter:]) @ ws[4]
+    dense_layer = (time.perf_counter() - t0) * (S / 256)
+    xh = torch.randn(128, hidden)
+    vslice = min(vocab, 16384)
+    wv = torch.randn(hidden, vslice)
+    t0 = time.perf_counter()
+    _ = xh @ wv
+    head = (time.perf_counter() - t0) * (S / 128) * (vocab / vslice)
+    total = L * (attn_layer + dense_layer) + head
+    return dict(tok_s=S / total, est_total_s=total, attn_s=L * attn_layer, dense_s=L * dense_layer + head,
+                sample_s=t_attn, cores=torch.get_num_threads(),
+                sample=(f"oracle bifocal attention for 2 query blocks of 128 rows (rows {S // 2}.. and {S - 128}..) x {Hk} heads "
+                        f"over the full key range + one layer's fp32 projections/MLP on 256 tokens + a 16384-column slice of the lm_head on 128 tokens; "
+                        f"extrapolated by causal-pair count, head count, token count and {L} layers"))
+
+
+def model_dims(cfg):
+    return dict(heads=cfg.num_attention_heads, kv_heads=cfg.num_key_value_heads, layers=cfg.num_hidden_layers,
+                hidden=cfg.hidden_size, inter=cfg.intermediate_size, vocab=cfg.vocab_size)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = model_config(args.model, args.w, args.w0, args.layers)
+    G = max(1, math.ceil(args.seq / args.w))
+    for _ in range(max(args.warmup, 0)):
+        cpu_prefill_sample(min(args.seq, 8192), model_dims(cfg), min(args.w0, 2048), G)
+    res = [cpu_prefill_sample(args.seq, model_dims(cfg), args.w0, G) for _ in range(max(args.steps, 1))]
+    best = max(res, key=lambda r: r["tok_s"])
+    line = dict(metric="prefill_tok_per_s", value=best["tok_s"], unit="tok/s", n_gpus=args.gpus, steps=args.steps,
+                warmup=args.warmup, ms_per_step=best["est_total_s"] * 1e3, higher_is_better=True, scaling="strong",
+                vs_baseline=None, dtype="f32", data="synthetic", impl="reference",
+                config=workload_config(args, cfg, G),
+                cpu_baseline=dict(value=best["tok_s"], unit="tok/s", cores=best["cores"], kind="port", sample=best["sample"]),
+                e2e=dict(value=best["tok_s"], unit="tok/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+                note="reference fused kernels are gated to sm_90 and need flash_attn.cute (not installed): the reference's "
+                     "eager composition (restated in oracle/) is timed on the host cores on a bounded sample and extrapolated")
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, cfg, G):
+    return dict(workload=f"{args.model} jetlong_fused full-model prefill, batch 1, {args.seq} tokens",
+                layers=cfg.num_hidden_layers, heads=cfg.num_attention_heads, kv_heads=cfg.num_key_value_heads,
+                head_dim=128, hidden=cfg.hidden_size, w=args.w, w_0=args.w0, group_size=G,
+                logits="all positions (reference bench protocol)" if args.logits_to_keep == 0 else f"last {args.logits_to_keep}",
+                l2="inputs and weights far exceed the 126 MB L2; decode microbench flushes L2 (256 MB write) between iterations",
+                parallelism=f"kv-sequence-sharded x{args.gpus}" if args.gpus > 1 else "single GPU")
+
+
+# --------------------------------------------------------------------------------------------------
+# decode-attention microbench (the reference's protocol: CUDA graph, 256 MB L2 flush, median)
+# --------------------------------------------------------------------------------------------------
+
+def decode_microbench(peaks, shard, iters=20):
+    from jetlm.kernels import cute_jetlong_backend as backend, jetlong_ops as ops
+    out = {}
+    H, Hk, D, ctx, w0, G = 32, 8, 128, 131072, 32768, 4
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    inv = 1.0 / (1.0e6 ** (torch.arange(0, D, 2, device="cuda").float() / D))
+    for B in (1, 8):
+        torch.manual_seed(0)
+        q = torch.randn(B, 1, H, D, device="cuda").bfloat16()
+        qg = torch.randn(B, 1, H, D, device="cuda").bfloat16()
+        kc = torch.randn(B, Hk, ctx, D, device="cuda").bfloat16()
+        vc = torch.randn(B, Hk, ctx, D, device="cuda").bfloat16()
+        boundary = ctx - 1 - w0
+        kv, vv = kc.transpose(1, 2), vc.transpose(1, 2)
+        if shard is None:
+            segs = [ops.KvSegment(kv[:, :boundary], vv[:, :boundary], 1), ops.KvSegment(kv[:, boundary:], vv[:, boundary:], 0)]
+            fn_pre = lambda: ops.decode_segments([q, qg], segs, return_lse=False)
+        else:
+            fn_pre = None
+        fn_inplace = lambda: backend.fused_jetlong_decode_cache(q, qg, kc, vc, boundary=boundary, inv_freq=inv, group_size=G,
+                                                                has_any_pad=False, training=False)
+        res = {}
+        for tag, fn in (("pregrouped", fn_pre), ("inplace_regroup", fn_inplace)):
+            if fn is None:
+                continue
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            graph = None
+            if shard is None:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    fn()
+            ts = []
+            for _ in range(iters):
+                flush.zero_()
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                if shard is not None:
+                    torch.distributed.barrier()
+                s.record()
+                graph.replay() if graph is not None else fn()
+                e.record()
+                torch.cuda.synchronize()
+                ts.append(s.elapsed_time(e) * 1e3)
+            us = statistics.median(ts)
+            if shard is not None:
+                t = torch.tensor([us], device="cuda")
+                torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+                us = float(t)
+            nbytes = B * ctx * Hk * D * 2 * 2
+            res[tag] = dict(us=round(us, 2), gbs=round(nbytes / us / 1e3, 1),
+                            frac_of_measured_hbm=round(nbytes / us / 1e3 / peaks["hbm_gbs"], 4))
+        out[f"batch{B}"] = res
+        del kc, vc, kv, vv
+    out["config"] = dict(heads=H, kv_heads=Hk, head_dim=D, ctx=ctx, w_0=w0, group_size=G,
+                         timing="CUDA graph replay" if shard is None else "eager launches + NCCL all-gather, max over ranks",
+                         l2="256 MB flush before every iteration")
+    return out
+
+
+# --------------------------------------------------------------------------------------------------
+# main arm
+# --------------------------------------------------------------------------------------------------
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="qwen3-8b", choices=sorted(MODEL_DIMS))
+    ap.add_argument("--seq", type=int, default=131072)
+    ap.add_argument("--w", type=int, default=32768)
+    ap.add_argument("--w0", type=int, default=32768)
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (debug only; shown in config)")
+    ap.add_argument("--logits-to-keep", type=int, default=0)
+    ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    from jetlm.kernels import _native
+    _native.lib()                                     # fail loudly right away if the extension is missing
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU path")
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    shard = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        from jetlm.kernels import cute_jetlong_backend as backend
+        from jetlm.kernels.sequence_parallel import SequenceShard
+        shard = SequenceShard(rank, world, block=1024)
+        backend.configure_sequence_sharding(shard)
+
+    from jetlm.kernels import jetlong_ops as ops
+    from jetlm.modeling.jetlong_fused import Qwen3JetLongFusedForCausalLM
+
+    peaks = load_peaks()
+    cfg = model_config(args.model, args.w, args.w0, args.layers or None)
+    G = max(1, math.ceil(args.seq / args.w))
+    torch.manual_seed(0)
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    with torch.device("cuda"):
+        model = Qwen3JetLongFusedForCausalLM(cfg).eval()
+    torch.set_default_dtype(prev)
+
+    gen = torch.Generator().manual_seed(1)
+    ids_host = torch.randint(0, cfg.vocab_size, (1, args.seq), generator=gen).pin_memory()
+    ids_dev = ids_host.cuda()
+    result_host = torch.empty(cfg.vocab_size, dtype=torch.bfloat16).pin_memory()
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    @torch.inference_mode()
+    def step(ids):
+        out = model(input_ids=ids, use_cache=True, logits_to_keep=args.logits_to_keep)
+        return out.logits[0, -1]
+
+    @torch.inference_mode()
+    def step_e2e():
+        ids = ids_host.to("cuda", non_blocking=True)
+        last = step(ids)
+        result_host.copy_(last, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def timed(fn, k):
+        barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(k):
+            fn()
+        e.record()
+        barrier()
+        ms = torch.tensor([s.elapsed_time(e)], device="cuda")
+        if world > 1:
+            torch.distributed.all_reduce(ms, op=torch.distributed.ReduceOp.MAX)
+        return float(ms)
+
+    for _ in range(args.warmup):
+        step(ids_dev)
+    sink: list = []
+    launches0 = ops.kernel_launch_count()
+    sampler = ClockSampler(local)
+    sampler.start()
+    ops.set_event_sink(sink)
+    total_ms = timed(lambda: step(ids_dev), args.steps)
+    ops.set_event_sink(None)
+    launches = ops.kernel_launch_count() - launches0
+    e2e_ms = timed(step_e2e, args.steps)
+    clocks = sampler.stop()
+
+    # roofline of the dominant kernel: algorithmic FLOPs of one launch / its mean device time
+    torch.cuda.synchronize()
+    pre = [(s.elapsed_time(e), info) for name, s, e, info in sink if name == "jl_prefill"]
+    H, D = cfg.num_attention_heads, 128
+    flops_launch = 4.0 * D * H * args.seq * (args.seq + 1) / 2 / world
+    mean_ms = statistics.mean(t for t, _ in pre) if pre else float("nan")
+    achieved = flops_launch / (mean_ms * 1e-3) / 1e12
+    roofline = dict(bound="tensor", kernel="jl_prefill (bifocal attention)", achieved=round(achieved, 1),
+                    peak=peaks["bf16_tflops_sustained"], unit="TFLOP/s",
+                    frac=round(achieved / peaks["bf16_tflops_sustained"], 4), peak_source=peaks["source"] + " (sustained)",
+                    frac_of_burst=round(achieved / peaks["bf16_tflops"], 4), frac_of_nominal_2250=round(achieved / 2250.0, 4),
+                    launches_timed=len(pre), mean_launch_ms=round(mean_ms, 3),
+                    attention_share_of_step=round(sum(t for t, _ in pre) / total_ms, 4) if pre else None,
+                    algorithmic_flops_per_launch=flops_launch, traffic=None)
+
+    line = dict(metric="prefill_tok_per_s", value=round(args.seq * args.steps / (total_ms * 1e-3), 1), unit="tok/s",
+                n_gpus=world, steps=args.steps, warmup=args.warmup, ms_per_step=round(total_ms / args.steps, 2),
+                higher_is_better=True, scaling="strong", vs_baseline=None, dtype="bf16", data="synthetic",
+                config=workload_config(args, cfg, G), clocks=clocks,
+                e2e=dict(value=round(args.seq * args.steps / (e2e_ms * 1e-3), 1), unit="tok/s",
+                         h2d_bytes_per_step=ids_host.numel() * ids_host.element_size(),
+                         d2h_bytes_per_step=result_host.numel() * result_host.element_size()),
+                gpu_launches=launches, roofline=roofline)
+
+    del model
+    torch.cuda.empty_cache()
+    if not args.no_decode:
+        line["decode_attn"] = decode_microbench(peaks, shard)
+    if rank == 0 and world == 1 and not args.no_cpu:
+        c = cpu_prefill_sample(args.seq, model_dims(cfg), args.w0, G)
+        line["cpu_baseline"] = dict(value=round(c["tok_s"], 3), unit="tok/s", cores=c["cores"], kind="port", sample=c["sample"],
+                                    sample_seconds=round(c["sample_s"], 2))
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -11,6 +11,17 @@ from __future__ import annotations
 import torch
 
 from . import jetlong_ops as ops
+from .sequence_parallel import SequenceShard, sharded_attention
+
+_SHARD: SequenceShard | None = None
+
+
+def configure_sequence_sharding(shard: SequenceShard | None) -> None:
+    """Split the key sequence of every following call across the ranks of `shard` (None = off).
+    Prefill takes a block-cyclic stripe of the keys, decode a contiguous range; partial (O, LSE)
+    pairs are all-gathered and merged, so every rank still returns the full result."""
+    global _SHARD
+    _SHARD = shard if shard is not None and shard.world > 1 else None
 
 
 def fused_jetlong_prefill(query_base, query_group, key_base, key_group, value, *, seqstart_q: int,
@@ -21,6 +32,16 @@ def fused_jetlong_prefill(query_base, query_group, key_base, key_group, value, *
     if has_any_pad:
         raise RuntimeError("JetLong backend 'fused' does not support left-padded prefill batches")
     t = lambda x: x.transpose(1, 2)
+    if _SHARD is not None:
+        sh = _SHARD
+        pos0, blk, stride = sh.geometry()
+        kb, kg, vv = (sh.take_stripe(x, dim=2) for x in (key_base, key_group, value))     # this rank's cache stripe
+        local = lambda: ops.posmap_prefill([t(query_base), t(query_group)], [t(kb), t(kg)], t(vv),
+                                           pmap=ops.PositionMap.jetlong(int(window_size_left)),
+                                           q_pos0=int(seqstart_q), k_pos0=pos0, k_block=blk, k_block_stride=stride,
+                                           softmax_scale=softmax_scale)
+        out, _ = sharded_attention(local, ops.merge_partials, sh)
+        return out
     out = ops.posmap_prefill([t(query_base), t(query_group)], [t(key_base), t(key_group)], t(value),
                              pmap=ops.PositionMap.jetlong(int(window_size_left)), q_pos0=int(seqstart_q),
                              softmax_scale=softmax_scale, return_lse=False)
@@ -40,3 +61,41 @@ def fused_jetlong_decode(query_base, query_group, key_near, value_near, key_dist
     segs = [ops.KvSegment(key_distant_group, value_distant, q_class=1),
             ops.KvSegment(key_near, value_near, q_class=0)]
     return ops.decode_segments([query_base, query_group], segs, return_lse=False)
+
+
+def fused_jetlong_decode_cache(query_base, query_group, key_cache, value_cache, *, boundary: int, inv_freq,
+                               group_size: int, softmax_scale=None, has_any_pad: bool, training: bool,
+                               cache_pos0: int = 0, return_lse: bool = False):
+    """Decode straight off a base-rotated (B,Hk,S,D) cache: keys [0, boundary) are the far class and are
+    regrouped inside the kernel while they stream, keys [boundary, S) are the near class.  Replaces the
+    reference's per-token host-side regroup of the whole distant cache plus its slice / pad copies
+    (modeling :428-440, backend :143-155).  cache_pos0 is the absolute position of cache row 0 (non-zero
+    for a sequence shard)."""
+    if training:
+        raise RuntimeError("JetLong backend 'fused' is inference-only")
+    if has_any_pad:
+        raise RuntimeError("JetLong backend 'fused' does not support left-padded decode batches")
+    kc, vc = key_cache.transpose(1, 2), value_cache.transpose(1, 2)        # (B,S,Hk,D) views
+    if _SHARD is not None and cache_pos0 == 0:
+        sh = _SHARD
+        lo, hi = sh.contiguous_range(kc.shape[1])
+        part = lambda: _decode_range(query_base, query_group, kc[:, lo:hi], vc[:, lo:hi], int(boundary) - lo, lo,
+                                     inv_freq, group_size, softmax_scale, True)
+        out, lse = sharded_attention(part, ops.merge_partials, sh)
+        return (out, lse) if return_lse else out
+    return _decode_range(query_base, query_group, kc, vc, int(boundary) - int(cache_pos0), int(cache_pos0),
+                         inv_freq, group_size, softmax_scale, return_lse)
+
+
+def _decode_range(query_base, query_group, kc, vc, b, pos0, inv_freq, group_size, softmax_scale, return_lse):
+    """Decode over rows of a (B,S,Hk,D) cache view whose row 0 has absolute position pos0; rows < b are far."""
+    b = max(0, min(b, kc.shape[1]))
+    segs = []
+    if b > 0:
+        segs.append(ops.KvSegment(kc[:, :b], vc[:, :b], q_class=1, rotate=True, pos0=int(pos0)))
+    if b < kc.shape[1]:
+        segs.append(ops.KvSegment(kc[:, b:], vc[:, b:], q_class=0))
+    if not segs:
+        raise RuntimeError("JetLong backend 'fused' got an empty key range")
+    return ops.decode_segments([query_base, query_group], segs, inv_freq=inv_freq, group_size=int(group_size),
+                               softmax_scale=softmax_scale, return_lse=return_lse)

@@ -60,6 +60,35 @@ def _st(t: torch.Tensor, i: int) -> int:
     return t.stride(i) if t.shape[i] > 1 else 0
 
 
+# Instrumentation used by the benchmark: kernel launches issued through this module, and (when a list
+# is installed with set_event_sink) a CUDA event pair around every attention kernel launch.
+LAUNCHES = {"jl_prefill": 0, "jl_decode": 0, "jl_merge": 0, "jl_rotate": 0}
+KERNELS_PER_CALL = {"jl_prefill": 1, "jl_decode": 2, "jl_merge": 1, "jl_rotate": 1}
+_EVENT_SINK: Optional[list] = None
+
+
+def set_event_sink(sink: Optional[list]) -> None:
+    """sink receives (name, start_event, end_event, info) per prefill/decode launch; None disables."""
+    global _EVENT_SINK
+    _EVENT_SINK = sink
+
+
+def kernel_launch_count() -> int:
+    return sum(LAUNCHES[k] * KERNELS_PER_CALL[k] for k in LAUNCHES)
+
+
+def _timed_call(name: str, fn, info=None) -> None:
+    LAUNCHES[name] += 1
+    if _EVENT_SINK is None or name not in ("jl_prefill", "jl_decode"):
+        N.check(name, fn())
+        return
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    N.check(name, fn())
+    e.record()
+    _EVENT_SINK.append((name, s, e, info))
+
+
 _WORKSPACES: dict[tuple, torch.Tensor] = {}
 
 
@@ -127,7 +156,7 @@ def rope_rotate(x: torch.Tensor, inv_freq: torch.Tensor, *, pos0: int = 0, div: 
                      B, S, H, D, int(pos0), int(div), int(div_mul), int(mod), int(mod_mul), int(add), int(t_max),
                      inv_freq.data_ptr())
     with torch.cuda.device(x.device):
-        N.check("jl_rotate", N.lib().jl_rotate(C.byref(a), _stream()))
+        _timed_call("jl_rotate", lambda: N.lib().jl_rotate(C.byref(a), _stream()))
     return out
 
 
@@ -195,7 +224,7 @@ def merge_partials(o_parts: Sequence[torch.Tensor], lse_parts: Sequence[torch.Te
     a.out = out.data_ptr()
     a.lse_out = lse_out.data_ptr() if lse_out is not None else None
     with torch.cuda.device(o0.device):
-        N.check("jl_merge", N.lib().jl_merge(C.byref(a), _stream()))
+        _timed_call("jl_merge", lambda: N.lib().jl_merge(C.byref(a), _stream()))
     return (out, lse_out) if return_lse else out
 
 
@@ -267,7 +296,8 @@ def posmap_prefill(q_ops: Sequence[torch.Tensor], k_ops: Sequence[torch.Tensor],
     a.map = pmap.c_struct()
     a.impl = int(impl)
     with torch.cuda.device(q0.device):
-        N.check("jl_prefill", N.lib().jl_prefill(C.byref(a), _stream()))
+        _timed_call("jl_prefill", lambda: N.lib().jl_prefill(C.byref(a), _stream()),
+                    dict(B=B, Sq=Sq, Skv=Skv, H=H, q_pos0=int(q_pos0)))
     return (out, lse) if return_lse else out
 
 
@@ -406,7 +436,7 @@ def decode_segments(q_ops: Sequence[Optional[torch.Tensor]], segments: Sequence[
     ws = workspace if workspace is not None else _workspace(q0.device, need)
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel() * ws.element_size()
     with torch.cuda.device(q0.device):
-        N.check("jl_decode", lib.jl_decode(C.byref(a), _stream()))
+        _timed_call("jl_decode", lambda: lib.jl_decode(C.byref(a), _stream()), dict(B=B, keys=total, Hk=Hk))
     return (out, lse) if return_lse else out
 
 

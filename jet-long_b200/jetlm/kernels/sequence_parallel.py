@@ -1,0 +1,78 @@
+"""KV-sequence sharding of the bifocal attention across the GPUs of one node.
+
+Softmax attention over a key set is associative under the (O, LSE) merge, so the key positions are
+split across ranks, every rank attends all its queries to its own keys, the partial (O, LSE) pairs
+are exchanged with ONE all-gather (NCCL over NVLink; remote data always lands in local HBM before
+the merge kernel reads it) and merged N-way on every rank.  There is no counterpart in the
+reference, which only replicates whole models across GPUs.
+
+Prefill uses a block-cyclic placement (block b belongs to rank b % world) so that causal work and
+cache memory are balanced; decode uses contiguous ranges.  The geometry helpers are pure Python and
+are exercised on CPU ranks (gloo) by the tests; the attention and merge callables are injected, so
+the same driver runs the CUDA kernels on GPUs and the oracle in those CPU tests.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class SequenceShard:
+    rank: int
+    world: int
+    block: int = 1024                 # keys per placement block (multiple of the kernels' 128-key tile)
+    group: Optional[object] = None    # torch.distributed process group (None = default)
+
+    # ---- block-cyclic placement (prefill) ----
+    def owned_rows(self, n_keys: int) -> torch.Tensor:
+        """Global key rows owned by this rank, ascending."""
+        starts = range(self.rank * self.block, n_keys, self.world * self.block)
+        if len(starts) == 0:
+            return torch.empty(0, dtype=torch.long)
+        return torch.cat([torch.arange(s, min(s + self.block, n_keys)) for s in starts])
+
+    def n_owned(self, n_keys: int) -> int:
+        full, rem = divmod(n_keys, self.world * self.block)
+        extra = min(max(rem - self.rank * self.block, 0), self.block)
+        return full * self.block + extra
+
+    def geometry(self) -> tuple[int, int, int]:
+        """(k_pos0, k_block, k_block_stride) of the owned rows for jl_prefill's key-position map."""
+        return self.rank * self.block, self.block, self.world * self.block
+
+    def take_stripe(self, x: torch.Tensor, dim: int = 1) -> torch.Tensor:
+        """The owned blocks of x along `dim`, packed contiguously (what this rank's cache holds)."""
+        n = x.shape[dim]
+        idx = self.owned_rows(n).to(x.device)
+        return x.index_select(dim, idx)
+
+    # ---- contiguous placement (decode) ----
+    def contiguous_range(self, n_keys: int) -> tuple[int, int]:
+        per = -(-n_keys // self.world)
+        lo = min(self.rank * per, n_keys)
+        return lo, min(lo + per, n_keys)
+
+
+def gather_partials(out: torch.Tensor, lse: torch.Tensor, shard: SequenceShard):
+    """All-gather one (O, LSE) pair per rank.  out (B,S,H,D), lse (B,H,S) fp32 ->
+    (outs (world,B,S,H,D), lses (world,B,H,S)), identical on every rank."""
+    outs = torch.empty((shard.world, *out.shape), dtype=out.dtype, device=out.device)
+    lses = torch.empty((shard.world, *lse.shape), dtype=lse.dtype, device=lse.device)
+    dist.all_gather_into_tensor(outs, out.contiguous(), group=shard.group)
+    dist.all_gather_into_tensor(lses, lse.contiguous(), group=shard.group)
+    return outs, lses
+
+
+def sharded_attention(local_attention: Callable[[], tuple[torch.Tensor, torch.Tensor]],
+                      merge: Callable[[Sequence[torch.Tensor], Sequence[torch.Tensor]], tuple[torch.Tensor, torch.Tensor]],
+                      shard: SequenceShard):
+    """partial (O, LSE) over this rank's keys -> all-gather -> N-way merge.  Returns (out, lse)."""
+    out, lse = local_attention()
+    if shard.world == 1:
+        return out, lse
+    outs, lses = gather_partials(out, lse, shard)
+    return merge(list(outs.unbind(0)), list(lses.unbind(0)))

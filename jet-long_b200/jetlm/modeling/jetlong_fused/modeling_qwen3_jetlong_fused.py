@@ -1,0 +1,309 @@
+"""Qwen3 with JetLong bifocal attention on the B200 kernels — the `jetlong_fused` method surface.
+
+Same class names, config keys (`config.jetlong = {"w", "w_0", ...}`), parameter names and
+`auto_map` target as the reference's jetlm/modeling/jetlong_fused/modeling_qwen3_jetlong_fused.py,
+so a `*-jetlong_fused` model directory loads unchanged.  What differs is below the surface:
+
+  * within the pretrained window (L <= w) attention is stock Qwen3 (reference :299-320);
+  * beyond it, the extended prefill / decode paths (reference :322-461) keep the reference's
+    position semantics — exact RoPE for 0 <= q-k <= w_0, positions floor(p/G) beyond, with
+    G = ceil(L/w) recomputed per forward call — but RoPE, regrouping and attention run in the
+    sm_100a kernels: fused fp32 rotation passes instead of ~10 elementwise torch kernels, one
+    single-pass bifocal attention kernel instead of packed-2S FA4 + merge, and a decode kernel that
+    regroups the far keys while it streams the cache instead of re-rotating the whole distant
+    cache on the host side every token;
+  * no per-layer host synchronisation: positions come from the cache length on the host.
+
+Runs under transformers >= 5.5 (layer types read from config, no reliance on cache_position).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+from torch import nn
+
+from transformers.cache_utils import Cache, DynamicCache
+from transformers.generation import GenerationMixin
+from transformers.masking_utils import create_causal_mask, create_sliding_window_causal_mask
+from transformers.modeling_outputs import BaseModelOutputWithPast, CausalLMOutputWithPast
+from transformers.modeling_utils import ALL_ATTENTION_FUNCTIONS
+from transformers.models.qwen3.configuration_qwen3 import Qwen3Config
+from transformers.models.qwen3.modeling_qwen3 import (
+    Qwen3DecoderLayer,
+    Qwen3PreTrainedModel,
+    Qwen3RMSNorm,
+    Qwen3RotaryEmbedding,
+    apply_rotary_pos_emb,
+    eager_attention_forward,
+)
+from transformers.utils import can_return_tuple
+from transformers.utils.generic import merge_with_config_defaults
+from transformers.utils.output_capturing import capture_outputs
+
+
+def _jetlong_cfg(config) -> Optional[dict]:
+    cfg = getattr(config, "jetlong", None)
+    if cfg is None and hasattr(config, "to_dict"):
+        cfg = config.to_dict().get("jetlong", None)
+    return cfg
+
+
+@dataclass
+class BifocalPlan:
+    """Host-side facts about one extended forward call, shared by all layers."""
+    group_size: int          # G = ceil(L_curr / w)
+    q_pos0: int              # absolute position of the first query token
+    max_q_pos: int           # absolute position of the last query token
+    has_any_pad: bool        # a left-padded batch (unsupported by the fused kernels)
+
+
+class Qwen3JetLongFusedRotaryEmbedding(Qwen3RotaryEmbedding):
+    """Base RoPE tables plus, past the pretrained window, the dynamic group size.
+
+    Returns (cos, sin) while L_curr = max position + 1 <= w, else
+    (cos, sin, G, inv_freq, position_ids, plan) — the first five entries are the reference's
+    extended tuple (:148-158); `plan` carries the same facts as host integers."""
+
+    def __init__(self, config: Qwen3Config, device=None):
+        super().__init__(config, device)
+        cfg = _jetlong_cfg(config)
+        self.jetlong_enabled = cfg is not None
+        if self.jetlong_enabled:
+            self.jetlong_w = int(cfg["w"])
+            self.jetlong_w_0 = int(cfg["w_0"])
+
+    @torch.no_grad()
+    def forward(self, x, position_ids, max_position: Optional[int] = None, kv_len: Optional[int] = None):
+        cos, sin = super().forward(x, position_ids)
+        if not self.jetlong_enabled:
+            return cos, sin
+        if max_position is None:
+            max_position = int(position_ids.max().item())      # caller-supplied positions: read them back
+        l_curr = max_position + 1
+        if l_curr <= self.jetlong_w:
+            return cos, sin
+        group = max(1, math.ceil(l_curr / self.jetlong_w))
+        seq = position_ids.shape[-1]
+        has_pad = False
+        if position_ids.shape[0] > 1 and kv_len is not None:
+            has_pad = bool(((kv_len - 1 - position_ids[:, -1]) > 0).any().item())
+        plan = BifocalPlan(group, max_position - seq + 1, max_position, has_pad)
+        return cos, sin, group, self.inv_freq.to(device=x.device, dtype=torch.float32), position_ids, plan
+
+
+class Qwen3JetLongFusedAttention(nn.Module):
+    """Qwen3 attention whose long-context branch is the bifocal kernel family."""
+
+    def __init__(self, config: Qwen3Config, layer_idx: int):
+        super().__init__()
+        self.config = config
+        self.layer_idx = layer_idx
+        self.layer_type = config.layer_types[layer_idx] if hasattr(config, "layer_types") else None
+        self.head_dim = getattr(config, "head_dim", None) or config.hidden_size // config.num_attention_heads
+        self.num_heads = config.num_attention_heads
+        self.num_kv_heads = config.num_key_value_heads
+        self.num_key_value_groups = self.num_heads // self.num_kv_heads
+        self.scaling = self.head_dim ** -0.5
+        self.attention_dropout = config.attention_dropout
+        self.is_causal = True
+        bias = config.attention_bias
+        self.q_proj = nn.Linear(config.hidden_size, self.num_heads * self.head_dim, bias=bias)
+        self.k_proj = nn.Linear(config.hidden_size, self.num_kv_heads * self.head_dim, bias=bias)
+        self.v_proj = nn.Linear(config.hidden_size, self.num_kv_heads * self.head_dim, bias=bias)
+        self.o_proj = nn.Linear(self.num_heads * self.head_dim, config.hidden_size, bias=bias)
+        self.q_norm = Qwen3RMSNorm(self.head_dim, eps=config.rms_norm_eps)
+        self.k_norm = Qwen3RMSNorm(self.head_dim, eps=config.rms_norm_eps)
+        self.sliding_window = config.sliding_window if self.layer_type == "sliding_attention" else None
+        cfg = _jetlong_cfg(config)
+        self.jetlong_enabled = cfg is not None
+        if self.jetlong_enabled:
+            self.jetlong_w = int(cfg["w"])
+            self.jetlong_w_0 = int(cfg["w_0"])
+
+    # -- stock Qwen3 attention (inside the pretrained window) --------------------------------------
+    def _within_window(self, q, k, v, position_embeddings, attention_mask, past_key_values, out_shape, **kwargs):
+        cos, sin = position_embeddings[:2]
+        q, k, v = (t.transpose(1, 2) for t in (q, k, v))
+        q, k = apply_rotary_pos_emb(q, k, cos, sin)
+        if past_key_values is not None:
+            k, v = past_key_values.update(k, v, self.layer_idx, {"sin": sin, "cos": cos})
+        interface = ALL_ATTENTION_FUNCTIONS.get_interface(self.config._attn_implementation, eager_attention_forward)
+        out, weights = interface(self, q, k, v, attention_mask,
+                                 dropout=0.0 if not self.training else self.attention_dropout,
+                                 scaling=self.scaling, sliding_window=self.sliding_window, **kwargs)
+        return self.o_proj(out.reshape(*out_shape, -1).contiguous()), weights
+
+    def forward(self, hidden_states, position_embeddings, attention_mask=None, past_key_values: Cache | None = None,
+                cache_position=None, **kwargs):
+        bsz, seq = hidden_states.shape[:2]
+        out_shape = (bsz, seq)
+        H, Hk, D = self.num_heads, self.num_kv_heads, self.head_dim
+        q = self.q_norm(self.q_proj(hidden_states).view(bsz, seq, H, D))
+        k = self.k_norm(self.k_proj(hidden_states).view(bsz, seq, Hk, D))
+        v = self.v_proj(hidden_states).view(bsz, seq, Hk, D)
+
+        if len(position_embeddings) < 4:
+            return self._within_window(q, k, v, position_embeddings, attention_mask, past_key_values, out_shape, **kwargs)
+
+        # ---- extended (bifocal) paths -------------------------------------------------------------
+        from jetlm.kernels import cute_jetlong_backend as backend      # resolved per call: the plugin seam
+        from jetlm.kernels import jetlong_ops as ops
+
+        group, inv_freq = position_embeddings[2], position_embeddings[3]
+        plan: BifocalPlan | None = position_embeddings[5] if len(position_embeddings) > 5 else None
+        if plan is None:      # driven with the reference's 5-tuple: recover the host facts from the tensors
+            pos = position_embeddings[4]
+            mx = int(pos.max().item())
+            plan = BifocalPlan(int(group), mx - seq + 1, mx, False)
+        if self.training:
+            raise RuntimeError("JetLong backend 'fused' is inference-only")
+        w_0 = self.jetlong_w_0
+
+        # base RoPE in one fused pass each; K is written straight into (B, Hk, S, D) cache layout
+        q_base = ops.rope_base(q, inv_freq, pos0=plan.q_pos0)
+        k_new = torch.empty(bsz, Hk, seq, D, dtype=k.dtype, device=k.device)
+        ops.rope_base(k, inv_freq, pos0=plan.q_pos0, out=k_new.transpose(1, 2))
+        v_new = v.transpose(1, 2)
+        if past_key_values is not None:
+            k_all, v_all = past_key_values.update(k_new, v_new, self.layer_idx, {})
+        else:
+            k_all, v_all = k_new, v_new
+        kv_len = k_all.shape[2]
+        q_group = ops.rope_regroup(q_base, inv_freq, group_size=group, pos0=plan.q_pos0)
+
+        if seq > 1:
+            # prefill / chunked prefill: regroup every cached key once for this call's G, then one kernel
+            k_group = torch.empty(bsz, Hk, kv_len, D, dtype=k_all.dtype, device=k_all.device)
+            ops.rope_regroup(k_all.transpose(1, 2), inv_freq, group_size=group, pos0=0, out=k_group.transpose(1, 2))
+            if k_all.stride() != k_group.stride():           # a cache that hands out non-dense views
+                k_all = k_all.contiguous()
+            attn = backend.fused_jetlong_prefill(
+                q_base.transpose(1, 2), q_group.transpose(1, 2), k_all, k_group, v_all,
+                seqstart_q=kv_len - seq, window_size_left=w_0, softmax_scale=self.scaling,
+                has_any_pad=plan.has_any_pad, training=self.training)
+        else:
+            boundary = max(plan.max_q_pos - w_0, 0)
+            if boundary == 0:
+                raise RuntimeError(
+                    f"jetlong_fused requires a non-empty distant decode region (decode context must exceed "
+                    f"w_0={w_0}); use the 'jetlong' method for short contexts.")
+            attn = backend.fused_jetlong_decode_cache(
+                q_base, q_group, k_all, v_all, boundary=boundary, inv_freq=inv_freq, group_size=group,
+                softmax_scale=self.scaling, has_any_pad=plan.has_any_pad, training=self.training)
+        return self.o_proj(attn.reshape(*out_shape, -1)), None
+
+
+class Qwen3JetLongFusedDecoderLayer(Qwen3DecoderLayer):
+    def __init__(self, config: Qwen3Config, layer_idx: int):
+        super().__init__(config, layer_idx)
+        self.self_attn = Qwen3JetLongFusedAttention(config=config, layer_idx=layer_idx)
+        self.attention_type = config.layer_types[layer_idx]
+
+
+class Qwen3JetLongFusedModel(Qwen3PreTrainedModel):
+    def __init__(self, config: Qwen3Config):
+        super().__init__(config)
+        self.padding_idx = config.pad_token_id
+        self.vocab_size = config.vocab_size
+        self.embed_tokens = nn.Embedding(config.vocab_size, config.hidden_size, self.padding_idx)
+        self.layers = nn.ModuleList(
+            Qwen3JetLongFusedDecoderLayer(config, i) for i in range(config.num_hidden_layers))
+        self.norm = Qwen3RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
+        self.rotary_emb = Qwen3JetLongFusedRotaryEmbedding(config=config)
+        self.gradient_checkpointing = False
+        self.has_sliding_layers = "sliding_attention" in self.config.layer_types
+        self.post_init()
+
+    @merge_with_config_defaults
+    @capture_outputs
+    def forward(self, input_ids=None, attention_mask=None, position_ids=None, past_key_values: Cache | None = None,
+                inputs_embeds=None, use_cache=None, cache_position=None, **kwargs) -> BaseModelOutputWithPast:
+        if (input_ids is None) ^ (inputs_embeds is not None):
+            raise ValueError("You must specify exactly one of input_ids or inputs_embeds")
+        if inputs_embeds is None:
+            inputs_embeds = self.embed_tokens(input_ids)
+        if use_cache and past_key_values is None:
+            past_key_values = DynamicCache(config=self.config)
+        seen = past_key_values.get_seq_length() if past_key_values is not None else 0
+        seq = inputs_embeds.shape[1]
+        host_max = None
+        if position_ids is None:
+            if cache_position is not None:
+                position_ids = cache_position.unsqueeze(0)
+            else:
+                position_ids = (torch.arange(seq, device=inputs_embeds.device) + seen).unsqueeze(0)
+                host_max = seen + seq - 1                     # known without touching the device
+        hidden = inputs_embeds
+        position_embeddings = self.rotary_emb(hidden, position_ids, max_position=host_max, kv_len=seen + seq)
+        extended = len(position_embeddings) >= 4
+
+        mask_map = attention_mask if isinstance(attention_mask, dict) else None
+        if mask_map is None and not extended:                  # the bifocal kernels mask by position
+            mk = dict(config=self.config, inputs_embeds=inputs_embeds, attention_mask=attention_mask,
+                      past_key_values=past_key_values, position_ids=position_ids)
+            mask_map = {"full_attention": create_causal_mask(**mk)}
+            if self.has_sliding_layers:
+                mask_map["sliding_attention"] = create_sliding_window_causal_mask(**mk)
+
+        for i, layer in enumerate(self.layers[: self.config.num_hidden_layers]):
+            hidden = layer(hidden,
+                           attention_mask=None if extended else mask_map[self.config.layer_types[i]],
+                           position_embeddings=position_embeddings, position_ids=position_ids,
+                           past_key_values=past_key_values, use_cache=use_cache, **kwargs)
+        hidden = self.norm(hidden)
+        return BaseModelOutputWithPast(last_hidden_state=hidden,
+                                       past_key_values=past_key_values if use_cache else None)
+
+
+class Qwen3JetLongFusedForCausalLM(Qwen3PreTrainedModel, GenerationMixin):
+    _tied_weights_keys = {"lm_head.weight": "model.embed_tokens.weight"}
+    _tp_plan = {"lm_head": "colwise_gather_output"}
+    _pp_plan = {"lm_head": (["hidden_states"], ["logits"])}
+
+    def __init__(self, config):
+        super().__init__(config)
+        self.model = Qwen3JetLongFusedModel(config)
+        self.vocab_size = config.vocab_size
+        self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False)
+        self.post_init()
+
+    def get_input_embeddings(self):
+        return self.model.embed_tokens
+
+    def set_input_embeddings(self, value):
+        self.model.embed_tokens = value
+
+    def get_output_embeddings(self):
+        return self.lm_head
+
+    def set_output_embeddings(self, new_embeddings):
+        self.lm_head = new_embeddings
+
+    def set_decoder(self, decoder):
+        self.model = decoder
+
+    def get_decoder(self):
+        return self.model
+
+    @can_return_tuple
+    def forward(self, input_ids=None, attention_mask=None, position_ids=None, past_key_values: Cache | None = None,
+                inputs_embeds=None, labels=None, use_cache=None, cache_position=None, logits_to_keep=0,
+                **kwargs) -> CausalLMOutputWithPast:
+        outputs: BaseModelOutputWithPast = self.model(
+            input_ids=input_ids, attention_mask=attention_mask, position_ids=position_ids,
+            past_key_values=past_key_values, inputs_embeds=inputs_embeds, use_cache=use_cache,
+            cache_position=cache_position, **kwargs)
+        hidden = outputs.last_hidden_state
+        keep = slice(-logits_to_keep, None) if isinstance(logits_to_keep, int) else logits_to_keep
+        logits = self.lm_head(hidden[:, keep, :])
+        loss = None
+        if labels is not None:
+            loss = self.loss_function(logits=logits, labels=labels, vocab_size=self.config.vocab_size, **kwargs)
+        return CausalLMOutputWithPast(loss=loss, logits=logits, past_key_values=outputs.past_key_values,
+                                      hidden_states=outputs.hidden_states, attentions=outputs.attentions)
+
+
+__all__ = ["Qwen3JetLongFusedForCausalLM", "Qwen3JetLongFusedModel", "Qwen3JetLongFusedRotaryEmbedding"]
