@@ -104,6 +104,10 @@ typedef struct {
 } jl_prefill_args;
 
 int jl_prefill(const jl_prefill_args* args, void* cuda_stream);
+/* Diagnostic (synchronises the device): 0 if no bounded wait inside the prefill kernel has ever given
+ * up on the current device, non-zero otherwise.  A kernel whose wait gives up drains and returns
+ * instead of hanging; its output is then invalid.  No reference counterpart. */
+int jl_prefill_status(void);
 
 /* ---------------------------------------------------------------------------------------------
  * jl_decode — split-KV attention of ONE query token per sequence over up to JL_MAX_SEGMENTS key

@@ -12,6 +12,7 @@ int launch_decode(const jl_decode_args* a, cudaStream_t stream);
 int launch_prefill_mma(const jl_prefill_args* a, cudaStream_t stream);
 int launch_prefill_tc(const jl_prefill_args* a, cudaStream_t stream);
 bool prefill_tc_supports(const jl_prefill_args* a);
+int prefill_tc_status();
 int32_t decode_auto_splits(int32_t batch, int32_t kv_heads, int64_t total_keys);
 size_t decode_workspace_bytes(int32_t batch, int32_t heads, int32_t head_dim, int32_t max_splits);
 
@@ -126,6 +127,8 @@ int jl_decode(const jl_decode_args* args, void* cuda_stream) {
   if (rc != JL_OK) return rc;
   return jl::launch_decode(args, static_cast<cudaStream_t>(cuda_stream));
 }
+
+int jl_prefill_status(void) { return jl::prefill_tc_status(); }
 
 int jl_prefill(const jl_prefill_args* args, void* cuda_stream) {
   int rc = jl::validate_prefill(args);

@@ -1,6 +1,571 @@
-// placeholder until the tcgen05 kernel lands: everything routes to the mma.sync kernel
+// Single-pass position-mapped causal prefill attention on the Blackwell tensor path:
+// TMA-staged tiles -> tcgen05.mma (QK^T from shared memory, PV with P in tensor memory) -> TMEM
+// accumulators, one online softmax carried across every position class.
+//
+// CTA = 256 query rows of one head = two 128-row query tiles that ping-pong on the tensor pipe.
+//   warp 0      TMA producer (Q tiles of the current class, K ring of 3, V ring of 2; 128B swizzle)
+//   warp 1      MMA issuer (one elected thread): S_t = Q_t K_j^T (SS), O_t += P_t V_j (TS)
+//   warp 2      TMEM allocator (all 512 columns: S0 | S1 | O0 | O1; P_t overlays the first 64 columns of S_t)
+//   warps 4-7   softmax of query tile 0: one thread per row (= TMEM lane), 128 scores in registers
+//   warps 8-11  softmax of query tile 1
+// Position map: the classes are processed as PHASES.  In phase c the CTA holds the class-c query
+// operand in shared memory and visits only the key tiles in which class c occurs for some of its
+// rows; per row, the keys of class c inside a tile form one column interval, so the mask is two
+// integer compares and tiles strictly inside a class need none.  A key tile crossed by a class
+// boundary is simply visited in both phases with complementary masks; the running (max, sum, O)
+// state is shared, so there is no second QK^T accumulator, no select, and no merge pass.
+// Rescaling of O is lazy: it happens only when a row maximum grows by more than 2^8.
+// Every wait is bounded; a wait that gives up sets a status word and lets the kernel drain.
+#include <cuda.h>
+
 #include "jl_common.cuh"
+
 namespace jl {
-bool prefill_tc_supports(const jl_prefill_args*) { return false; }
-int launch_prefill_tc(const jl_prefill_args*, cudaStream_t) { return fail(JL_ERR_UNSUPPORTED, "tcgen05 prefill not built"); }
+
+namespace tc {
+
+constexpr int kTileM = 128, kTileN = 128, kRowsPerCta = 256;
+constexpr int kKStages = 3, kVStages = 2;
+constexpr int kTileBytes = 128 * 256;           // 128 rows x 128 bf16
+constexpr int kHalfBytes = 128 * 128;           // one 64-column half (a TMA box)
+constexpr int kThreads = 384;
+constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr int64_t kNegInfPos = -(int64_t(1) << 60);
+
+struct Params {
+  int sq, sk, heads, kv_heads, batch;
+  int64_t q_pos0, k_pos0, k_block, k_block_stride;
+  float scale_log2;
+  int map_kind, n_classes;
+  int64_t near_span, chunk;
+  int k_map[JL_MAX_CLASSES];      // index into the distinct key tensor maps
+  __nv_bfloat16* out;
+  float* lse;
+  int64_t os_b, os_s, os_h;
+  int* status;                    // device status word (0 = ok)
+};
+
+struct Maps {
+  CUtensorMap q[JL_MAX_CLASSES];
+  CUtensorMap k[2];
+  CUtensorMap v;
+};
+
+struct Smem {
+  alignas(1024) uint8_t q[2][kTileBytes];
+  alignas(1024) uint8_t k[kKStages][kTileBytes];
+  alignas(1024) uint8_t v[kVStages][kTileBytes];
+  uint64_t q_full, q_free, k_full[kKStages], k_empty[kKStages], v_full[kVStages], v_empty[kVStages];
+  uint64_t s_full[2], p_full[2], all_done;
+  uint32_t tmem_base;
+  int failed;
+};
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: once any wait in the CTA has given up, all later waits return immediately so the
+// kernel drains instead of hanging; the host sees the status word.
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, Smem& sm) {
+  if (mbar_try_wait(bar, parity)) return;
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return;
+    if ((i & 1023u) == 1023u && *reinterpret_cast<volatile int*>(&sm.failed)) return;
+  }
+  *reinterpret_cast<volatile int*>(&sm.failed) = 1;
+}
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  // start address | leading byte offset | stride byte offset | version 1 (sm_100) | 128-byte swizzle
+  return static_cast<uint64_t>((saddr >> 4) & 0x3FFF) | (static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16) |
+         (static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32) | (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+// kind::f16 instruction descriptor: fp32 accumulate, bf16 A and B, M x N tile
+__device__ __host__ constexpr uint32_t instr_desc(int m, int n, int b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(b_mn_major) << 16) |
+         (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+               ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+               ::"r"(d_tmem), "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+#define JL_R32(r, o) "=r"(r[o + 0]), "=r"(r[o + 1]), "=r"(r[o + 2]), "=r"(r[o + 3]), "=r"(r[o + 4]), "=r"(r[o + 5]), "=r"(r[o + 6]), "=r"(r[o + 7]), \
+  "=r"(r[o + 8]), "=r"(r[o + 9]), "=r"(r[o + 10]), "=r"(r[o + 11]), "=r"(r[o + 12]), "=r"(r[o + 13]), "=r"(r[o + 14]), "=r"(r[o + 15]), \
+  "=r"(r[o + 16]), "=r"(r[o + 17]), "=r"(r[o + 18]), "=r"(r[o + 19]), "=r"(r[o + 20]), "=r"(r[o + 21]), "=r"(r[o + 22]), "=r"(r[o + 23]), \
+  "=r"(r[o + 24]), "=r"(r[o + 25]), "=r"(r[o + 26]), "=r"(r[o + 27]), "=r"(r[o + 28]), "=r"(r[o + 29]), "=r"(r[o + 30]), "=r"(r[o + 31])
+#define JL_W32(r, o) "r"(r[o + 0]), "r"(r[o + 1]), "r"(r[o + 2]), "r"(r[o + 3]), "r"(r[o + 4]), "r"(r[o + 5]), "r"(r[o + 6]), "r"(r[o + 7]), \
+  "r"(r[o + 8]), "r"(r[o + 9]), "r"(r[o + 10]), "r"(r[o + 11]), "r"(r[o + 12]), "r"(r[o + 13]), "r"(r[o + 14]), "r"(r[o + 15]), \
+  "r"(r[o + 16]), "r"(r[o + 17]), "r"(r[o + 18]), "r"(r[o + 19]), "r"(r[o + 20]), "r"(r[o + 21]), "r"(r[o + 22]), "r"(r[o + 23]), \
+  "r"(r[o + 24]), "r"(r[o + 25]), "r"(r[o + 26]), "r"(r[o + 27]), "r"(r[o + 28]), "r"(r[o + 29]), "r"(r[o + 30]), "r"(r[o + 31])
+#define JL_TMEM_LD32(taddr, r, o)                                                                                          \
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18," \
+               "%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"                                               \
+               : JL_R32(r, o) : "r"(taddr))
+#define JL_TMEM_ST32(taddr, r, o)                                                                                          \
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17," \
+               "%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"                                              \
+               ::"r"(taddr), JL_W32(r, o) : "memory")
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------------------------
+// Position-map arithmetic shared by all roles
+// ---------------------------------------------------------------------------------------------
+// Inclusive range of key POSITIONS that belong to class c for a query at position pq.
+__device__ __forceinline__ void class_interval(const Params& p, int c, int64_t pq, int64_t& lo, int64_t& hi) {
+  if (p.map_kind == JL_MAP_BAND) {
+    if (c == 0) { lo = pq - p.near_span; hi = pq; }
+    else        { lo = kNegInfPos;       hi = pq - p.near_span - 1; }
+  } else {
+    const int64_t cs = pq / p.chunk * p.chunk;
+    if (c == 0)      { lo = cs;           hi = pq; }
+    else if (c == 1) { lo = cs - p.chunk; hi = cs - 1; }
+    else             { lo = kNegInfPos;   hi = cs - p.chunk - 1; }
+  }
+}
+// First local key row whose position is >= pos, and last local row whose position is <= pos
+// (rows are laid out in blocks of k_block positions every k_block_stride positions; k_block == 0: contiguous).
+__device__ __forceinline__ int64_t row_at_or_after(const Params& p, int64_t pos) {
+  const int64_t rel = pos - p.k_pos0;
+  if (rel <= 0) return 0;
+  if (p.k_block <= 0) return rel;
+  const int64_t b = rel / p.k_block_stride, off = rel - b * p.k_block_stride;
+  return off < p.k_block ? b * p.k_block + off : (b + 1) * p.k_block;
+}
+__device__ __forceinline__ int64_t row_at_or_before(const Params& p, int64_t pos) {
+  const int64_t rel = pos - p.k_pos0;
+  if (rel < 0) return -1;
+  if (p.k_block <= 0) return rel;
+  const int64_t b = rel / p.k_block_stride, off = rel - b * p.k_block_stride;
+  return off < p.k_block ? b * p.k_block + off : b * p.k_block + p.k_block - 1;
+}
+
+struct Schedule {
+  int n_phases;
+  int cls[JL_MAX_CLASSES], j_lo[JL_MAX_CLASSES], n_tiles[JL_MAX_CLASSES];
+  int total;
+};
+
+__device__ __forceinline__ Schedule make_schedule(const Params& p, int q_row0) {
+  Schedule s;
+  s.n_phases = 0;
+  s.total = 0;
+  const int rows = min(kRowsPerCta, p.sq - q_row0);
+  const int64_t pq_first = p.q_pos0 + q_row0, pq_last = pq_first + rows - 1;
+  for (int c = p.n_classes - 1; c >= 0; --c) {       // far classes first, the diagonal last
+    int64_t lo, hi, dummy;
+    class_interval(p, c, pq_first, lo, dummy);
+    class_interval(p, c, pq_last, dummy, hi);
+    if (hi < lo) continue;
+    int64_t r_lo = row_at_or_after(p, lo), r_hi = row_at_or_before(p, hi);
+    if (r_hi > p.sk - 1) r_hi = p.sk - 1;
+    if (r_lo > r_hi) continue;
+    const int i = s.n_phases++;
+    s.cls[i] = c;
+    s.j_lo[i] = static_cast<int>(r_lo / kTileN);
+    s.n_tiles[i] = static_cast<int>(r_hi / kTileN) - s.j_lo[i] + 1;
+    s.total += s.n_tiles[i];
+  }
+  return s;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The kernel
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_constant__ Maps maps, const Params p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q_tile_pair = gridDim.x - 1 - blockIdx.x;          // latest (heaviest) rows first
+  const int head = blockIdx.y, b = blockIdx.z;
+  const int kvh = head / (p.heads / p.kv_heads);
+  const int q_row0 = q_tile_pair * kRowsPerCta;
+  const Schedule sched = make_schedule(p, q_row0);
+
+  if (threadIdx.x == 0) {
+    sm.failed = 0;
+    mbar_init(&sm.q_full, 1);
+    mbar_init(&sm.q_free, 1);
+    for (int i = 0; i < kKStages; ++i) { mbar_init(&sm.k_full[i], 1); mbar_init(&sm.k_empty[i], 1); }
+    for (int i = 0; i < kVStages; ++i) { mbar_init(&sm.v_full[i], 1); mbar_init(&sm.v_empty[i], 1); }
+    for (int t = 0; t < 2; ++t) { mbar_init(&sm.s_full[t], 1); mbar_init(&sm.p_full[t], 128); }
+    mbar_init(&sm.all_done, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(512u));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+
+  if (warp == 0) {
+    // ===================================== TMA producer =====================================
+    if (lane == 0) {
+      int g = 0;
+      for (int ph = 0; ph < sched.n_phases; ++ph) {
+        const int c = sched.cls[ph];
+        // the query tiles of this class replace the previous class's once its QK^T MMAs have retired
+        mbar_wait(&sm.q_free, (ph & 1) ^ 1, sm);
+        mbar_expect_tx(&sm.q_full, 2 * kTileBytes);
+        for (int t = 0; t < 2; ++t)
+          for (int h = 0; h < 2; ++h)
+            tma_load_4d(sm.q[t] + h * kHalfBytes, &maps.q[c], &sm.q_full, h * 64, head, q_row0 + t * kTileM, b);
+        const CUtensorMap* km = &maps.k[p.k_map[c]];
+        for (int jj = 0; jj < sched.n_tiles[ph]; ++jj, ++g) {
+          const int row = (sched.j_lo[ph] + jj) * kTileN;
+          const int ks = g % kKStages, vs = g % kVStages;
+          mbar_wait(&sm.k_empty[ks], ((g / kKStages) & 1) ^ 1, sm);
+          mbar_expect_tx(&sm.k_full[ks], kTileBytes);
+          for (int h = 0; h < 2; ++h) tma_load_4d(sm.k[ks] + h * kHalfBytes, km, &sm.k_full[ks], h * 64, kvh, row, b);
+          mbar_wait(&sm.v_empty[vs], ((g / kVStages) & 1) ^ 1, sm);
+          mbar_expect_tx(&sm.v_full[vs], kTileBytes);
+          for (int h = 0; h < 2; ++h) tma_load_4d(sm.v[vs] + h * kHalfBytes, &maps.v, &sm.v_full[vs], h * 64, kvh, row, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ====================================== MMA issuer ======================================
+    if (lane == 0 && sched.total > 0) {
+      const uint32_t idesc_qk = instr_desc(kTileM, kTileN, 0);
+      const uint32_t idesc_pv = instr_desc(kTileM, kHeadDim, 1);
+      auto issue_qk = [&](int t, int g) {
+        const int ks = g % kKStages;
+        const uint32_t qa = smem_u32(sm.q[t]), ka = smem_u32(sm.k[ks]);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
+          mma_ss(tmem + t * 128, smem_desc(qa + off, 16, 1024), smem_desc(ka + off, 16, 1024), idesc_qk, kk > 0);
+        }
+        mma_commit(&sm.s_full[t]);
+      };
+      int g = 0;           // global tile counter (K/V ring index, barrier parities)
+      for (int ph = 0; ph < sched.n_phases; ++ph) {
+        mbar_wait(&sm.q_full, ph & 1, sm);
+        tc_fence_after();
+        const int n = sched.n_tiles[ph];
+        // S_t(first tile of the phase)
+        mbar_wait(&sm.k_full[g % kKStages], (g / kKStages) & 1, sm);
+        tc_fence_after();
+        issue_qk(0, g);
+        issue_qk(1, g);
+        if (n == 1) mma_commit(&sm.q_free);
+        mma_commit(&sm.k_empty[g % kKStages]);
+        for (int jj = 0; jj < n; ++jj, ++g) {
+          const int vs = g % kVStages;
+          const bool more = jj + 1 < n;
+          for (int t = 0; t < 2; ++t) {
+            mbar_wait(&sm.p_full[t], g & 1, sm);
+            if (t == 0) mbar_wait(&sm.v_full[vs], (g / kVStages) & 1, sm);
+            tc_fence_after();
+            const uint32_t va = smem_u32(sm.v[vs]);
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk)
+              mma_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8, smem_desc(va + kk * 2048, kHalfBytes, 1024), idesc_pv,
+                     (g > 0 || kk > 0) ? 1u : 0u);
+            if (t == 1) mma_commit(&sm.v_empty[vs]);
+            if (more) {
+              const int gn = g + 1;
+              if (t == 0) { mbar_wait(&sm.k_full[gn % kKStages], (gn / kKStages) & 1, sm); tc_fence_after(); }
+              issue_qk(t, gn);
+              if (t == 1) {
+                if (jj + 2 == n) mma_commit(&sm.q_free);       // last QK^T of this phase issued
+                mma_commit(&sm.k_empty[gn % kKStages]);
+              }
+            }
+          }
+        }
+      }
+      mma_commit(&sm.all_done);
+    }
+  } else if (warp >= 4) {
+    // ================================ softmax + epilogue ================================
+    const int t = (warp - 4) >> 2;                          // query tile 0 / 1
+    const int quad = warp & 3;                              // TMEM lane quadrant this warp may access
+    const int row_in_tile = quad * 32 + lane;
+    const int q_row = q_row0 + t * kTileM + row_in_tile;
+    const bool row_valid = q_row < p.sq;
+    const int64_t pq = p.q_pos0 + (row_valid ? q_row : p.sq - 1);
+    // bounds of this tile's valid rows, for the uniform-tile test
+    const int tile_rows = min(kTileM, p.sq - (q_row0 + t * kTileM));
+    const int64_t pq_t0 = p.q_pos0 + q_row0 + t * kTileM;
+    const int64_t pq_t1 = pq_t0 + (tile_rows > 0 ? tile_rows - 1 : 0);
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t t_s = tmem + lane_base + t * 128;
+    const uint32_t t_o = tmem + lane_base + 256 + t * 128;
+
+    float m_ref = -INFINITY, l_sum = 0.f;
+    int g = 0;
+    for (int ph = 0; ph < sched.n_phases; ++ph) {
+      const int c = sched.cls[ph];
+      int64_t row_lo, row_hi, tile_lo_max, tile_hi_min, dummy;
+      class_interval(p, c, pq, row_lo, row_hi);
+      class_interval(p, c, pq_t1, tile_lo_max, dummy);      // largest lower bound over the tile's rows
+      class_interval(p, c, pq_t0, dummy, tile_hi_min);      // smallest upper bound over the tile's rows
+      for (int jj = 0; jj < sched.n_tiles[ph]; ++jj, ++g) {
+        const int j = sched.j_lo[ph] + jj;
+        const int64_t tp0 = key_position(static_cast<int64_t>(j) * kTileN, p.k_pos0, p.k_block, p.k_block_stride);
+        const int valid = min(kTileN, p.sk - j * kTileN);
+        const bool uniform = valid == kTileN && tile_lo_max <= tp0 && tile_hi_min >= tp0 + kTileN - 1;
+
+        mbar_wait(&sm.s_full[t], g & 1, sm);
+        tc_fence_after();
+        uint32_t s[128];
+        JL_TMEM_LD32(t_s + 0, s, 0);
+        JL_TMEM_LD32(t_s + 32, s, 32);
+        JL_TMEM_LD32(t_s + 64, s, 64);
+        JL_TMEM_LD32(t_s + 96, s, 96);
+        tmem_wait_ld();
+
+        float mx = -INFINITY;
+        if (uniform) {
+#pragma unroll
+          for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
+        } else {
+          const int64_t lo64 = row_lo - tp0, hi64 = row_hi - tp0 + 1;
+          const int c_lo = lo64 < 0 ? 0 : (lo64 > 128 ? 128 : static_cast<int>(lo64));
+          const int c_hi = hi64 < 0 ? 0 : (hi64 > valid ? valid : static_cast<int>(hi64));
+#pragma unroll
+          for (int i = 0; i < 128; ++i) {
+            const float v = (i >= c_lo && i < c_hi) ? __uint_as_float(s[i]) : -INFINITY;
+            s[i] = __float_as_uint(v);
+            mx = fmaxf(mx, v);
+          }
+        }
+        mx *= p.scale_log2;                                  // scale > 0: max commutes with the scaling
+        // lazy rescale: only when some row of the warp outgrew its reference maximum by 2^8
+        const bool grow = mx > m_ref + 8.f;
+        if (__any_sync(0xffffffffu, grow)) {
+          const float m_new = fmaxf(m_ref, mx);
+          const float alpha = m_new == -INFINITY ? 1.f : fast_exp2(m_ref - m_new);
+          l_sum *= alpha;
+          if (g > 0) {
+            // O_t is quiescent here: S_t(g) ready implies P_t V(g-1) retired, and P_t V(g) waits for our P
+#pragma unroll
+            for (int cchunk = 0; cchunk < 4; ++cchunk) {
+              uint32_t o[32];
+              JL_TMEM_LD32(t_o + cchunk * 32, o, 0);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              JL_TMEM_ST32(t_o + cchunk * 32, o, 0);
+            }
+          }
+          m_ref = m_new;
+        }
+        const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+        float rs = 0.f;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t pk[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(s[half * 64 + 2 * i]), p.scale_log2, -m_use));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(s[half * 64 + 2 * i + 1]), p.scale_log2, -m_use));
+            rs += p0 + p1;
+            pk[i] = pack_bf16x2(p0, p1);
+          }
+          JL_TMEM_ST32(t_s + half * 32, pk, 0);
+        }
+        l_sum += rs;
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&sm.p_full[t]);
+      }
+    }
+
+    // ---- epilogue: O / l -> bf16, LSE ----
+    if (sched.total > 0) {
+      mbar_wait(&sm.all_done, 0, sm);
+      tc_fence_after();
+    }
+    const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+    __nv_bfloat16* orow = p.out + b * p.os_b + static_cast<int64_t>(q_row) * p.os_s + head * p.os_h;
+#pragma unroll
+    for (int cchunk = 0; cchunk < 4; ++cchunk) {
+      uint32_t o[32];
+      if (sched.total > 0) {
+        JL_TMEM_LD32(t_o + cchunk * 32, o, 0);
+        tmem_wait_ld();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = 0u;
+      }
+      if (row_valid) {
+#pragma unroll
+        for (int v4 = 0; v4 < 4; ++v4) {
+          uint4 w;
+          w.x = pack_bf16x2(__uint_as_float(o[v4 * 8 + 0]) * inv, __uint_as_float(o[v4 * 8 + 1]) * inv);
+          w.y = pack_bf16x2(__uint_as_float(o[v4 * 8 + 2]) * inv, __uint_as_float(o[v4 * 8 + 3]) * inv);
+          w.z = pack_bf16x2(__uint_as_float(o[v4 * 8 + 4]) * inv, __uint_as_float(o[v4 * 8 + 5]) * inv);
+          w.w = pack_bf16x2(__uint_as_float(o[v4 * 8 + 6]) * inv, __uint_as_float(o[v4 * 8 + 7]) * inv);
+          *reinterpret_cast<uint4*>(orow + cchunk * 32 + v4 * 8) = w;
+        }
+      }
+    }
+    if (row_valid && p.lse != nullptr)
+      p.lse[(static_cast<int64_t>(b) * p.heads + head) * p.sq + q_row] = l_sum > 0.f ? (m_ref + log2f(l_sum)) * kLn2 : -INFINITY;
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u));
+  }
+  if (threadIdx.x == 0 && sm.failed && p.status != nullptr) atomicExch(p.status, 1);
+}
+
+}  // namespace tc
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    cudaDriverEntryPointQueryResult q;
+    void* ptr = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess) fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// (B, S, Hx, 128) bf16 view -> 4-D map (d, h, s, b), box 64 x 1 x 128 x 1, 128-byte swizzle, zero fill past the end.
+static int make_map(CUtensorMap* m, const void* base, int batch, int seq, int heads, int64_t sb, int64_t ss, int64_t sh) {
+  EncodeTiledFn enc = encode_fn();
+  if (enc == nullptr) return fail(JL_ERR_LAUNCH, "jl_prefill: cuTensorMapEncodeTiled is not available from the driver");
+  // size-1 dimensions may arrive with stride 0; the encoder wants positive multiples of 16 bytes
+  const int64_t dflt = 256;
+  const cuuint64_t dims[4] = {128, static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(seq), static_cast<cuuint64_t>(batch)};
+  const cuuint64_t strides[3] = {static_cast<cuuint64_t>((heads > 1 && sh > 0 ? sh : dflt / 2) * 2),
+                                 static_cast<cuuint64_t>((seq > 1 && ss > 0 ? ss : dflt / 2) * 2),
+                                 static_cast<cuuint64_t>((batch > 1 && sb > 0 ? sb : dflt / 2) * 2)};
+  const cuuint32_t box[4] = {64, 1, 128, 1};
+  const cuuint32_t es[4] = {1, 1, 1, 1};
+  const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, es,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(JL_ERR_BAD_ARG, "jl_prefill: tensor map encoding failed (CUresult %d)", static_cast<int>(r));
+  return JL_OK;
+}
+
+bool prefill_tc_supports(const jl_prefill_args* a) {
+  if (a->seqlen_k < 1) return false;
+  if (a->k_block > 0 && a->k_block < a->seqlen_k && (a->k_block % tc::kTileN != 0)) return false;
+  int distinct = 0;
+  const void* seen[2] = {nullptr, nullptr};
+  for (int c = 0; c < a->map.n_classes; ++c) {
+    bool found = false;
+    for (int i = 0; i < distinct; ++i) found |= seen[i] == a->k[c];
+    if (!found) {
+      if (distinct == 2) return false;
+      seen[distinct++] = a->k[c];
+    }
+  }
+  return true;
+}
+
+// Status word of the bounded waits: a file-scope device variable (no allocation), one per device image.
+__device__ int g_prefill_status = 0;
+
+static int* status_word() {
+  static int* words[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (words[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_prefill_status) != cudaSuccess) return nullptr;
+    words[dev] = static_cast<int*>(ptr);
+  }
+  return words[dev];
+}
+
+int prefill_tc_status() {
+  int* w = status_word();
+  int v = 0;
+  if (w != nullptr && cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) v = -1;
+  return v;
+}
+
+int launch_prefill_tc(const jl_prefill_args* a, cudaStream_t stream) {
+  tc::Maps maps;
+  tc::Params p{};
+  int n_k = 0;
+  const void* kptr[2] = {nullptr, nullptr};
+  for (int c = 0; c < a->map.n_classes; ++c) {
+    int rc = make_map(&maps.q[c], a->q[c], a->batch, a->seqlen_q, a->heads, a->q_stride_b, a->q_stride_s, a->q_stride_h);
+    if (rc != JL_OK) return rc;
+    int slot = -1;
+    for (int i = 0; i < n_k; ++i)
+      if (kptr[i] == a->k[c]) slot = i;
+    if (slot < 0) {
+      slot = n_k++;
+      kptr[slot] = a->k[c];
+      rc = make_map(&maps.k[slot], a->k[c], a->batch, a->seqlen_k, a->kv_heads, a->k_stride_b, a->k_stride_s, a->k_stride_h);
+      if (rc != JL_OK) return rc;
+    }
+    p.k_map[c] = slot;
+  }
+  for (int c = a->map.n_classes; c < JL_MAX_CLASSES; ++c) maps.q[c] = maps.q[0];
+  if (n_k == 1) maps.k[1] = maps.k[0];
+  int rc = make_map(&maps.v, a->v, a->batch, a->seqlen_k, a->kv_heads, a->v_stride_b, a->v_stride_s, a->v_stride_h);
+  if (rc != JL_OK) return rc;
+  p.sq = a->seqlen_q; p.sk = a->seqlen_k; p.heads = a->heads; p.kv_heads = a->kv_heads; p.batch = a->batch;
+  p.q_pos0 = a->q_pos0; p.k_pos0 = a->k_pos0;
+  p.k_block = (a->k_block > 0 && a->k_block < a->seqlen_k) ? a->k_block : 0;
+  p.k_block_stride = a->k_block_stride;
+  p.scale_log2 = a->softmax_scale * kLog2e;
+  p.map_kind = a->map.kind; p.n_classes = a->map.n_classes;
+  p.near_span = a->map.near_span; p.chunk = a->map.chunk > 0 ? a->map.chunk : 1;
+  p.out = static_cast<__nv_bfloat16*>(a->out);
+  p.lse = a->lse;
+  p.os_b = a->o_stride_b; p.os_s = a->o_stride_s; p.os_h = a->o_stride_h;
+  p.status = status_word();
+  const int smem = static_cast<int>(sizeof(tc::Smem)) + 1024;
+  static bool attr_done = false;
+  if (!attr_done) {
+    if (cudaFuncSetAttribute(tc::prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return check_launch("jl_prefill (shared memory opt-in)");
+    attr_done = true;
+  }
+  dim3 grid((a->seqlen_q + tc::kRowsPerCta - 1) / tc::kRowsPerCta, a->heads, a->batch);
+  tc::prefill_tc_kernel<<<grid, tc::kThreads, smem, stream>>>(maps, p);
+  return check_launch("jl_prefill (tcgen05)");
+}
+
 }  // namespace jl

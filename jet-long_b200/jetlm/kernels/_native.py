@@ -85,6 +85,7 @@ EXPORTS = [
     ("jl_status_string", C.c_char_p, [C.c_int]),
     ("jl_last_error", C.c_char_p, []),
     ("jl_prefill", C.c_int, [C.POINTER(PrefillArgs), C.c_void_p]),
+    ("jl_prefill_status", C.c_int, []),
     ("jl_decode_workspace_bytes", C.c_size_t, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     ("jl_decode_auto_splits", C.c_int32, [C.c_int32, C.c_int32, C.c_int64]),
     ("jl_decode", C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
