@@ -158,6 +158,32 @@ size_t jl_decode_workspace_bytes(int32_t batch, int32_t heads, int32_t head_dim,
 int32_t jl_decode_auto_splits(int32_t batch, int32_t kv_heads, int64_t total_keys);
 int jl_decode(const jl_decode_args* args, void* cuda_stream);
 
+/* jl_decode_static — jl_decode for callers that cannot allocate device memory.  (No counterpart in
+ * the reference, whose Python layer always allocates its split-K workspace with torch.)
+ *
+ * Who needs it: a server that gives its whole device-memory budget to one arena when it starts and
+ * treats any later cudaMalloc as a bug (it may fail, and it can stall every stream on the device
+ * while it runs), or a plug-in that is handed nothing but input and output pointers and has no
+ * allocator of its own.  Such a caller has nowhere to get the split-KV workspace from, so this
+ * variant keeps the partials in a fixed array that is part of the library image.
+ *
+ * Same arguments and results as jl_decode; args->workspace and args->workspace_bytes are ignored.
+ * The library makes no allocation on this path.
+ *   - Limit: the partials, batch * heads * splits * (head_dim + 1) * 4 bytes, must fit in
+ *     jl_decode_static_scratch_bytes() (4 MiB; batch * heads * splits <= 8128).  Larger requests are
+ *     refused with JL_ERR_WORKSPACE and a message naming both sizes; nothing is launched.
+ *   - Cost: every GPU on which the library is loaded carries those 4 MiB until the process exits.
+ *   - The first call on each device looks up the array's device address (one cheap runtime query, made
+ *     with that device current).  Make that first call during start-up, before any stream capture
+ *     begins.
+ *   - All calls on a device share the one array, and it keeps whatever the previous call left in it.
+ *     Nothing in it has to start at zero: each launch writes every slot it later reads.  Two calls
+ *     whose kernels may overlap on the GPU (different streams, no dependency between them) race on
+ *     it; order them on one stream or with events, or give the overlapping ones jl_decode with
+ *     workspaces of their own. */
+int jl_decode_static(const jl_decode_args* args, void* cuda_stream);
+size_t jl_decode_static_scratch_bytes(void);
+
 /* ---------------------------------------------------------------------------------------------
  * jl_merge — N-way (O, LSE) merge of partial attention results over disjoint key sets:
  *   out = sum_p O_p e^{lse_p - m} / sum_p e^{lse_p - m},  lse = m + log sum_p e^{lse_p - m}.

@@ -9,6 +9,8 @@ namespace jl {
 int launch_merge(const jl_merge_args* a, cudaStream_t stream);
 int launch_rotate(const jl_rotate_args* a, cudaStream_t stream);
 int launch_decode(const jl_decode_args* a, cudaStream_t stream);
+int launch_decode_static(const jl_decode_args* a, cudaStream_t stream);
+size_t decode_static_scratch_bytes();
 int launch_prefill_mma(const jl_prefill_args* a, cudaStream_t stream);
 int launch_prefill_tc(const jl_prefill_args* a, cudaStream_t stream);
 bool prefill_tc_supports(const jl_prefill_args* a);
@@ -127,6 +129,15 @@ int jl_decode(const jl_decode_args* args, void* cuda_stream) {
   if (rc != JL_OK) return rc;
   return jl::launch_decode(args, static_cast<cudaStream_t>(cuda_stream));
 }
+
+int jl_decode_static(const jl_decode_args* args, void* cuda_stream) {
+  if (args == nullptr) return jl::fail(JL_ERR_BAD_ARG, "jl_decode_static: args is NULL");
+  int rc = jl::check_device_arch();
+  if (rc != JL_OK) return rc;
+  return jl::launch_decode_static(args, static_cast<cudaStream_t>(cuda_stream));
+}
+
+size_t jl_decode_static_scratch_bytes(void) { return jl::decode_static_scratch_bytes(); }
 
 int jl_prefill_status(void) { return jl::prefill_tc_status(); }
 

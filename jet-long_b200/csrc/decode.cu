@@ -414,4 +414,53 @@ int launch_decode(const jl_decode_args* a, cudaStream_t stream) {
   return check_launch("jl_decode (combine)");
 }
 
+// ---------------------------------------------------------------------------------------------
+// Decode with built-in scratch: for callers that are not allowed to allocate device memory.
+//
+// The split-KV partials normally live in a workspace the caller allocates.  Some callers cannot do
+// that: a serving process that hands all of its device memory to one arena at start-up and forbids
+// any later cudaMalloc (an allocation there can fail, fragment the arena's neighbour, or stall every
+// stream of the device while the driver services it), or a plug-in that only receives raw input and
+// output pointers from its host and owns no allocator at all.  For them the scratch is this fixed
+// array inside the library image.  It costs kStaticScratchBytes on every GPU that loads the library,
+// for the life of the process, whether or not this entry point is ever used.
+// ---------------------------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = size_t(4) << 20;      // 4 MiB: B * H * splits <= 8128 at head_dim 128
+static __device__ __align__(256) float g_decode_scratch[kStaticScratchBytes / sizeof(float)];
+
+int launch_decode_static(const jl_decode_args* a, cudaStream_t stream) {
+  // In host code `g_decode_scratch` is only a handle for the runtime, not a device pointer, so the
+  // device address is looked up once per device (with that device current) and cached.
+  static float* device_addr[64] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(JL_ERR_LAUNCH, "jl_decode_static: no current CUDA device");
+  if (device_addr[dev] == nullptr) {
+    float* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_decode_scratch);
+    if (e != cudaSuccess || ptr == nullptr)
+      return fail(JL_ERR_LAUNCH, "jl_decode_static: cannot resolve the built-in scratch array: %s", cudaGetErrorString(e));
+    device_addr[dev] = ptr;
+  }
+  if (a->batch <= 0 || a->heads <= 0 || a->kv_heads <= 0 || a->n_segments < 1 || a->n_segments > JL_MAX_SEGMENTS)
+    return fail(JL_ERR_BAD_ARG, "jl_decode_static: batch/heads/kv_heads/n_segments out of range");
+  int64_t total = 0;
+  for (int s = 0; s < a->n_segments; ++s) total += a->seg[s].len > 0 ? a->seg[s].len : 0;
+  int splits = a->num_splits > 0 ? a->num_splits : decode_auto_splits(a->batch, a->kv_heads, total);
+  const int64_t tiles = (total + kDecTile - 1) / kDecTile;
+  if (splits > tiles) splits = static_cast<int>(tiles > 0 ? tiles : 1);
+  const size_t need = decode_workspace_bytes(a->batch, a->heads, a->head_dim, splits);
+  if (need > kStaticScratchBytes)
+    return fail(JL_ERR_WORKSPACE,
+                "jl_decode_static: batch %d x heads %d x %d splits needs %zu bytes of scratch but the built-in array holds %zu; "
+                "lower num_splits or the batch, or use jl_decode with a caller-provided workspace",
+                a->batch, a->heads, splits, need, kStaticScratchBytes);
+  jl_decode_args with_scratch = *a;
+  with_scratch.num_splits = splits;
+  with_scratch.workspace = device_addr[dev];
+  with_scratch.workspace_bytes = kStaticScratchBytes;
+  return launch_decode(&with_scratch, stream);
+}
+
+size_t decode_static_scratch_bytes() { return kStaticScratchBytes; }
+
 }  // namespace jl

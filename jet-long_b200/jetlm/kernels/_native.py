@@ -89,6 +89,8 @@ EXPORTS = [
     ("jl_decode_workspace_bytes", C.c_size_t, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     ("jl_decode_auto_splits", C.c_int32, [C.c_int32, C.c_int32, C.c_int64]),
     ("jl_decode", C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
+    ("jl_decode_static", C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
+    ("jl_decode_static_scratch_bytes", C.c_size_t, []),
     ("jl_merge", C.c_int, [C.POINTER(MergeArgs), C.c_void_p]),
     ("jl_rotate", C.c_int, [C.POINTER(RotateArgs), C.c_void_p]),
 ]
