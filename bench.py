@@ -277,6 +277,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debug only; shown in config)")
     ap.add_argument("--logits-to-keep", type=int, default=0)
     ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--only-decode", action="store_true", help="run just the decode-attention microbench (profiling aid)")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
 
@@ -306,6 +307,13 @@ def main():
     from jetlm.modeling.jetlong_fused import Qwen3JetLongFusedForCausalLM
 
     peaks = load_peaks()
+    if args.only_decode:
+        res = decode_microbench(peaks, shard, iters=max(args.steps, 1))
+        if rank == 0:
+            print(json.dumps(dict(metric="decode_attn_us", unit="us", n_gpus=world, decode_attn=res)), flush=True)
+        if world > 1:
+            torch.distributed.destroy_process_group()
+        return
     cfg = model_config(args.model, args.w, args.w0, args.layers or None)
     G = max(1, math.ceil(args.seq / args.w))
     torch.manual_seed(0)
