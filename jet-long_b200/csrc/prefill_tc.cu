@@ -229,6 +229,10 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
 
+  // Register budget per role: the data-movement warpgroup gives registers back, the two softmax
+  // warpgroups (one thread per row, 128 scores live) take them.
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::);
   if (warp == 0) {
     // ===================================== TMA producer =====================================
     if (lane == 0) {
@@ -308,8 +312,10 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
       }
       mma_commit(&sm.all_done);
     }
-  } else if (warp >= 4) {
+  }
+  } else {
     // ================================ softmax + epilogue ================================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;" ::);
     const int t = (warp - 4) >> 2;                          // query tile 0 / 1
     const int quad = warp & 3;                              // TMEM lane quadrant this warp may access
     const int row_in_tile = quad * 32 + lane;
@@ -347,10 +353,13 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
         JL_TMEM_LD32(t_s + 96, s, 96);
         tmem_wait_ld();
 
-        float mx = -INFINITY;
+        // row maximum with 8 independent chains (a single chain would serialise 128 dependent ops)
+        float m8[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) m8[i] = -INFINITY;
         if (uniform) {
 #pragma unroll
-          for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
+          for (int i = 0; i < 128; ++i) m8[i & 7] = fmaxf(m8[i & 7], __uint_as_float(s[i]));
         } else {
           const int64_t lo64 = row_lo - tp0, hi64 = row_hi - tp0 + 1;
           const int c_lo = lo64 < 0 ? 0 : (lo64 > 128 ? 128 : static_cast<int>(lo64));
@@ -359,9 +368,10 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
           for (int i = 0; i < 128; ++i) {
             const float v = (i >= c_lo && i < c_hi) ? __uint_as_float(s[i]) : -INFINITY;
             s[i] = __float_as_uint(v);
-            mx = fmaxf(mx, v);
+            m8[i & 7] = fmaxf(m8[i & 7], v);
           }
         }
+        float mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
         mx *= p.scale_log2;                                  // scale > 0: max commutes with the scaling
         // lazy rescale: only when some row of the warp outgrew its reference maximum by 2^8
         const bool grow = mx > m_ref + 8.f;
@@ -384,7 +394,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
           m_ref = m_new;
         }
         const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-        float rs = 0.f;
+        float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           uint32_t pk[32];
@@ -392,11 +402,12 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
           for (int i = 0; i < 32; ++i) {
             const float p0 = fast_exp2(fmaf(__uint_as_float(s[half * 64 + 2 * i]), p.scale_log2, -m_use));
             const float p1 = fast_exp2(fmaf(__uint_as_float(s[half * 64 + 2 * i + 1]), p.scale_log2, -m_use));
-            rs += p0 + p1;
+            rs4[i & 3] += p0 + p1;
             pk[i] = pack_bf16x2(p0, p1);
           }
           JL_TMEM_ST32(t_s + half * 32, pk, 0);
         }
+        const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
         l_sum += rs;
         tmem_wait_st();
         tc_fence_before();
