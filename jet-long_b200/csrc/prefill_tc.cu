@@ -20,6 +20,10 @@
 
 #include "jl_common.cuh"
 
+#ifndef JL_EXP
+#define JL_EXP 0
+#endif
+
 namespace jl {
 
 namespace tc {
@@ -29,7 +33,6 @@ constexpr int kKStages = 3, kVStages = 2;
 constexpr int kTileBytes = 128 * 256;           // 128 rows x 128 bf16
 constexpr int kHalfBytes = 128 * 128;           // one 64-column half (a TMA box)
 constexpr int kThreads = 384;
-constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr int64_t kNegInfPos = -(int64_t(1) << 60);
 
 struct Params {
@@ -79,15 +82,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
                : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return ok != 0;
 }
-// Bounded wait: once any wait in the CTA has given up, all later waits return immediately so the
-// kernel drains instead of hanging; the host sees the status word.
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait.  A wait that has not been satisfied after kWaitLimitNs gives up and raises the CTA's
+// `failed` flag; from then on every wait of the CTA returns at once, so the kernel drains instead of
+// hanging (its output is then invalid and the status word tells the host).  CTAs that start after
+// the device status word has been raised skip their waits from the beginning.
+constexpr uint64_t kWaitLimitNs = 20ull * 1000 * 1000;
 __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, Smem& sm) {
   if (mbar_try_wait(bar, parity)) return;
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return;
-    if ((i & 1023u) == 1023u && *reinterpret_cast<volatile int*>(&sm.failed)) return;
+  volatile int* failed = reinterpret_cast<volatile int*>(&sm.failed);
+  if (*failed) return;
+  const uint64_t t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+      if (mbar_try_wait(bar, parity)) return;
+    if (*failed) return;
+    if (globaltimer_ns() - t0 > kWaitLimitNs) { *failed = 1; return; }
   }
-  *reinterpret_cast<volatile int*>(&sm.failed) = 1;
 }
 __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
   asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
@@ -211,7 +227,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
   const Schedule sched = make_schedule(p, q_row0);
 
   if (threadIdx.x == 0) {
-    sm.failed = 0;
+    sm.failed = (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
     mbar_init(&sm.q_full, 1);
     mbar_init(&sm.q_free, 1);
     for (int i = 0; i < kKStages; ++i) { mbar_init(&sm.k_full[i], 1); mbar_init(&sm.k_empty[i], 1); }
@@ -232,7 +248,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
   // Register budget per role: the data-movement warpgroup gives registers back, the two softmax
   // warpgroups (one thread per row, 128 scores live) take them.
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::);
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;" ::);
   if (warp == 0) {
     // ===================================== TMA producer =====================================
     if (lane == 0) {
@@ -260,49 +276,62 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
     }
   } else if (warp == 1) {
     // ====================================== MMA issuer ======================================
-    if (lane == 0 && sched.total > 0) {
+    // The whole warp walks the schedule so that barrier parities, ring indices and descriptors are
+    // warp-uniform values; one elected lane issues the tcgen05 instructions and their commits.
+    if (sched.total > 0) {
+      uint32_t leader;
+      asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(leader));
       const uint32_t idesc_qk = instr_desc(kTileM, kTileN, 0);
       const uint32_t idesc_pv = instr_desc(kTileM, kHeadDim, 1);
+      const uint64_t q_desc0 = smem_desc(smem_u32(sm.q[0]), 16, 1024);
+      const uint64_t k_desc0 = smem_desc(smem_u32(sm.k[0]), 16, 1024);
+      const uint64_t v_desc0 = smem_desc(smem_u32(sm.v[0]), kHalfBytes, 1024);
       auto issue_qk = [&](int t, int g) {
         const int ks = g % kKStages;
-        const uint32_t qa = smem_u32(sm.q[t]), ka = smem_u32(sm.k[ks]);
+        const uint64_t qd = q_desc0 + static_cast<uint64_t>((t * kTileBytes) >> 4);
+        const uint64_t kd = k_desc0 + static_cast<uint64_t>((ks * kTileBytes) >> 4);
+        if (leader) {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
-          mma_ss(tmem + t * 128, smem_desc(qa + off, 16, 1024), smem_desc(ka + off, 16, 1024), idesc_qk, kk > 0);
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint64_t off = static_cast<uint64_t>(((kk >> 2) * kHalfBytes + (kk & 3) * 32) >> 4);
+            mma_ss(tmem + t * 128, qd + off, kd + off, idesc_qk, kk > 0);
+          }
+          mma_commit(&sm.s_full[t]);
         }
-        mma_commit(&sm.s_full[t]);
       };
       int g = 0;           // global tile counter (K/V ring index, barrier parities)
       for (int ph = 0; ph < sched.n_phases; ++ph) {
         mbar_wait(&sm.q_full, ph & 1, sm);
-        tc_fence_after();
         const int n = sched.n_tiles[ph];
-        // S_t(first tile of the phase)
         mbar_wait(&sm.k_full[g % kKStages], (g / kKStages) & 1, sm);
         tc_fence_after();
         issue_qk(0, g);
         issue_qk(1, g);
-        if (n == 1) mma_commit(&sm.q_free);
-        mma_commit(&sm.k_empty[g % kKStages]);
+        if (leader) {
+          if (n == 1) mma_commit(&sm.q_free);
+          mma_commit(&sm.k_empty[g % kKStages]);
+        }
         for (int jj = 0; jj < n; ++jj, ++g) {
           const int vs = g % kVStages;
           const bool more = jj + 1 < n;
+          const uint64_t vd = v_desc0 + static_cast<uint64_t>((vs * kTileBytes) >> 4);
+#pragma unroll
           for (int t = 0; t < 2; ++t) {
             mbar_wait(&sm.p_full[t], g & 1, sm);
             if (t == 0) mbar_wait(&sm.v_full[vs], (g / kVStages) & 1, sm);
             tc_fence_after();
-            const uint32_t va = smem_u32(sm.v[vs]);
+            if (leader) {
 #pragma unroll
-            for (int kk = 0; kk < 8; ++kk)
-              mma_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8, smem_desc(va + kk * 2048, kHalfBytes, 1024), idesc_pv,
-                     (g > 0 || kk > 0) ? 1u : 0u);
-            if (t == 1) mma_commit(&sm.v_empty[vs]);
+              for (int kk = 0; kk < 8; ++kk)
+                mma_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8, vd + static_cast<uint64_t>((kk * 2048) >> 4), idesc_pv,
+                       (g > 0 || kk > 0) ? 1u : 0u);
+              if (t == 1) mma_commit(&sm.v_empty[vs]);
+            }
             if (more) {
               const int gn = g + 1;
               if (t == 0) { mbar_wait(&sm.k_full[gn % kKStages], (gn / kKStages) & 1, sm); tc_fence_after(); }
               issue_qk(t, gn);
-              if (t == 1) {
+              if (t == 1 && leader) {
                 if (jj + 2 == n) mma_commit(&sm.q_free);       // last QK^T of this phase issued
                 mma_commit(&sm.k_empty[gn % kKStages]);
               }
@@ -310,12 +339,13 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
           }
         }
       }
-      mma_commit(&sm.all_done);
+      if (leader) mma_commit(&sm.all_done);
+      __syncwarp();
     }
   }
   } else {
     // ================================ softmax + epilogue ================================
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;" ::);
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;" ::);
     const int t = (warp - 4) >> 2;                          // query tile 0 / 1
     const int quad = warp & 3;                              // TMEM lane quadrant this warp may access
     const int row_in_tile = quad * 32 + lane;
@@ -346,6 +376,11 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
 
         mbar_wait(&sm.s_full[t], g & 1, sm);
         tc_fence_after();
+#if JL_EXP == 4
+        tc_fence_before();
+        mbar_arrive(&sm.p_full[t]);
+        continue;
+#endif
         uint32_t s[128];
         JL_TMEM_LD32(t_s + 0, s, 0);
         JL_TMEM_LD32(t_s + 32, s, 32);
@@ -400,8 +435,15 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
           uint32_t pk[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
+#if JL_EXP == 1
+            const float p0 = fmaf(__uint_as_float(s[half * 64 + 2 * i]), p.scale_log2, -m_use) * 1e-3f;
+            const float p1 = fmaf(__uint_as_float(s[half * 64 + 2 * i + 1]), p.scale_log2, -m_use) * 1e-3f;
+#elif JL_EXP == 2
+            const float p0 = __uint_as_float(s[half * 64 + 2 * i]), p1 = __uint_as_float(s[half * 64 + 2 * i + 1]);
+#else
             const float p0 = fast_exp2(fmaf(__uint_as_float(s[half * 64 + 2 * i]), p.scale_log2, -m_use));
             const float p1 = fast_exp2(fmaf(__uint_as_float(s[half * 64 + 2 * i + 1]), p.scale_log2, -m_use));
+#endif
             rs4[i & 3] += p0 + p1;
             pk[i] = pack_bf16x2(p0, p1);
           }

@@ -62,8 +62,8 @@ def gather_partials(out: torch.Tensor, lse: torch.Tensor, shard: SequenceShard):
     (outs (world,B,S,H,D), lses (world,B,H,S)), identical on every rank."""
     outs = torch.empty((shard.world, *out.shape), dtype=out.dtype, device=out.device)
     lses = torch.empty((shard.world, *lse.shape), dtype=lse.dtype, device=lse.device)
-    dist.all_gather_into_tensor(outs, out.contiguous(), group=shard.group)
-    dist.all_gather_into_tensor(lses, lse.contiguous(), group=shard.group)
+    dist.all_gather_into_tensor(outs.view(-1), out.contiguous().view(-1), group=shard.group)
+    dist.all_gather_into_tensor(lses.view(-1), lse.contiguous().view(-1), group=shard.group)
     return outs, lses
 
 

@@ -1,0 +1,94 @@
+"""KV-sequence sharding on CPU ranks (gloo, world size 2 and 3): stripe geometry, the one all-gather
+and the N-way merge reproduce attention over the whole key sequence.  The local attention and the
+merge are the CPU oracle here; on GPUs the same driver runs the CUDA kernels."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import PKG, ROOT
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, block, results):
+    sys.path[:0] = [PKG, os.path.join(ROOT, "oracle")]
+    import jetlong_oracle as orc
+    from jetlm.kernels.sequence_parallel import SequenceShard, sharded_attention
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.manual_seed(7)                                   # same tensors on every rank
+        B, S, H, Hk, D, w0, ss = 1, 300, 4, 2, 128, 70, 37     # 37 keys were already cached: chunked prefill
+        Skv = S + ss
+        qb, qg = torch.randn(B, S, H, D), torch.randn(B, S, H, D)
+        kb, kg, v = (torch.randn(B, Skv, Hk, D) for _ in range(3))
+        shard = SequenceShard(rank, world, block=block)
+        rows = shard.owned_rows(Skv)
+        assert rows.numel() == shard.n_owned(Skv)
+        pos0, blk, stride = shard.geometry()
+        j = torch.arange(rows.numel())
+        assert torch.equal(rows, pos0 + (j // blk) * stride + j % blk)      # the kernels' key-position map
+
+        def local():                                           # attention of all queries over this rank's keys only
+            near, far = orc.bifocal_masks(S, Skv, ss, w0)
+            on, ln = orc.attention(qb, kb[:, rows], v[:, rows], near[:, :, rows])
+            of, lf = orc.attention(qg, kg[:, rows], v[:, rows], far[:, :, rows])
+            return orc.merge2(on, ln, of, lf)
+
+        merge = lambda outs, lses: orc.merge_partials(torch.stack(outs), torch.stack(lses))
+        out, lse = sharded_attention(local, merge, shard)
+        eo, el = orc.jetlong_prefill(qb, qg, kb, kg, v, seqstart=ss, w0=w0)
+        d, cos = orc.compare(out, eo)
+        dl, _ = orc.compare(lse, el)
+        # decode: contiguous ranges
+        lo, hi = shard.contiguous_range(Skv)
+        boundary = Skv - 1 - w0
+        q1, q1g = qb[:, -1:], qg[:, -1:]
+
+        def local_dec():
+            kn, vn = kb[:, max(lo, boundary):hi], v[:, max(lo, boundary):hi]
+            kf, vf = kg[:, lo:min(hi, boundary)], v[:, lo:min(hi, boundary)]
+            on, ln = orc.attention(q1, kn, vn) if kn.shape[1] else (torch.zeros(B, 1, H, D), torch.full((B, H, 1), -float("inf")))
+            of, lf = orc.attention(q1g, kf, vf) if kf.shape[1] else (torch.zeros(B, 1, H, D), torch.full((B, H, 1), -float("inf")))
+            return orc.merge2(on, ln, of, lf)
+
+        od, ld = sharded_attention(local_dec, merge, shard)
+        eod, eld = orc.jetlong_decode(q1, q1g, kb[:, boundary:], v[:, boundary:], kg[:, :boundary], v[:, :boundary])
+        dd, _ = orc.compare(od, eod)
+        dld, _ = orc.compare(ld, eld)
+        results[rank] = (d, cos, dl, dd, dld)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,block", [(2, 128), (3, 64)])
+def test_sharded_attention_equals_full_attention(world, block):
+    port = _free_port()
+    with mp.Manager() as mgr:
+        results = mgr.dict()
+        mp.spawn(_worker, args=(world, port, block, results), nprocs=world, join=True)
+        assert len(results) == world
+        for rank, (d, cos, dl, dd, dld) in results.items():
+            assert d < 1e-5 and cos > 0.99999 and dl < 1e-5 and dd < 1e-5 and dld < 1e-5, (rank, d, cos, dl, dd, dld)
+
+
+def test_stripe_geometry_partitions_the_keys():
+    sys.path[:0] = [PKG]
+    from jetlm.kernels.sequence_parallel import SequenceShard
+    for n_keys in (1, 127, 128, 1000, 4097):
+        for world in (1, 2, 4, 8):
+            rows = [SequenceShard(r, world, block=128).owned_rows(n_keys) for r in range(world)]
+            allrows = torch.cat(rows).sort().values
+            assert torch.equal(allrows, torch.arange(n_keys))
+            ranges = [SequenceShard(r, world).contiguous_range(n_keys) for r in range(world)]
+            assert ranges[0][0] == 0 and ranges[-1][1] == n_keys
+            assert all(ranges[i][1] == ranges[i + 1][0] for i in range(world - 1))
