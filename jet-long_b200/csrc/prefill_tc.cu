@@ -17,6 +17,7 @@
 // Rescaling of O is lazy: it happens only when a row maximum grows by more than 2^8.
 // Every wait is bounded; a wait that gives up sets a status word and lets the kernel drain.
 #include <cuda.h>
+#include <cstdio>
 
 #include "jl_common.cuh"
 
@@ -33,6 +34,10 @@ constexpr int kKStages = 3, kVStages = 2;
 constexpr int kTileBytes = 128 * 256;           // 128 rows x 128 bf16
 constexpr int kHalfBytes = 128 * 128;           // one 64-column half (a TMA box)
 constexpr int kThreads = 384;
+#ifndef JL_POLY
+#define JL_POLY 3
+#endif
+constexpr int kPolyOf8 = JL_POLY;               // of every 8 score pairs, how many take the FMA-pipe exp2
 constexpr int64_t kNegInfPos = -(int64_t(1) << 60);
 
 struct Params {
@@ -149,6 +154,65 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
   asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17," \
                "%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"                                              \
                ::"r"(taddr), JL_W32(r, o) : "memory")
+// ---- packed fp32 pairs (one instruction per two lanes of work) and the FMA-pipe exp2 ----
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2_round_down(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rm.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// 2^x for a pair, on the FMA and integer pipes only (the SFU is the co-bottleneck of attention at
+// head_dim 128).  x = n + f with n = floor(x) taken from a round-down add of 1.5 * 2^23 (n then
+// sits in the low mantissa bits), f in [0, 1); 2^f by a cubic with equi-ripple relative error
+// 7.5e-5 (fitted for this file; the result feeds a bf16 rounding of relative step 3.9e-3);
+// 2^n is applied by adding n to the exponent field.  x is clamped at -126 so the exponent cannot wrap.
+__device__ __forceinline__ uint64_t exp2_pair_fma(uint64_t x) {
+  float x0, x1;
+  unpack2(x, x0, x1);
+  x = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+  const uint64_t magic = pack2(12582912.f, 12582912.f);
+  const uint64_t t = add2_round_down(x, magic);
+  const uint64_t f = sub2(x, sub2(t, magic));
+  uint64_t q = fma2(pack2(0.07802429050207138f, 0.07802429050207138f), f, pack2(0.22606779634952545f, 0.22606779634952545f));
+  q = fma2(q, f, pack2(0.695833146572113f, 0.695833146572113f));
+  q = fma2(q, f, pack2(0.9999252557754517f, 0.9999252557754517f));
+  float t0, t1, q0, q1;
+  unpack2(t, t0, t1);
+  unpack2(q, q0, q1);
+  return pack2(__uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23)),
+               __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23)));
+}
+__device__ __forceinline__ uint64_t exp2_pair_sfu(uint64_t x) {
+  float x0, x1;
+  unpack2(x, x0, x1);
+  return pack2(fast_exp2(x0), fast_exp2(x1));
+}
+
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -362,6 +426,9 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
 
     float m_ref = -INFINITY, l_sum = 0.f;
     int g = 0;
+#if JL_EXP == 5
+    long long dbg_wait = 0, dbg_work = 0;
+#endif
     for (int ph = 0; ph < sched.n_phases; ++ph) {
       const int c = sched.cls[ph];
       int64_t row_lo, row_hi, tile_lo_max, tile_hi_min, dummy;
@@ -374,8 +441,15 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
         const int valid = min(kTileN, p.sk - j * kTileN);
         const bool uniform = valid == kTileN && tile_lo_max <= tp0 && tile_hi_min >= tp0 + kTileN - 1;
 
+#if JL_EXP == 5
+        const long long tw0 = clock64();
+#endif
         mbar_wait(&sm.s_full[t], g & 1, sm);
         tc_fence_after();
+#if JL_EXP == 5
+        const long long tw1 = clock64();
+        dbg_wait += tw1 - tw0;
+#endif
 #if JL_EXP == 4
         tc_fence_before();
         mbar_arrive(&sm.p_full[t]);
@@ -388,25 +462,22 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
         JL_TMEM_LD32(t_s + 96, s, 96);
         tmem_wait_ld();
 
-        // row maximum with 8 independent chains (a single chain would serialise 128 dependent ops)
-        float m8[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) m8[i] = -INFINITY;
-        if (uniform) {
-#pragma unroll
-          for (int i = 0; i < 128; ++i) m8[i & 7] = fmaxf(m8[i & 7], __uint_as_float(s[i]));
-        } else {
+        // row maximum: 4 independent chains of 3-input max
+        float mx;
+        if (!uniform) {
           const int64_t lo64 = row_lo - tp0, hi64 = row_hi - tp0 + 1;
           const int c_lo = lo64 < 0 ? 0 : (lo64 > 128 ? 128 : static_cast<int>(lo64));
           const int c_hi = hi64 < 0 ? 0 : (hi64 > valid ? valid : static_cast<int>(hi64));
 #pragma unroll
-          for (int i = 0; i < 128; ++i) {
-            const float v = (i >= c_lo && i < c_hi) ? __uint_as_float(s[i]) : -INFINITY;
-            s[i] = __float_as_uint(v);
-            m8[i & 7] = fmaxf(m8[i & 7], v);
-          }
+          for (int i = 0; i < 128; ++i)
+            if (!(i >= c_lo && i < c_hi)) s[i] = 0xff800000u;        // -inf
         }
-        float mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
+        {
+          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+          for (int i = 0; i < 64; ++i) m4[i & 3] = max3(m4[i & 3], __uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1]));
+          mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+        }
         mx *= p.scale_log2;                                  // scale > 0: max commutes with the scaling
         // lazy rescale: only when some row of the warp outgrew its reference maximum by 2^8
         const bool grow = mx > m_ref + 8.f;
@@ -429,40 +500,55 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
           m_ref = m_new;
         }
         const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-        float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+        // p = 2^(s * scale - m): packed FMA, then kPolyOf8 of every 8 pairs on the FMA pipe, the rest on the SFU
+        const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negm2 = pack2(-m_use, -m_use);
+        uint64_t acc2[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           uint32_t pk[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
+            const int e = half * 64 + 2 * i;
+            const uint64_t x = fma2(pack2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), scale2, negm2);
 #if JL_EXP == 1
-            const float p0 = fmaf(__uint_as_float(s[half * 64 + 2 * i]), p.scale_log2, -m_use) * 1e-3f;
-            const float p1 = fmaf(__uint_as_float(s[half * 64 + 2 * i + 1]), p.scale_log2, -m_use) * 1e-3f;
-#elif JL_EXP == 2
-            const float p0 = __uint_as_float(s[half * 64 + 2 * i]), p1 = __uint_as_float(s[half * 64 + 2 * i + 1]);
+            const uint64_t pp = x;
 #else
-            const float p0 = fast_exp2(fmaf(__uint_as_float(s[half * 64 + 2 * i]), p.scale_log2, -m_use));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(s[half * 64 + 2 * i + 1]), p.scale_log2, -m_use));
+            const uint64_t pp = (i & 7) < kPolyOf8 ? exp2_pair_fma(x) : exp2_pair_sfu(x);
 #endif
-            rs4[i & 3] += p0 + p1;
+            acc2[i & 3] = add2(acc2[i & 3], pp);
+            float p0, p1;
+            unpack2(pp, p0, p1);
             pk[i] = pack_bf16x2(p0, p1);
           }
           JL_TMEM_ST32(t_s + half * 32, pk, 0);
         }
-        const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+        float rs;
+        {
+          float a0, a1;
+          unpack2(add2(add2(acc2[0], acc2[1]), add2(acc2[2], acc2[3])), a0, a1);
+          rs = a0 + a1;
+        }
         l_sum += rs;
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&sm.p_full[t]);
+#if JL_EXP == 5
+        dbg_work += clock64() - tw1;
+#endif
       }
     }
+#if JL_EXP == 5
+    if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 4 || warp == 8))
+      printf("tile %d: iters %d  wait/iter %lld  work/iter %lld\n", t, g, dbg_wait / max(g, 1), dbg_work / max(g, 1));
+#endif
 
     // ---- epilogue: O / l -> bf16, LSE ----
     if (sched.total > 0) {
       mbar_wait(&sm.all_done, 0, sm);
       tc_fence_after();
     }
-    const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+    const bool seen = m_ref != -INFINITY;                 // masked scores add ~1e-38 each to l_sum, never to m_ref
+    const float inv = seen ? 1.f / l_sum : 0.f;
     __nv_bfloat16* orow = p.out + b * p.os_b + static_cast<int64_t>(q_row) * p.os_s + head * p.os_h;
 #pragma unroll
     for (int cchunk = 0; cchunk < 4; ++cchunk) {
@@ -487,7 +573,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
       }
     }
     if (row_valid && p.lse != nullptr)
-      p.lse[(static_cast<int64_t>(b) * p.heads + head) * p.sq + q_row] = l_sum > 0.f ? (m_ref + log2f(l_sum)) * kLn2 : -INFINITY;
+      p.lse[(static_cast<int64_t>(b) * p.heads + head) * p.sq + q_row] = seen ? (m_ref + log2f(l_sum)) * kLn2 : -INFINITY;
   }
 
   tc_fence_before();
