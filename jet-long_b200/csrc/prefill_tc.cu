@@ -34,10 +34,12 @@ constexpr int kKStages = 3, kVStages = 2;
 constexpr int kTileBytes = 128 * 256;           // 128 rows x 128 bf16
 constexpr int kHalfBytes = 128 * 128;           // one 64-column half (a TMA box)
 constexpr int kThreads = 384;
-#ifndef JL_POLY
-#define JL_POLY 3
+#ifndef JL_POLY_MASK
+#define JL_POLY_MASK 0x11
 #endif
-constexpr int kPolyOf8 = JL_POLY;               // of every 8 score pairs, how many take the FMA-pipe exp2
+// Which of every 8 consecutive score pairs take the FMA-pipe exp2 (bit i = pair i); the rest use the SFU.
+// The set is spread evenly so that SFU instructions are separated by FMA-pipe work in program order.
+constexpr unsigned kPolyMask = JL_POLY_MASK;
 constexpr int64_t kNegInfPos = -(int64_t(1) << 60);
 
 struct Params {
@@ -64,7 +66,7 @@ struct Smem {
   alignas(1024) uint8_t k[kKStages][kTileBytes];
   alignas(1024) uint8_t v[kVStages][kTileBytes];
   uint64_t q_full, q_free, k_full[kKStages], k_empty[kKStages], v_full[kVStages], v_empty[kVStages];
-  uint64_t s_full[2], p_full[2], all_done;
+  uint64_t s_full[2], p_half[2][2], all_done;     // p_half[t][h]: probabilities of keys 64h..64h+63 of tile t are in TMEM
   uint32_t tmem_base;
   int failed;
 };
@@ -204,8 +206,8 @@ __device__ __forceinline__ uint64_t exp2_pair_fma(uint64_t x) {
   float t0, t1, q0, q1;
   unpack2(t, t0, t1);
   unpack2(q, q0, q1);
-  return pack2(__uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23)),
-               __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23)));
+  return pack2(__uint_as_float(__float_as_uint(t0) * 8388608u + __float_as_uint(q0)),      // (n << 23) + bits: one IMAD
+               __uint_as_float(__float_as_uint(t1) * 8388608u + __float_as_uint(q1)));
 }
 __device__ __forceinline__ uint64_t exp2_pair_sfu(uint64_t x) {
   float x0, x1;
@@ -296,7 +298,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
     mbar_init(&sm.q_free, 1);
     for (int i = 0; i < kKStages; ++i) { mbar_init(&sm.k_full[i], 1); mbar_init(&sm.k_empty[i], 1); }
     for (int i = 0; i < kVStages; ++i) { mbar_init(&sm.v_full[i], 1); mbar_init(&sm.v_empty[i], 1); }
-    for (int t = 0; t < 2; ++t) { mbar_init(&sm.s_full[t], 1); mbar_init(&sm.p_full[t], 128); }
+    for (int t = 0; t < 2; ++t) { mbar_init(&sm.s_full[t], 1); mbar_init(&sm.p_half[t][0], 128); mbar_init(&sm.p_half[t][1], 128); }
     mbar_init(&sm.all_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -381,15 +383,20 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
           const uint64_t vd = v_desc0 + static_cast<uint64_t>((vs * kTileBytes) >> 4);
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
-            mbar_wait(&sm.p_full[t], g & 1, sm);
-            if (t == 0) mbar_wait(&sm.v_full[vs], (g / kVStages) & 1, sm);
-            tc_fence_after();
-            if (leader) {
+            // the softmax warps publish P in two halves so that the first four k-steps of P V overlap
+            // the exponentials of the second half
 #pragma unroll
-              for (int kk = 0; kk < 8; ++kk)
-                mma_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8, vd + static_cast<uint64_t>((kk * 2048) >> 4), idesc_pv,
-                       (g > 0 || kk > 0) ? 1u : 0u);
-              if (t == 1) mma_commit(&sm.v_empty[vs]);
+            for (int h = 0; h < 2; ++h) {
+              mbar_wait(&sm.p_half[t][h], g & 1, sm);
+              if (t == 0 && h == 0) mbar_wait(&sm.v_full[vs], (g / kVStages) & 1, sm);
+              tc_fence_after();
+              if (leader) {
+#pragma unroll
+                for (int kk = 4 * h; kk < 4 * h + 4; ++kk)
+                  mma_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8, vd + static_cast<uint64_t>((kk * 2048) >> 4), idesc_pv,
+                         (g > 0 || kk > 0) ? 1u : 0u);
+                if (t == 1 && h == 1) mma_commit(&sm.v_empty[vs]);
+              }
             }
             if (more) {
               const int gn = g + 1;
@@ -427,7 +434,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
     float m_ref = -INFINITY, l_sum = 0.f;
     int g = 0;
 #if JL_EXP == 5
-    long long dbg_wait = 0, dbg_work = 0;
+    long long dbg_wait = 0, dbg_work = 0, dbg_a = 0, dbg_b = 0, dbg_c = 0, dbg_d = 0;
 #endif
     for (int ph = 0; ph < sched.n_phases; ++ph) {
       const int c = sched.cls[ph];
@@ -452,7 +459,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
 #endif
 #if JL_EXP == 4
         tc_fence_before();
-        mbar_arrive(&sm.p_full[t]);
+        mbar_arrive(&sm.p_half[t][0]);
+        mbar_arrive(&sm.p_half[t][1]);
         continue;
 #endif
         uint32_t s[128];
@@ -461,6 +469,9 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
         JL_TMEM_LD32(t_s + 64, s, 64);
         JL_TMEM_LD32(t_s + 96, s, 96);
         tmem_wait_ld();
+#if JL_EXP == 5
+        const long long tw2 = clock64();
+#endif
 
         // row maximum: 4 independent chains of 3-input max
         float mx;
@@ -499,10 +510,16 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
           }
           m_ref = m_new;
         }
+#if JL_EXP == 5
+        const long long tw3 = clock64();
+#endif
         const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-        // p = 2^(s * scale - m): packed FMA, then kPolyOf8 of every 8 pairs on the FMA pipe, the rest on the SFU
+        // p = 2^(s * scale - m): packed FMA, then the exponentials split between the FMA pipe and the SFU (kPolyMask)
         const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negm2 = pack2(-m_use, -m_use);
         uint64_t acc2[4] = {0ull, 0ull, 0ull, 0ull};
+#if JL_EXP == 5
+        long long tw4 = 0;
+#endif
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           uint32_t pk[32];
@@ -513,7 +530,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
 #if JL_EXP == 1
             const uint64_t pp = x;
 #else
-            const uint64_t pp = (i & 7) < kPolyOf8 ? exp2_pair_fma(x) : exp2_pair_sfu(x);
+            const uint64_t pp = ((kPolyMask >> (i & 7)) & 1u) ? exp2_pair_fma(x) : exp2_pair_sfu(x);
 #endif
             acc2[i & 3] = add2(acc2[i & 3], pp);
             float p0, p1;
@@ -521,25 +538,27 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
             pk[i] = pack_bf16x2(p0, p1);
           }
           JL_TMEM_ST32(t_s + half * 32, pk, 0);
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(&sm.p_half[t][half]);
+#if JL_EXP == 5
+          if (half == 0) tw4 = clock64();
+#endif
         }
-        float rs;
         {
           float a0, a1;
           unpack2(add2(add2(acc2[0], acc2[1]), add2(acc2[2], acc2[3])), a0, a1);
-          rs = a0 + a1;
+          l_sum += a0 + a1;
         }
-        l_sum += rs;
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(&sm.p_full[t]);
 #if JL_EXP == 5
-        dbg_work += clock64() - tw1;
+        { const long long tw5 = clock64(); dbg_work += tw5 - tw1; dbg_a += tw2 - tw1; dbg_b += tw3 - tw2; dbg_c += tw4 - tw3; dbg_d += tw5 - tw4; }
 #endif
       }
     }
 #if JL_EXP == 5
     if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 4 || warp == 8))
-      printf("tile %d: iters %d  wait/iter %lld  work/iter %lld\n", t, g, dbg_wait / max(g, 1), dbg_work / max(g, 1));
+      printf("tile %d: iters %d  wait %lld  work %lld = ld %lld + max/rescale %lld + exp half0 %lld + exp half1 %lld\n", t, g,
+             dbg_wait / max(g, 1), dbg_work / max(g, 1), dbg_a / max(g, 1), dbg_b / max(g, 1), dbg_c / max(g, 1), dbg_d / max(g, 1));
 #endif
 
     // ---- epilogue: O / l -> bf16, LSE ----
