@@ -46,7 +46,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         o = os.path.join(OBJ_DIR, src.replace(".cu", ".o"))
         objs.append(o)
         if force or _stale(o, [s] + headers):
-            cmd = [nvcc, *NVCC_FLAGS, *os.environ.get("JL_NVCC_EXTRA", "").split(), "-c", s, "-o", o] + (["-Xptxas", "-v"] if verbose else [])
+            cmd = [nvcc, *NVCC_FLAGS, "-c", s, "-o", o] + (["-Xptxas", "-v"] if verbose else [])
             jobs.append(cmd)
 
     def run(cmd):

@@ -46,11 +46,14 @@ struct DecSmem {
   float inv_freq[64];
 };
 
-// sin/cos of an fp32 angle of any magnitude reached by RoPE positions: exact reduction by 2*pi in
-// fp64 (one DFMA), then the SFU approximations on [-pi, pi].
+// sin/cos of an fp32 angle of any magnitude reached by RoPE positions (|theta| up to ~1e6 rad):
+// two-constant Cody-Waite reduction by 2*pi.  The first FMA subtracts k * fl32(2*pi) with the product
+// kept exact inside the FMA, so the cancellation costs nothing; the second adds back k times the
+// representation error of fl32(2*pi).  The SFU approximations are then used on [-pi, pi] only.
 __device__ __forceinline__ void sincos_reduced(float theta, float* s, float* c) {
   const float k = rintf(theta * 0.15915494309189535f);
-  const float r = static_cast<float>(fma(-static_cast<double>(k), 6.283185307179586, static_cast<double>(theta)));
+  float r = fmaf(-k, 6.2831854820251465f, theta);
+  r = fmaf(k, 1.7484555314695172e-7f, r);
   *s = __sinf(r);
   *c = __cosf(r);
 }

@@ -21,6 +21,68 @@ struct MergeParams {
 
 __device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16(x)); }
 
+// One row, NPARTS > 0: the part count is a compile-time constant so that every part's 16-byte load and
+// LSE load is issued before the first is consumed (NPARTS * 16 B in flight per thread); NPARTS == 0:
+// run-time count, loads issued part by part.
+template <int NPARTS>
+__device__ __forceinline__ void merge_row(const MergeParams& p, int64_t row, int lane16, int64_t lidx) {
+  constexpr int kMax = NPARTS > 0 ? NPARTS : 1;
+  const int n = NPARTS > 0 ? NPARTS : p.n_parts;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  float m = -INFINITY, wsum = 0.f;
+  if (NPARTS > 0) {
+    uint4 x[kMax];
+    float l[kMax];
+#pragma unroll
+    for (int i = 0; i < kMax; ++i) {
+      x[i] = p.o[i][row * 16 + lane16];
+      l[i] = p.lse[i][lidx];
+    }
+#pragma unroll
+    for (int i = 0; i < kMax; ++i) m = fmaxf(m, l[i]);
+    const float m_safe = (m == -INFINITY) ? 0.f : m;
+#pragma unroll
+    for (int i = 0; i < kMax; ++i) {
+      const float w = exp2f((l[i] - m_safe) * kLog2e);
+      wsum += w;
+      const uint32_t* u = reinterpret_cast<const uint32_t*>(&x[i]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16x2(u[j]);
+        acc[2 * j] = fmaf(w, f.x, acc[2 * j]);
+        acc[2 * j + 1] = fmaf(w, f.y, acc[2 * j + 1]);
+      }
+    }
+    m = m_safe;
+  } else {
+    for (int i = 0; i < n; ++i) m = fmaxf(m, p.lse[i][lidx]);
+    const float m_safe = (m == -INFINITY) ? 0.f : m;
+    for (int i = 0; i < n; ++i) {
+      const float w = exp2f((p.lse[i][lidx] - m_safe) * kLog2e);
+      wsum += w;
+      const uint4 x = p.o[i][row * 16 + lane16];
+      const uint32_t* u = reinterpret_cast<const uint32_t*>(&x);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16x2(u[j]);
+        acc[2 * j] = fmaf(w, f.x, acc[2 * j]);
+        acc[2 * j + 1] = fmaf(w, f.y, acc[2 * j + 1]);
+      }
+    }
+    m = m_safe;
+  }
+  const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+  uint4 r;
+  uint32_t* ur = reinterpret_cast<uint32_t*>(&r);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) ur[j] = pack_bf16x2(acc[2 * j] * inv, acc[2 * j + 1] * inv);
+  p.out[row * 16 + lane16] = r;
+  if (p.lse_out != nullptr && lane16 == 0) p.lse_out[lidx] = wsum > 0.f ? m + logf(wsum) : -INFINITY;
+}
+
+template <int NPARTS>
 __global__ void __launch_bounds__(256) merge_kernel(const MergeParams p) {
   const int lane16 = threadIdx.x & 15;
   const int64_t row_stride = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 4);
@@ -56,32 +118,7 @@ __global__ void __launch_bounds__(256) merge_kernel(const MergeParams p) {
       continue;
     }
 
-    float m = -INFINITY;
-    for (int i = 0; i < p.n_parts; ++i) m = fmaxf(m, p.lse[i][lidx]);
-    const float m_safe = (m == -INFINITY) ? 0.f : m;
-    float acc[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    float wsum = 0.f;
-    for (int i = 0; i < p.n_parts; ++i) {
-      const float w = exp2f((p.lse[i][lidx] - m_safe) * kLog2e);
-      wsum += w;
-      const uint4 x = p.o[i][row * 16 + lane16];
-      const uint32_t* u = reinterpret_cast<const uint32_t*>(&x);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = unpack_bf16x2(u[j]);
-        acc[2 * j] = fmaf(w, f.x, acc[2 * j]);
-        acc[2 * j + 1] = fmaf(w, f.y, acc[2 * j + 1]);
-      }
-    }
-    const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
-    uint4 r;
-    uint32_t* ur = reinterpret_cast<uint32_t*>(&r);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) ur[j] = pack_bf16x2(acc[2 * j] * inv, acc[2 * j + 1] * inv);
-    p.out[row * 16 + lane16] = r;
-    if (p.lse_out != nullptr && lane16 == 0) p.lse_out[lidx] = wsum > 0.f ? m_safe + logf(wsum) : -INFINITY;
+    merge_row<NPARTS>(p, row, lane16, lidx);
   }
 }
 
@@ -108,8 +145,13 @@ int launch_merge(const jl_merge_args* a, cudaStream_t stream) {
   p.round_like_reference = a->round_like_reference;
   if (p.rows == 0) return JL_OK;
   const int64_t blocks_needed = (p.rows + 15) / 16;
-  const int grid = static_cast<int>(blocks_needed < 148 * 16 ? blocks_needed : 148 * 16);
-  merge_kernel<<<grid, 256, 0, stream>>>(p);
+  const int grid = static_cast<int>(blocks_needed < 148 * 32 ? blocks_needed : 148 * 32);
+  switch (a->round_like_reference ? 0 : a->n_parts) {
+    case 2: merge_kernel<2><<<grid, 256, 0, stream>>>(p); break;
+    case 4: merge_kernel<4><<<grid, 256, 0, stream>>>(p); break;
+    case 8: merge_kernel<8><<<grid, 256, 0, stream>>>(p); break;
+    default: merge_kernel<0><<<grid, 256, 0, stream>>>(p); break;
+  }
   return check_launch("jl_merge");
 }
 

@@ -17,13 +17,9 @@
 // Rescaling of O is lazy: it happens only when a row maximum grows by more than 2^8.
 // Every wait is bounded; a wait that gives up sets a status word and lets the kernel drain.
 #include <cuda.h>
-#include <cstdio>
 
 #include "jl_common.cuh"
 
-#ifndef JL_EXP
-#define JL_EXP 0
-#endif
 
 namespace jl {
 
@@ -433,9 +429,6 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
 
     float m_ref = -INFINITY, l_sum = 0.f;
     int g = 0;
-#if JL_EXP == 5
-    long long dbg_wait = 0, dbg_work = 0, dbg_a = 0, dbg_b = 0, dbg_c = 0, dbg_d = 0;
-#endif
     for (int ph = 0; ph < sched.n_phases; ++ph) {
       const int c = sched.cls[ph];
       int64_t row_lo, row_hi, tile_lo_max, tile_hi_min, dummy;
@@ -448,30 +441,14 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
         const int valid = min(kTileN, p.sk - j * kTileN);
         const bool uniform = valid == kTileN && tile_lo_max <= tp0 && tile_hi_min >= tp0 + kTileN - 1;
 
-#if JL_EXP == 5
-        const long long tw0 = clock64();
-#endif
         mbar_wait(&sm.s_full[t], g & 1, sm);
         tc_fence_after();
-#if JL_EXP == 5
-        const long long tw1 = clock64();
-        dbg_wait += tw1 - tw0;
-#endif
-#if JL_EXP == 4
-        tc_fence_before();
-        mbar_arrive(&sm.p_half[t][0]);
-        mbar_arrive(&sm.p_half[t][1]);
-        continue;
-#endif
         uint32_t s[128];
         JL_TMEM_LD32(t_s + 0, s, 0);
         JL_TMEM_LD32(t_s + 32, s, 32);
         JL_TMEM_LD32(t_s + 64, s, 64);
         JL_TMEM_LD32(t_s + 96, s, 96);
         tmem_wait_ld();
-#if JL_EXP == 5
-        const long long tw2 = clock64();
-#endif
 
         // row maximum: 4 independent chains of 3-input max
         float mx;
@@ -510,16 +487,10 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
           }
           m_ref = m_new;
         }
-#if JL_EXP == 5
-        const long long tw3 = clock64();
-#endif
         const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
         // p = 2^(s * scale - m): packed FMA, then the exponentials split between the FMA pipe and the SFU (kPolyMask)
         const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negm2 = pack2(-m_use, -m_use);
         uint64_t acc2[4] = {0ull, 0ull, 0ull, 0ull};
-#if JL_EXP == 5
-        long long tw4 = 0;
-#endif
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           uint32_t pk[32];
@@ -527,11 +498,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
           for (int i = 0; i < 32; ++i) {
             const int e = half * 64 + 2 * i;
             const uint64_t x = fma2(pack2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), scale2, negm2);
-#if JL_EXP == 1
-            const uint64_t pp = x;
-#else
             const uint64_t pp = ((kPolyMask >> (i & 7)) & 1u) ? exp2_pair_fma(x) : exp2_pair_sfu(x);
-#endif
             acc2[i & 3] = add2(acc2[i & 3], pp);
             float p0, p1;
             unpack2(pp, p0, p1);
@@ -541,25 +508,14 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
           tmem_wait_st();
           tc_fence_before();
           mbar_arrive(&sm.p_half[t][half]);
-#if JL_EXP == 5
-          if (half == 0) tw4 = clock64();
-#endif
         }
         {
           float a0, a1;
           unpack2(add2(add2(acc2[0], acc2[1]), add2(acc2[2], acc2[3])), a0, a1);
           l_sum += a0 + a1;
         }
-#if JL_EXP == 5
-        { const long long tw5 = clock64(); dbg_work += tw5 - tw1; dbg_a += tw2 - tw1; dbg_b += tw3 - tw2; dbg_c += tw4 - tw3; dbg_d += tw5 - tw4; }
-#endif
       }
     }
-#if JL_EXP == 5
-    if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp == 4 || warp == 8))
-      printf("tile %d: iters %d  wait %lld  work %lld = ld %lld + max/rescale %lld + exp half0 %lld + exp half1 %lld\n", t, g,
-             dbg_wait / max(g, 1), dbg_work / max(g, 1), dbg_a / max(g, 1), dbg_b / max(g, 1), dbg_c / max(g, 1), dbg_d / max(g, 1));
-#endif
 
     // ---- epilogue: O / l -> bf16, LSE ----
     if (sched.total > 0) {
