@@ -237,10 +237,17 @@ def decode_microbench(peaks, shard, iters=20):
                 fn()
             torch.cuda.synchronize()
             graph = None
-            if shard is None:
+            try:                                   # kernels + (for N > 1) the NCCL all-gather in one graph
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph):
                     fn()
+                graph.replay()
+                torch.cuda.synchronize()
+            except Exception:
+                if shard is None:
+                    raise
+                graph = None
+                torch.cuda.synchronize()
             ts = []
             for _ in range(iters):
                 cold_l2()
@@ -263,7 +270,7 @@ def decode_microbench(peaks, shard, iters=20):
         out[f"batch{B}"] = res
         del kc, vc, kv, vv
     out["config"] = dict(heads=H, kv_heads=Hk, head_dim=D, ctx=ctx, w_0=w0, group_size=G,
-                         timing="CUDA graph replay" if shard is None else "eager launches + NCCL all-gather, max over ranks",
+                         timing="CUDA graph replay" if shard is None else "CUDA graph replay incl. NCCL all-gather (eager if capture fails), max over ranks",
                          l2="256 MB write + 256 MB read before every iteration (cold, clean L2)")
     return out
 

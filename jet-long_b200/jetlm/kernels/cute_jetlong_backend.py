@@ -11,9 +11,19 @@ from __future__ import annotations
 import torch
 
 from . import jetlong_ops as ops
-from .sequence_parallel import SequenceShard, sharded_attention
+from .sequence_parallel import PartialBuffer, SequenceShard, sharded_attention
 
 _SHARD: SequenceShard | None = None
+_BUFFERS: dict[tuple, PartialBuffer] = {}
+
+
+def _partial_buffer(shard, out_shape, lse_shape, dtype, device) -> PartialBuffer:
+    """Gather buffers are cached per shape: the same (O, LSE) exchange repeats every layer and step."""
+    key = (shard.rank, shard.world, tuple(out_shape), tuple(lse_shape), dtype, device)
+    buf = _BUFFERS.get(key)
+    if buf is None:
+        buf = _BUFFERS[key] = PartialBuffer(shard, out_shape, lse_shape, dtype, device)
+    return buf
 
 
 def configure_sequence_sharding(shard: SequenceShard | None) -> None:
@@ -36,11 +46,13 @@ def fused_jetlong_prefill(query_base, query_group, key_base, key_group, value, *
         sh = _SHARD
         pos0, blk, stride = sh.geometry()
         kb, kg, vv = (sh.take_stripe(x, dim=2) for x in (key_base, key_group, value))     # this rank's cache stripe
-        local = lambda: ops.posmap_prefill([t(query_base), t(query_group)], [t(kb), t(kg)], t(vv),
-                                           pmap=ops.PositionMap.jetlong(int(window_size_left)),
-                                           q_pos0=int(seqstart_q), k_pos0=pos0, k_block=blk, k_block_stride=stride,
-                                           softmax_scale=softmax_scale)
-        out, _ = sharded_attention(local, ops.merge_partials, sh)
+        B, H, S, D = query_base.shape
+        local = lambda out, lse: ops.posmap_prefill([t(query_base), t(query_group)], [t(kb), t(kg)], t(vv),
+                                                    pmap=ops.PositionMap.jetlong(int(window_size_left)),
+                                                    q_pos0=int(seqstart_q), k_pos0=pos0, k_block=blk, k_block_stride=stride,
+                                                    softmax_scale=softmax_scale, out=out, lse=lse)
+        buf = _partial_buffer(sh, (B, S, H, D), (B, H, S), query_base.dtype, query_base.device)
+        out, _ = sharded_attention(local, ops.merge_partials, sh, buf)
         return out
     out = ops.posmap_prefill([t(query_base), t(query_group)], [t(key_base), t(key_group)], t(value),
                              pmap=ops.PositionMap.jetlong(int(window_size_left)), q_pos0=int(seqstart_q),
@@ -79,15 +91,18 @@ def fused_jetlong_decode_cache(query_base, query_group, key_cache, value_cache, 
     if _SHARD is not None and cache_pos0 == 0:
         sh = _SHARD
         lo, hi = sh.contiguous_range(kc.shape[1])
-        part = lambda: _decode_range(query_base, query_group, kc[:, lo:hi], vc[:, lo:hi], int(boundary) - lo, lo,
-                                     inv_freq, group_size, softmax_scale, True)
-        out, lse = sharded_attention(part, ops.merge_partials, sh)
+        B, _, H, D = query_base.shape
+        part = lambda out, lse: _decode_range(query_base, query_group, kc[:, lo:hi], vc[:, lo:hi], int(boundary) - lo, lo,
+                                              inv_freq, group_size, softmax_scale, True, out=out, lse=lse)
+        buf = _partial_buffer(sh, (B, 1, H, D), (B, H, 1), query_base.dtype, query_base.device)
+        out, lse = sharded_attention(part, ops.merge_partials, sh, buf)
         return (out, lse) if return_lse else out
     return _decode_range(query_base, query_group, kc, vc, int(boundary) - int(cache_pos0), int(cache_pos0),
                          inv_freq, group_size, softmax_scale, return_lse)
 
 
-def _decode_range(query_base, query_group, kc, vc, b, pos0, inv_freq, group_size, softmax_scale, return_lse):
+def _decode_range(query_base, query_group, kc, vc, b, pos0, inv_freq, group_size, softmax_scale, return_lse,
+                  out=None, lse=None):
     """Decode over rows of a (B,S,Hk,D) cache view whose row 0 has absolute position pos0; rows < b are far."""
     b = max(0, min(b, kc.shape[1]))
     segs = []
@@ -98,4 +113,4 @@ def _decode_range(query_base, query_group, kc, vc, b, pos0, inv_freq, group_size
     if not segs:
         raise RuntimeError("JetLong backend 'fused' got an empty key range")
     return ops.decode_segments([query_base, query_group], segs, inv_freq=inv_freq, group_size=int(group_size),
-                               softmax_scale=softmax_scale, return_lse=return_lse)
+                               softmax_scale=softmax_scale, return_lse=return_lse, out=out, lse=lse)

@@ -57,6 +57,40 @@ class SequenceShard:
         return lo, min(lo + per, n_keys)
 
 
+class PartialBuffer:
+    """One allocation that is both where this rank's kernel writes its partial (O, LSE) and the
+    receive buffer of the all-gather: slot r holds rank r's O (bf16/fp32) followed by its LSE (fp32).
+    The local kernel writes straight into slot `rank`, the collective runs in place, and the merge
+    kernel reads the slots where they land — no packing or unpacking copies."""
+
+    def __init__(self, shard: SequenceShard, out_shape, lse_shape, out_dtype, device):
+        self.shard = shard
+        self.out_shape, self.lse_shape, self.out_dtype = tuple(out_shape), tuple(lse_shape), out_dtype
+        esz = torch.empty(0, dtype=out_dtype).element_size()
+        n_out = 1
+        for d in out_shape:
+            n_out *= d
+        n_lse = 1
+        for d in lse_shape:
+            n_lse *= d
+        self.o_bytes = (n_out * esz + 255) // 256 * 256            # keep the LSE block 256-byte aligned
+        self.slot_bytes = (self.o_bytes + n_lse * 4 + 255) // 256 * 256
+        self._n_out, self._n_lse, self._esz = n_out, n_lse, esz
+        self.buf = torch.empty(shard.world, self.slot_bytes, dtype=torch.uint8, device=device)
+
+    def out_view(self, r: int) -> torch.Tensor:
+        return self.buf[r, : self._n_out * self._esz].view(self.out_dtype).view(self.out_shape)
+
+    def lse_view(self, r: int) -> torch.Tensor:
+        return self.buf[r, self.o_bytes: self.o_bytes + self._n_lse * 4].view(torch.float32).view(self.lse_shape)
+
+    def gather(self):
+        """In-place all-gather of the slots; returns ([out_r], [lse_r]) views for r in range(world)."""
+        sh = self.shard
+        dist.all_gather_into_tensor(self.buf.view(-1), self.buf[sh.rank].view(-1), group=sh.group)
+        return [self.out_view(r) for r in range(sh.world)], [self.lse_view(r) for r in range(sh.world)]
+
+
 def gather_partials(out: torch.Tensor, lse: torch.Tensor, shard: SequenceShard):
     """All-gather one (O, LSE) pair per rank.  out (B,S,H,D), lse (B,H,S) fp32 ->
     (outs (world,B,S,H,D), lses (world,B,H,S)), identical on every rank."""
@@ -67,10 +101,20 @@ def gather_partials(out: torch.Tensor, lse: torch.Tensor, shard: SequenceShard):
     return outs, lses
 
 
-def sharded_attention(local_attention: Callable[[], tuple[torch.Tensor, torch.Tensor]],
+def sharded_attention(local_attention: Callable[..., tuple[torch.Tensor, torch.Tensor]],
                       merge: Callable[[Sequence[torch.Tensor], Sequence[torch.Tensor]], tuple[torch.Tensor, torch.Tensor]],
-                      shard: SequenceShard):
-    """partial (O, LSE) over this rank's keys -> all-gather -> N-way merge.  Returns (out, lse)."""
+                      shard: SequenceShard, buffer: Optional[PartialBuffer] = None):
+    """partial (O, LSE) over this rank's keys -> all-gather -> N-way merge.  Returns (out, lse).
+
+    Without `buffer`, local_attention() returns its (out, lse) and they are gathered into fresh tensors.
+    With `buffer`, local_attention(out=..., lse=...) must write into the given views (slot `rank` of the
+    buffer) and the gather runs in place."""
+    if buffer is not None:
+        local_attention(out=buffer.out_view(shard.rank), lse=buffer.lse_view(shard.rank))
+        if shard.world == 1:
+            return buffer.out_view(0), buffer.lse_view(0)
+        outs, lses = buffer.gather()
+        return merge(outs, lses)
     out, lse = local_attention()
     if shard.world == 1:
         return out, lse

@@ -61,7 +61,16 @@ def _worker(rank, world, port, block, results):
             of, lf = orc.attention(q1g, kf, vf) if kf.shape[1] else (torch.zeros(B, 1, H, D), torch.full((B, H, 1), -float("inf")))
             return orc.merge2(on, ln, of, lf)
 
-        od, ld = sharded_attention(local_dec, merge, shard)
+        from jetlm.kernels.sequence_parallel import PartialBuffer
+        buf = PartialBuffer(shard, (B, 1, H, D), (B, H, 1), torch.float32, "cpu")      # in-place gather path
+
+        def local_dec_into(out, lse):
+            o, l = local_dec()
+            out.copy_(o); lse.copy_(l)
+
+        od, ld = sharded_attention(local_dec_into, merge, shard, buf)
+        od2, ld2 = sharded_attention(local_dec, merge, shard)
+        assert torch.equal(od, od2) and torch.equal(ld, ld2)
         eod, eld = orc.jetlong_decode(q1, q1g, kb[:, boundary:], v[:, boundary:], kg[:, :boundary], v[:, :boundary])
         dd, _ = orc.compare(od, eod)
         dld, _ = orc.compare(ld, eld)
