@@ -399,7 +399,10 @@ def main():
                     frac_of_burst=round(achieved / peaks["bf16_tflops"], 4), frac_of_nominal_2250=round(achieved / 2250.0, 4),
                     launches_timed=len(pre), mean_launch_ms=round(mean_ms, 3),
                     attention_share_of_step=round(sum(t for t, _ in pre) / total_ms, 4) if pre else None,
-                    algorithmic_flops_per_launch=flops_launch, traffic=None)
+                    algorithmic_flops_per_launch=flops_launch,
+                    # dram read+write bytes of one launch: ncu capture at 32768 tokens (0.958 GB, profiles/), scaled by
+                    # tokens — every operand crosses HBM once and K/V re-reads are L2 hits, so traffic grows with S
+                    traffic=round(0.958e9 * args.seq / 32768 / world), traffic_source="ncu at 32768 tokens, scaled by tokens")
 
     line = dict(metric="prefill_tok_per_s", value=round(args.seq * args.steps / (total_ms * 1e-3), 1), unit="tok/s",
                 n_gpus=world, steps=args.steps, warmup=args.warmup, ms_per_step=round(total_ms / args.steps, 2),
