@@ -65,16 +65,6 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) decode_kernel(const DecPara
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int rep = p.heads / p.kv_heads;            // query heads per kv head (<= 16)
 
-  // ---- stage the packed query rows of every class (rows >= rep are zero) ----
-  for (int i = threadIdx.x; i < JL_MAX_CLASSES * 16 * 16; i += blockDim.x) {
-    const int c = i / 256, row = (i / 16) % 16, chunk = i % 16;
-    uint4 val = make_uint4(0, 0, 0, 0);
-    if (p.q[c] != nullptr && row < rep)
-      val = *reinterpret_cast<const uint4*>(p.q[c] + b * p.qs_b + (kvh * rep + row) * p.qs_h + chunk * 8);
-    *reinterpret_cast<uint4*>(&sm.q[c][swz256(row, chunk)]) = val;
-  }
-  if (threadIdx.x < 64) sm.inv_freq[threadIdx.x] = p.inv_freq != nullptr ? p.inv_freq[threadIdx.x] : 0.f;
-
   // ---- this CTA's key range in the virtual concatenation of the segments ----
   int seg_len[JL_MAX_SEGMENTS];
   int64_t total = 0;
@@ -107,7 +97,6 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) decode_kernel(const DecPara
       base += seg_len[s];
     }
   }
-  __syncthreads();
 
   auto locate = [&](int t, int& s_out, int& row0, int& valid) {
     int s = 0;
@@ -147,8 +136,21 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) decode_kernel(const DecPara
   for (int i = 0; i < 16; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
+  // start streaming K/V before anything else: the first tiles' latency overlaps the query staging
 #pragma unroll
   for (int t = 0; t < kDecStages - 1; ++t) issue(t);
+
+  // ---- stage the packed query rows of every class (rows >= rep are zero) ----
+  for (int i = threadIdx.x; i < JL_MAX_CLASSES * 16 * 16; i += blockDim.x) {
+    const int c = i / 256, row = (i / 16) % 16, chunk = i % 16;
+    uint4 val = make_uint4(0, 0, 0, 0);
+    if (p.q[c] != nullptr && row < rep)
+      val = *reinterpret_cast<const uint4*>(p.q[c] + b * p.qs_b + (kvh * rep + row) * p.qs_h + chunk * 8);
+    *reinterpret_cast<uint4*>(&sm.q[c][swz256(row, chunk)]) = val;
+  }
+  if (threadIdx.x < 64) sm.inv_freq[threadIdx.x] = p.inv_freq != nullptr ? p.inv_freq[threadIdx.x] : 0.f;
+
+  __syncthreads();
 
   for (int t = 0; t < n_tiles; ++t) {
     cp_async_wait<kDecStages - 2>();
@@ -318,10 +320,20 @@ __global__ void __launch_bounds__(128) decode_combine_kernel(const float* __rest
   for (int s = 0; s < num_splits; ++s) m = fmaxf(m, part_lse[base + s]);
   const float ms = m == -INFINITY ? 0.f : m;
   float wsum = 0.f, acc = 0.f;
-  for (int s = 0; s < num_splits; ++s) {
-    const float w = exp2f((part_lse[base + s] - ms) * kLog2e);
-    wsum += w;
-    acc = fmaf(w, part_o[(base + s) * 128 + d], acc);
+  for (int s0 = 0; s0 < num_splits; s0 += 8) {
+    float x[8], l[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {          // 8 independent loads in flight per thread
+      const bool ok = s0 + k < num_splits;
+      x[k] = ok ? part_o[(base + s0 + k) * 128 + d] : 0.f;
+      l[k] = ok ? part_lse[base + s0 + k] : -INFINITY;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float w = exp2f((l[k] - ms) * kLog2e);
+      wsum += w;
+      acc = fmaf(w, x[k], acc);
+    }
   }
   out[b * os_b + h * os_h + d] = __float2bfloat16(wsum > 0.f ? acc / wsum : 0.f);
   if (lse_out != nullptr && d == 0) lse_out[static_cast<int64_t>(b) * heads + h] = wsum > 0.f ? ms + logf(wsum) : -INFINITY;
