@@ -10,9 +10,11 @@ dominant kernel and the reference's CPU path timed beside it.
 
 One "step" is one prefill forward `model(input_ids, use_cache=True)` over a fresh 131072-token
 prompt (the reference's own protocol: scripts/throughput/bench_prefill_throughput.py:83-95 in the
-Jet-Long repository), random-init bf16 weights, uniform random token ids.  With N > 1 the key
-sequence of every attention call is sharded block-cyclically over the ranks and partial (O, LSE)
-pairs are combined after an NCCL all-gather (strong scaling: the prompt stays 131072 tokens).
+Jet-Long repository), random-init bf16 weights, uniform random token ids.  With N > 1 the prompt is
+sequence-parallel: tokens (projections, MLP, logits) and the KV cache are sharded block-cyclically
+over the ranks; per layer the base-rotated queries are all-gathered, every rank attends all query
+stripes to its own key stripe, and the partial (O, LSE) pairs go back to the ranks that own the
+rows (all-to-all) where the merge kernel combines them (strong scaling: the prompt stays 131072 tokens).
 Rank 0 prints ONE JSON line.
 """
 from __future__ import annotations
@@ -193,7 +195,8 @@ def workload_config(args, cfg, G):
                 head_dim=128, hidden=cfg.hidden_size, w=args.w, w_0=args.w0, group_size=G,
                 logits="all positions (reference bench protocol)" if args.logits_to_keep == 0 else f"last {args.logits_to_keep}",
                 l2="inputs and weights far exceed the 126 MB L2; decode microbench flushes L2 (256 MB write + 256 MB read) between iterations",
-                parallelism=f"kv-sequence-sharded x{args.gpus}" if args.gpus > 1 else "single GPU")
+                parallelism=(f"sequence-parallel x{args.gpus}: tokens and KV cache block-cyclic over ranks, Q all-gather, "
+                             f"partial (O,LSE) all-to-all + N-way merge") if args.gpus > 1 else "single GPU")
 
 
 # --------------------------------------------------------------------------------------------------
@@ -337,6 +340,9 @@ def main():
     with torch.device("cuda"):
         model = Qwen3JetLongFusedForCausalLM(cfg).eval()
     torch.set_default_dtype(prev)
+    if shard is not None:
+        # sequence parallel: every rank embeds / projects / stores only its block-cyclic stripe of the prompt
+        model.model.token_sharded = True
 
     gen = torch.Generator().manual_seed(1)
     ids_host = torch.randint(0, cfg.vocab_size, (1, args.seq), generator=gen).pin_memory()
@@ -390,7 +396,7 @@ def main():
     torch.cuda.synchronize()
     pre = [(s.elapsed_time(e), info) for name, s, e, info in sink if name == "jl_prefill"]
     H, D = cfg.num_attention_heads, 128
-    flops_launch = 4.0 * D * H * args.seq * (args.seq + 1) / 2 / world
+    flops_launch = 4.0 * D * H * args.seq * (args.seq + 1) / 2 / world ** 2      # N launches per layer and rank, one per query stripe
     mean_ms = statistics.mean(t for t, _ in pre) if pre else float("nan")
     achieved = flops_launch / (mean_ms * 1e-3) / 1e12
     roofline = dict(bound="tensor", kernel="jl_prefill (bifocal attention)", achieved=round(achieved, 1),
@@ -402,7 +408,7 @@ def main():
                     algorithmic_flops_per_launch=flops_launch,
                     # dram read+write bytes of one launch: ncu capture at 32768 tokens (0.958 GB, profiles/), scaled by
                     # tokens — every operand crosses HBM once and K/V re-reads are L2 hits, so traffic grows with S
-                    traffic=round(0.958e9 * args.seq / 32768 / world), traffic_source="ncu at 32768 tokens, scaled by tokens")
+                    traffic=round(0.958e9 * args.seq / 32768 / world ** 2), traffic_source="ncu at 32768 tokens, scaled by tokens")
 
     line = dict(metric="prefill_tok_per_s", value=round(args.seq * args.steps / (total_ms * 1e-3), 1), unit="tok/s",
                 n_gpus=world, steps=args.steps, warmup=args.warmup, ms_per_step=round(total_ms / args.steps, 2),

@@ -76,9 +76,11 @@ typedef struct {
 /* ---------------------------------------------------------------------------------------------
  * jl_prefill — single-pass position-mapped causal attention for a block of Sq query tokens
  * against Skv keys.  One online softmax spans all classes; no packed 2S tensors, no separate
- * merge.  Query row i has absolute position q_pos0 + i.  Key row j has absolute position
- * k_pos0 + (j / k_block) * k_block_stride + (j % k_block): a contiguous cache uses
- * k_block >= Skv; a block-cyclic shard of a sequence-parallel cache uses its stripe geometry.
+ * merge.  Key row j has absolute position k_pos0 + (j / k_block) * k_block_stride + (j % k_block):
+ * a contiguous cache uses k_block <= 0; a block-cyclic shard of a sequence-parallel cache uses its
+ * stripe geometry.  Query rows follow the same rule with q_pos0 / q_block / q_block_stride (a
+ * contiguous block of queries uses q_block <= 0, i.e. row i is at q_pos0 + i; q_block must be a
+ * multiple of 256 otherwise).
  *
  * q[c]: (B, Sq, H, D)   k[c], v: (B, Skv, Hk, D)   out: (B, Sq, H, D)   lse: (B, H, Sq) fp32.
  * lse may be NULL.  Rows that see no key produce a zero output row and lse = -inf.
@@ -101,6 +103,8 @@ typedef struct {
   float softmax_scale;
   jl_posmap map;
   int32_t impl;             /* 0 = default kernel; 1 = legacy mma.sync kernel kept as GPU cross-check */
+  int64_t q_block;          /* <= 0 means contiguous */
+  int64_t q_block_stride;
 } jl_prefill_args;
 
 int jl_prefill(const jl_prefill_args* args, void* cuda_stream);
@@ -205,7 +209,8 @@ int jl_merge(const jl_merge_args* args, void* cuda_stream);
 
 /* ---------------------------------------------------------------------------------------------
  * jl_rotate — rotate-half RoPE of x by an integer position function, fp32 math, one rounding:
- *   t(p)  = min((p / div) * div_mul + (p % mod) * mod_mul + add, t_max),  p = pos0 + row
+ *   t(p)  = min((p / div) * div_mul + (p % mod) * mod_mul + add, t_max),
+ *   p     = pos0 + row, or pos0 + (row / pos_block) * pos_block_stride + row % pos_block for a block-cyclic stripe
  *   theta = fp32(t) * inv_freq[d]            (one fp32 rounding, as the reference forms it)
  *   out[d], out[d+D/2] = x[d] cos - x[d+D/2] sin, x[d+D/2] cos + x[d] sin
  * Covers base RoPE (t = p), the jetlong regroup of base-rotated tensors (t = p/G - p),
@@ -221,6 +226,8 @@ typedef struct {
   int64_t pos0;
   int64_t div, div_mul, mod, mod_mul, add, t_max;
   const float* inv_freq;    /* (head_dim/2,) fp32 device array */
+  int64_t pos_block;        /* <= 0 means contiguous */
+  int64_t pos_block_stride;
 } jl_rotate_args;
 
 int jl_rotate(const jl_rotate_args* args, void* cuda_stream);

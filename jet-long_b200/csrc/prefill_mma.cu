@@ -22,7 +22,7 @@ struct PfParams {
   float* lse;
   int64_t qs_b, qs_s, qs_h, ks_b, ks_s, ks_h, vs_b, vs_s, vs_h, os_b, os_s, os_h;
   int batch, sq, sk, heads, kv_heads;
-  int64_t q_pos0, k_pos0, k_block, k_block_stride;
+  int64_t q_pos0, k_pos0, k_block, k_block_stride, q_block, q_block_stride;
   float scale_log2;
   int map_kind, n_classes;
   int64_t near_span, chunk;
@@ -50,7 +50,8 @@ __global__ void __launch_bounds__(kPfWarps * 32, 1) prefill_mma_kernel(const PfP
   const int kvh = h / (p.heads / p.kv_heads);
   const int q0 = qt * kPfM;
   const int q_valid = min(kPfM, p.sq - q0);
-  const int64_t pq_first = p.q_pos0 + q0, pq_last = p.q_pos0 + q0 + q_valid - 1;
+  // a 128-row query tile never straddles a position block (q_block is a multiple of 256)
+  const int64_t pq_first = key_position(q0, p.q_pos0, p.q_block, p.q_block_stride), pq_last = pq_first + q_valid - 1;
 
   // ---- Q tiles of every class (zero-filled past the end) ----
   for (int c = 0; c < p.n_classes; ++c) {
@@ -127,7 +128,7 @@ __global__ void __launch_bounds__(kPfWarps * 32, 1) prefill_mma_kernel(const PfP
   for (int i = 0; i < 16; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const int g = lane >> 2, tq = lane & 3;
-  const int64_t pq_row[2] = {p.q_pos0 + q0 + warp * 16 + g, p.q_pos0 + q0 + warp * 16 + g + 8};
+  const int64_t pq_row[2] = {pq_first + warp * 16 + g, pq_first + warp * 16 + g + 8};
 
   load_tile(0, 0);
   for (int j = 0; j < n_ktiles; ++j) {
@@ -290,6 +291,9 @@ int launch_prefill_mma(const jl_prefill_args* a, cudaStream_t stream) {
   p.q_pos0 = a->q_pos0; p.k_pos0 = a->k_pos0;
   p.k_block = (a->k_block > 0 && a->k_block < a->seqlen_k) ? a->k_block : 0;
   p.k_block_stride = a->k_block_stride;
+  p.q_block = (a->q_block > 0 && a->q_block < a->seqlen_q) ? a->q_block : 0;
+  p.q_block_stride = a->q_block_stride;
+  if (p.q_block % 256 != 0) return fail(JL_ERR_UNSUPPORTED, "jl_prefill: q_block must be a multiple of 256");
   if (p.k_block > 0 && p.k_block % kPfN != 0)
     return fail(JL_ERR_UNSUPPORTED, "jl_prefill: k_block must be a multiple of %d", kPfN);
   p.scale_log2 = a->softmax_scale * kLog2e;

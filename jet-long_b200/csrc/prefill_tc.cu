@@ -40,7 +40,7 @@ constexpr int64_t kNegInfPos = -(int64_t(1) << 60);
 
 struct Params {
   int sq, sk, heads, kv_heads, batch;
-  int64_t q_pos0, k_pos0, k_block, k_block_stride;
+  int64_t q_pos0, k_pos0, k_block, k_block_stride, q_block, q_block_stride;
   float scale_log2;
   int map_kind, n_classes;
   int64_t near_span, chunk;
@@ -257,7 +257,8 @@ __device__ __forceinline__ Schedule make_schedule(const Params& p, int q_row0) {
   s.n_phases = 0;
   s.total = 0;
   const int rows = min(kRowsPerCta, p.sq - q_row0);
-  const int64_t pq_first = p.q_pos0 + q_row0, pq_last = pq_first + rows - 1;
+  // the CTA's 256 rows never straddle a position block (q_block is a multiple of 256)
+  const int64_t pq_first = key_position(q_row0, p.q_pos0, p.q_block, p.q_block_stride), pq_last = pq_first + rows - 1;
   for (int c = p.n_classes - 1; c >= 0; --c) {       // far classes first, the diagonal last
     int64_t lo, hi, dummy;
     class_interval(p, c, pq_first, lo, dummy);
@@ -418,10 +419,11 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
     const int row_in_tile = quad * 32 + lane;
     const int q_row = q_row0 + t * kTileM + row_in_tile;
     const bool row_valid = q_row < p.sq;
-    const int64_t pq = p.q_pos0 + (row_valid ? q_row : p.sq - 1);
+    const int64_t pq_cta0 = key_position(q_row0, p.q_pos0, p.q_block, p.q_block_stride);     // position of the CTA's first row
+    const int64_t pq = pq_cta0 + (row_valid ? q_row : p.sq - 1) - q_row0;
     // bounds of this tile's valid rows, for the uniform-tile test
     const int tile_rows = min(kTileM, p.sq - (q_row0 + t * kTileM));
-    const int64_t pq_t0 = p.q_pos0 + q_row0 + t * kTileM;
+    const int64_t pq_t0 = pq_cta0 + t * kTileM;
     const int64_t pq_t1 = pq_t0 + (tile_rows > 0 ? tile_rows - 1 : 0);
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t t_s = tmem + lane_base + t * 128;
@@ -601,6 +603,7 @@ static int make_map(CUtensorMap* m, const void* base, int batch, int seq, int he
 bool prefill_tc_supports(const jl_prefill_args* a) {
   if (a->seqlen_k < 1) return false;
   if (a->k_block > 0 && a->k_block < a->seqlen_k && (a->k_block % tc::kTileN != 0)) return false;
+  if (a->q_block > 0 && a->q_block < a->seqlen_q && (a->q_block % tc::kRowsPerCta != 0)) return false;
   int distinct = 0;
   const void* seen[2] = {nullptr, nullptr};
   for (int c = 0; c < a->map.n_classes; ++c) {
@@ -663,6 +666,8 @@ int launch_prefill_tc(const jl_prefill_args* a, cudaStream_t stream) {
   p.q_pos0 = a->q_pos0; p.k_pos0 = a->k_pos0;
   p.k_block = (a->k_block > 0 && a->k_block < a->seqlen_k) ? a->k_block : 0;
   p.k_block_stride = a->k_block_stride;
+  p.q_block = (a->q_block > 0 && a->q_block < a->seqlen_q) ? a->q_block : 0;
+  p.q_block_stride = a->q_block_stride;
   p.scale_log2 = a->softmax_scale * kLog2e;
   p.map_kind = a->map.kind; p.n_classes = a->map.n_classes;
   p.near_span = a->map.near_span; p.chunk = a->map.chunk > 0 ? a->map.chunk : 1;

@@ -12,7 +12,7 @@ struct RotateParams {
   __nv_bfloat16* out;
   int64_t xs_b, xs_s, xs_h, os_b, os_s, os_h;
   int batch, seqlen, heads;
-  int64_t pos0, div, div_mul, mod, mod_mul, add, t_max;
+  int64_t pos0, div, div_mul, mod, mod_mul, add, t_max, pos_block, pos_block_stride;
   const float* inv_freq;
 };
 
@@ -29,7 +29,7 @@ __global__ void __launch_bounds__(256) rotate_kernel(const RotateParams p) {
     r /= p.heads;
     const int64_t s = r % p.seqlen;
     const int64_t b = r / p.seqlen;
-    const int64_t pos = p.pos0 + s;
+    const int64_t pos = key_position(s, p.pos0, p.pos_block, p.pos_block_stride);
     int64_t t = (pos / p.div) * p.div_mul + (pos % p.mod) * p.mod_mul + p.add;
     t = t < p.t_max ? t : p.t_max;
     const float tf = static_cast<float>(t);
@@ -75,6 +75,8 @@ int launch_rotate(const jl_rotate_args* a, cudaStream_t stream) {
   p.batch = a->batch; p.seqlen = a->seqlen; p.heads = a->heads;
   p.pos0 = a->pos0; p.div = a->div; p.div_mul = a->div_mul; p.mod = a->mod; p.mod_mul = a->mod_mul;
   p.add = a->add; p.t_max = a->t_max;
+  p.pos_block = (a->pos_block > 0 && a->pos_block < a->seqlen) ? a->pos_block : 0;
+  p.pos_block_stride = a->pos_block_stride;
   p.inv_freq = a->inv_freq;
   const int64_t total = static_cast<int64_t>(a->batch) * a->seqlen * a->heads * 8;
   if (total == 0) return JL_OK;

@@ -35,6 +35,7 @@ class PrefillArgs(C.Structure):
         ("heads", C.c_int32), ("kv_heads", C.c_int32), ("head_dim", C.c_int32),
         ("q_pos0", C.c_int64), ("k_pos0", C.c_int64), ("k_block", C.c_int64), ("k_block_stride", C.c_int64),
         ("softmax_scale", C.c_float), ("map", PosMap), ("impl", C.c_int32),
+        ("q_block", C.c_int64), ("q_block_stride", C.c_int64),
     ]
 
 
@@ -76,6 +77,7 @@ class RotateArgs(C.Structure):
         ("batch", C.c_int32), ("seqlen", C.c_int32), ("heads", C.c_int32), ("head_dim", C.c_int32),
         ("pos0", C.c_int64), ("div", C.c_int64), ("div_mul", C.c_int64), ("mod", C.c_int64),
         ("mod_mul", C.c_int64), ("add", C.c_int64), ("t_max", C.c_int64), ("inv_freq", C.c_void_p),
+        ("pos_block", C.c_int64), ("pos_block_stride", C.c_int64),
     ]
 
 

@@ -34,6 +34,59 @@ def configure_sequence_sharding(shard: SequenceShard | None) -> None:
     _SHARD = shard if shard is not None and shard.world > 1 else None
 
 
+def sequence_shard() -> SequenceShard | None:
+    return _SHARD
+
+
+def fused_jetlong_prefill_token_sharded(query_base, key_base, key_group, value, *, q_start: int, inv_freq,
+                                        group_size: int, window_size_left: int, softmax_scale: float):
+    """Bifocal prefill when the TOKENS are sharded block-cyclically over the ranks (every rank ran the
+    projections only for its own stripe of the prompt and keeps only its stripe of the KV cache).
+
+    query_base (B, S_loc, H, D): this rank's base-rotated queries, row i at position
+    q_start + rank*blk + (i // blk) * world*blk + i % blk.  key_base / key_group / value
+    (B, Skv_loc, Hk, D) views: this rank's cache stripe (same geometry from position 0).
+    Steps: all-gather the base-rotated queries (the regrouped ones are re-derived locally), attend
+    every rank's query stripe to the local key stripe, send each partial (O, LSE) to the rank that
+    owns those query rows (all-to-all), merge the N partials of the local rows.  Returns (B, S_loc, H, D).
+    K and V never cross NVLink; per layer a rank receives one copy of Q and one copy of O."""
+    import torch.distributed as dist
+    sh = _SHARD
+    if sh is None:
+        raise RuntimeError("token-sharded prefill needs configure_sequence_sharding(...) first")
+    N, blk = sh.world, sh.block
+    B, S_loc, H, D = query_base.shape
+    if S_loc % blk != 0:
+        raise ValueError(f"token-sharded prefill needs whole blocks per rank: {S_loc} local rows, block {blk}")
+    dev, dt = query_base.device, query_base.dtype
+    key = ("tok", sh.rank, N, B, S_loc, H, D, dt, dev)
+    bufs = _BUFFERS.get(key)
+    if bufs is None:
+        bufs = _BUFFERS[key] = dict(
+            q_all=torch.empty(N, B, S_loc, H, D, dtype=dt, device=dev),
+            q_grp=torch.empty(B, S_loc, H, D, dtype=dt, device=dev),
+            send_o=torch.empty(N, B, S_loc, H, D, dtype=dt, device=dev),
+            send_l=torch.empty(N, B, H, S_loc, dtype=torch.float32, device=dev),
+            recv_o=torch.empty(N, B, S_loc, H, D, dtype=dt, device=dev),
+            recv_l=torch.empty(N, B, H, S_loc, dtype=torch.float32, device=dev))
+    q_all, q_grp = bufs["q_all"], bufs["q_grp"]
+    dist.all_gather_into_tensor(q_all.view(-1), query_base.contiguous().view(-1), group=sh.group)
+    pmap = ops.PositionMap.jetlong(int(window_size_left))
+    stride = N * blk
+    for r in range(N):
+        qb = q_all[r]
+        ops.rope_regroup(qb, inv_freq, group_size=int(group_size), pos0=int(q_start) + r * blk, pos_block=blk,
+                         pos_block_stride=stride, out=q_grp)
+        ops.posmap_prefill([qb, q_grp], [key_base, key_group], value, pmap=pmap,
+                           q_pos0=int(q_start) + r * blk, q_block=blk, q_block_stride=stride,
+                           k_pos0=sh.rank * blk, k_block=blk, k_block_stride=stride, softmax_scale=softmax_scale,
+                           out=bufs["send_o"][r], lse=bufs["send_l"][r])
+    dist.all_to_all_single(bufs["recv_o"].view(-1), bufs["send_o"].view(-1), group=sh.group)
+    dist.all_to_all_single(bufs["recv_l"].view(-1), bufs["send_l"].view(-1), group=sh.group)
+    out = ops.merge_partials(list(bufs["recv_o"].unbind(0)), list(bufs["recv_l"].unbind(0)), return_lse=False)
+    return out
+
+
 def fused_jetlong_prefill(query_base, query_group, key_base, key_group, value, *, seqstart_q: int,
                           window_size_left: int, softmax_scale: float, has_any_pad: bool, training: bool):
     """(B,H,S,D) / (B,Hk,Skv,D) views in, attention output (B,S,H,D) out."""

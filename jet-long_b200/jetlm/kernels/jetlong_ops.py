@@ -135,9 +135,11 @@ _BIG = (1 << 62)
 
 def rope_rotate(x: torch.Tensor, inv_freq: torch.Tensor, *, pos0: int = 0, div: int = 1, div_mul: int = 1,
                 mod: int = _BIG, mod_mul: int = 0, add: int = 0, t_max: int = _BIG,
+                pos_block: int = 0, pos_block_stride: int = 0,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out = rotate-half RoPE of x (B,S,H,D view) at t(p) = min((p//div)*div_mul + (p%mod)*mod_mul + add, t_max),
-    p = pos0 + row.  fp32 math on the angles fp32(t)*inv_freq, one rounding to bf16."""
+    p = pos0 + row (or the block-cyclic pos0 + (row // pos_block) * pos_block_stride + row % pos_block).
+    fp32 math on the angles fp32(t)*inv_freq, one rounding to bf16."""
     op = "rope_rotate"
     _check_view(op, "x", x)
     if x.dtype not in _SUPPORTED_DTYPES:
@@ -154,20 +156,21 @@ def rope_rotate(x: torch.Tensor, inv_freq: torch.Tensor, *, pos0: int = 0, div: 
     B, S, H, D = x.shape
     a = N.RotateArgs(x.data_ptr(), out.data_ptr(), _st(x, 0), _st(x, 1), _st(x, 2), _st(out, 0), _st(out, 1), _st(out, 2),
                      B, S, H, D, int(pos0), int(div), int(div_mul), int(mod), int(mod_mul), int(add), int(t_max),
-                     inv_freq.data_ptr())
+                     inv_freq.data_ptr(), int(pos_block), int(pos_block_stride))
     with torch.cuda.device(x.device):
         _timed_call("jl_rotate", lambda: N.lib().jl_rotate(C.byref(a), _stream()))
     return out
 
 
-def rope_base(x, inv_freq, *, pos0=0, out=None):
+def rope_base(x, inv_freq, *, pos0=0, pos_block=0, pos_block_stride=0, out=None):
     """Base RoPE: t = p."""
-    return rope_rotate(x, inv_freq, pos0=pos0, out=out)
+    return rope_rotate(x, inv_freq, pos0=pos0, pos_block=pos_block, pos_block_stride=pos_block_stride, out=out)
 
 
-def rope_regroup(x_base, inv_freq, *, group_size: int, pos0=0, out=None):
+def rope_regroup(x_base, inv_freq, *, group_size: int, pos0=0, pos_block=0, pos_block_stride=0, out=None):
     """jetlong far-class operand from a base-rotated tensor: extra rotation by floor(p/G) - p."""
-    return rope_rotate(x_base, inv_freq, pos0=pos0, div=int(group_size), div_mul=1, mod=_BIG, mod_mul=-1, out=out)
+    return rope_rotate(x_base, inv_freq, pos0=pos0, div=int(group_size), div_mul=1, mod=_BIG, mod_mul=-1,
+                       pos_block=pos_block, pos_block_stride=pos_block_stride, out=out)
 
 
 # ----------------------------------------------------------------------------------------------
@@ -234,7 +237,8 @@ def merge_partials(o_parts: Sequence[torch.Tensor], lse_parts: Sequence[torch.Te
 
 def posmap_prefill(q_ops: Sequence[torch.Tensor], k_ops: Sequence[torch.Tensor], v: torch.Tensor, *,
                    pmap: PositionMap, q_pos0: int, k_pos0: int = 0, softmax_scale: Optional[float] = None,
-                   k_block: int = 0, k_block_stride: int = 0, out: Optional[torch.Tensor] = None,
+                   k_block: int = 0, k_block_stride: int = 0, q_block: int = 0, q_block_stride: int = 0,
+                   out: Optional[torch.Tensor] = None,
                    lse: Optional[torch.Tensor] = None, return_lse: bool = True, impl: int = 0):
     """Single-pass position-mapped causal attention (see jl_prefill).  q_ops[c]: (B,Sq,H,D) views sharing
     strides; k_ops[c], v: (B,Skv,Hk,D) views (all k_ops share strides).  Returns (out, lse) or out."""
@@ -295,6 +299,7 @@ def posmap_prefill(q_ops: Sequence[torch.Tensor], k_ops: Sequence[torch.Tensor],
     a.softmax_scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
     a.map = pmap.c_struct()
     a.impl = int(impl)
+    a.q_block, a.q_block_stride = int(q_block), int(q_block_stride)
     with torch.cuda.device(q0.device):
         _timed_call("jl_prefill", lambda: N.lib().jl_prefill(C.byref(a), _stream()),
                     dict(B=B, Sq=Sq, Skv=Skv, H=H, q_pos0=int(q_pos0)))

@@ -58,6 +58,7 @@ class BifocalPlan:
     q_pos0: int              # absolute position of the first query token
     max_q_pos: int           # absolute position of the last query token
     has_any_pad: bool        # a left-padded batch (unsupported by the fused kernels)
+    token_shard: object = None   # SequenceShard when this rank holds a block-cyclic stripe of the tokens
 
 
 class Qwen3JetLongFusedRotaryEmbedding(Qwen3RotaryEmbedding):
@@ -76,7 +77,8 @@ class Qwen3JetLongFusedRotaryEmbedding(Qwen3RotaryEmbedding):
             self.jetlong_w_0 = int(cfg["w_0"])
 
     @torch.no_grad()
-    def forward(self, x, position_ids, max_position: Optional[int] = None, kv_len: Optional[int] = None):
+    def forward(self, x, position_ids, max_position: Optional[int] = None, kv_len: Optional[int] = None,
+                first_position: Optional[int] = None, token_shard=None):
         cos, sin = super().forward(x, position_ids)
         if not self.jetlong_enabled:
             return cos, sin
@@ -90,7 +92,8 @@ class Qwen3JetLongFusedRotaryEmbedding(Qwen3RotaryEmbedding):
         has_pad = False
         if position_ids.shape[0] > 1 and kv_len is not None:
             has_pad = bool(((kv_len - 1 - position_ids[:, -1]) > 0).any().item())
-        plan = BifocalPlan(group, max_position - seq + 1, max_position, has_pad)
+        first = first_position if first_position is not None else max_position - seq + 1
+        plan = BifocalPlan(group, first, max_position, has_pad, token_shard)
         return cos, sin, group, self.inv_freq.to(device=x.device, dtype=torch.float32), position_ids, plan
 
 
@@ -162,6 +165,9 @@ class Qwen3JetLongFusedAttention(nn.Module):
             raise RuntimeError("JetLong backend 'fused' is inference-only")
         w_0 = self.jetlong_w_0
 
+        if plan.token_shard is not None:
+            return self._token_sharded_prefill(q, k, v, plan, group, inv_freq, past_key_values, out_shape, backend, ops)
+
         # base RoPE in one fused pass each; K is written straight into (B, Hk, S, D) cache layout
         q_base = ops.rope_base(q, inv_freq, pos0=plan.q_pos0)
         k_new = torch.empty(bsz, Hk, seq, D, dtype=k.dtype, device=k.device)
@@ -196,6 +202,29 @@ class Qwen3JetLongFusedAttention(nn.Module):
         return self.o_proj(attn.reshape(*out_shape, -1)), None
 
 
+    def _token_sharded_prefill(self, q, k, v, plan, group, inv_freq, past_key_values, out_shape, backend, ops):
+        """This rank ran the projections for a block-cyclic stripe of the prompt only; it keeps that
+        stripe of the KV cache, and the attention exchanges Q and partial (O, LSE) between ranks."""
+        sh = plan.token_shard
+        bsz, seq = out_shape
+        Hk, D = self.num_kv_heads, self.head_dim
+        geo = dict(pos_block=sh.block, pos_block_stride=sh.world * sh.block)
+        q_base = ops.rope_base(q, inv_freq, pos0=plan.q_pos0 + sh.rank * sh.block, **geo)
+        k_new = torch.empty(bsz, Hk, seq, D, dtype=k.dtype, device=k.device)
+        ops.rope_base(k, inv_freq, pos0=plan.q_pos0 + sh.rank * sh.block, out=k_new.transpose(1, 2), **geo)
+        if past_key_values is not None:
+            k_all, v_all = past_key_values.update(k_new, v.transpose(1, 2), self.layer_idx, {})
+        else:
+            k_all, v_all = k_new, v.transpose(1, 2)
+        k_group = torch.empty(k_all.shape, dtype=k_all.dtype, device=k_all.device)
+        ops.rope_regroup(k_all.transpose(1, 2), inv_freq, group_size=group, pos0=sh.rank * sh.block,
+                         out=k_group.transpose(1, 2), **geo)
+        attn = backend.fused_jetlong_prefill_token_sharded(
+            q_base, k_all.transpose(1, 2), k_group.transpose(1, 2), v_all.transpose(1, 2), q_start=plan.q_pos0,
+            inv_freq=inv_freq, group_size=group, window_size_left=self.jetlong_w_0, softmax_scale=self.scaling)
+        return self.o_proj(attn.reshape(bsz, seq, -1)), None
+
+
 class Qwen3JetLongFusedDecoderLayer(Qwen3DecoderLayer):
     def __init__(self, config: Qwen3Config, layer_idx: int):
         super().__init__(config, layer_idx)
@@ -223,6 +252,10 @@ class Qwen3JetLongFusedModel(Qwen3PreTrainedModel):
                 inputs_embeds=None, use_cache=None, cache_position=None, **kwargs) -> BaseModelOutputWithPast:
         if (input_ids is None) ^ (inputs_embeds is not None):
             raise ValueError("You must specify exactly one of input_ids or inputs_embeds")
+        from jetlm.kernels import cute_jetlong_backend as backend
+        shard = backend.sequence_shard() if getattr(self, "token_sharded", False) else None
+        if shard is not None:
+            return self._forward_token_sharded(input_ids, past_key_values, use_cache, shard, **kwargs)
         if inputs_embeds is None:
             inputs_embeds = self.embed_tokens(input_ids)
         if use_cache and past_key_values is None:
@@ -256,6 +289,32 @@ class Qwen3JetLongFusedModel(Qwen3PreTrainedModel):
         hidden = self.norm(hidden)
         return BaseModelOutputWithPast(last_hidden_state=hidden,
                                        past_key_values=past_key_values if use_cache else None)
+
+
+    def _forward_token_sharded(self, input_ids, past_key_values, use_cache, shard, **kwargs) -> BaseModelOutputWithPast:
+        """Sequence-parallel prefill: `input_ids` is the whole (B, S) chunk on every rank; this rank embeds,
+        projects and stores only its block-cyclic stripe of the tokens (S must be a multiple of
+        world * block).  Returns the hidden states of the local stripe, in stripe order."""
+        if input_ids is None:
+            raise ValueError("token-sharded prefill takes input_ids")
+        seq = input_ids.shape[1]
+        if seq % (shard.world * shard.block) != 0:
+            raise ValueError(f"token-sharded prefill needs a multiple of {shard.world * shard.block} tokens, got {seq}")
+        if use_cache and past_key_values is None:
+            past_key_values = DynamicCache(config=self.config)
+        seen = (past_key_values.get_seq_length() if past_key_values is not None else 0) * shard.world
+        rows = shard.owned_rows(seq).to(input_ids.device)
+        hidden = self.embed_tokens(input_ids[:, rows])
+        position_ids = (rows + seen).unsqueeze(0)
+        position_embeddings = self.rotary_emb(hidden, position_ids, max_position=seen + seq - 1, kv_len=None,
+                                              first_position=seen, token_shard=shard)
+        if len(position_embeddings) < 4:
+            raise RuntimeError("token-sharded prefill is implemented for the extended (L > w) path only")
+        for layer in self.layers[: self.config.num_hidden_layers]:
+            hidden = layer(hidden, attention_mask=None, position_embeddings=position_embeddings,
+                           position_ids=position_ids, past_key_values=past_key_values, use_cache=use_cache, **kwargs)
+        hidden = self.norm(hidden)
+        return BaseModelOutputWithPast(last_hidden_state=hidden, past_key_values=past_key_values if use_cache else None)
 
 
 class Qwen3JetLongFusedForCausalLM(Qwen3PreTrainedModel, GenerationMixin):

@@ -48,7 +48,33 @@ def _worker(rank, world, port, results):
         o_1, l_1 = be.fused_jetlong_decode_cache(q1, q1g, kb, v, **dk)
         d_dec, cos_dec = orc.compare(o_sh.float().cpu(), o_1.float().cpu())
         d_lse, _ = orc.compare(l_sh.cpu(), l_1.cpu())
-        results[rank] = (d_pre, cos_pre, d_dec, cos_dec, d_lse)
+        # token-sharded (sequence-parallel) model forward vs the unsharded forward of the same weights
+        import json
+        from transformers.models.qwen3.configuration_qwen3 import Qwen3Config
+        from jetlm.modeling.jetlong_fused import Qwen3JetLongFusedForCausalLM
+        with open(os.path.join(PKG, "model_configs", "Qwen3-1.7B-Base-jetlong_fused", "config.json")) as f:
+            d = json.load(f)
+        d.pop("auto_map"); d.pop("architectures")
+        d.update(dict(num_hidden_layers=2, vocab_size=256, hidden_size=256, intermediate_size=512,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=128, max_window_layers=2))
+        cfg = Qwen3Config(**d)
+        cfg.jetlong["w"], cfg.jetlong["w_0"] = 300, 130
+        cfg._attn_implementation = "sdpa"
+        torch.manual_seed(11)
+        model = Qwen3JetLongFusedForCausalLM(cfg).eval().to("cuda", torch.bfloat16)
+        model.model.rotary_emb.inv_freq = orc.default_inv_freq().cuda()
+        ids = torch.randint(0, 256, (1, 256 * world * 3), device="cuda")
+        with torch.inference_mode():
+            full = model(input_ids=ids).logits.float()
+            shard = SequenceShard(rank, world, block=256)
+            be.configure_sequence_sharding(shard)
+            model.model.token_sharded = True
+            local = model(input_ids=ids).logits.float()
+            be.configure_sequence_sharding(None)
+            model.model.token_sharded = False
+        rows = shard.owned_rows(ids.shape[1]).cuda()
+        d_tok, cos_tok = orc.compare(local.cpu(), full[:, rows].cpu())
+        results[rank] = (d_pre, cos_pre, d_dec, cos_dec, d_lse, d_tok, cos_tok)
     finally:
         dist.destroy_process_group()
 
@@ -62,7 +88,8 @@ def test_sharded_kernels_match_unsharded():
         results = mgr.dict()
         mp.spawn(_worker, args=(world, port, results), nprocs=world, join=True)
         assert len(results) == world
-        for rank, (d_pre, cos_pre, d_dec, cos_dec, d_lse) in results.items():
+        for rank, (d_pre, cos_pre, d_dec, cos_dec, d_lse, d_tok, cos_tok) in results.items():
+            assert cos_tok >= 0.999 and d_tok <= 0.15, (rank, d_tok, cos_tok)     # logits after 2 bf16 layers
             # partials are rounded to bf16 before the merge: one extra rounding step
             assert d_pre <= 2e-2 and cos_pre >= 0.9999, (rank, d_pre, cos_pre)
             assert d_dec <= 2e-2 and cos_dec >= 0.9999 and d_lse <= 1e-3, (rank, d_dec, cos_dec, d_lse)
