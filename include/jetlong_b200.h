@@ -117,8 +117,9 @@ int jl_prefill_status(void);
  * jl_decode — split-KV attention of ONE query token per sequence over up to JL_MAX_SEGMENTS key
  * segments read in place (no slicing, padding or regrouping copies).  Segment s is scored with
  * query operand q[seg[s].q_class].  If seg[s].rotate != 0 the keys of that segment are rotated
- * in-kernel by (floor(p / group_size) - p) * inv_freq, p = seg[s].pos0 + row, i.e. the far class
- * of the jetlong map is formed on the fly from a base-rotated cache.
+ * in-kernel by (floor(p / group_size) - p) * inv_freq, p = seg[s].pos0 + row (or, for a block-cyclic
+ * cache stripe, seg[s].pos0 + (row / pos_block) * pos_block_stride + row % pos_block), i.e. the far
+ * class of the jetlong map is formed on the fly from a base-rotated cache.
  *
  * q[c]: (B, 1, H, D)   seg[s].k / .v: (B, len, Hk, D)   out: (B, 1, H, D)   lse: (B, H) fp32.
  * seg[s].len_dev, if not NULL, is an int32 device array (B,) of per-sequence valid lengths
@@ -135,6 +136,8 @@ typedef struct {
   int32_t q_class;
   int32_t rotate;
   int32_t reserved;
+  int64_t pos_block;        /* <= 0 means contiguous positions; else a multiple of 8 */
+  int64_t pos_block_stride;
 } jl_kv_segment;
 
 typedef struct {

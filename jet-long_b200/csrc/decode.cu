@@ -25,7 +25,7 @@ struct DecSeg {
   const __nv_bfloat16* v;
   int64_t ks_b, ks_s, ks_h, vs_b, vs_s, vs_h;
   const int32_t* len_dev;
-  int64_t pos0;
+  int64_t pos0, pos_block, pos_block_stride;
   int len, q_class, rotate;
 };
 
@@ -178,7 +178,7 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) decode_kernel(const DecPara
       // its rotation partner d + 64 sits in kf[kk + 4][i].
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        const int64_t pos = sg.pos0 + row0 + warp * 16 + half * 8 + (lane >> 2);
+        const int64_t pos = key_position(row0 + warp * 16 + half * 8 + (lane >> 2), sg.pos0, sg.pos_block, sg.pos_block_stride);
         const float tf = static_cast<float>(pos / p.group_size - pos);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
@@ -387,6 +387,9 @@ int launch_decode(const jl_decode_args* a, cudaStream_t stream) {
     d.vs_b = g.v_stride_b; d.vs_s = g.v_stride_s; d.vs_h = g.v_stride_h;
     d.len_dev = g.len_dev;
     d.pos0 = g.pos0;
+    d.pos_block = g.pos_block > 0 ? g.pos_block : 0;
+    d.pos_block_stride = g.pos_block_stride;
+    if (d.pos_block % 8 != 0) return fail(JL_ERR_BAD_ARG, "jl_decode: segment %d pos_block must be a multiple of 8", s);
     d.len = g.len;
     d.q_class = g.q_class;
     d.rotate = g.rotate != 0;

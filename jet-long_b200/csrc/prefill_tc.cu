@@ -445,27 +445,44 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
 
         mbar_wait(&sm.s_full[t], g & 1, sm);
         tc_fence_after();
+        // scores -> registers and row maximum (4 independent chains of 3-input max).  The four 32-column
+        // loads are software-pipelined against the reduction: chunk c+1 is in flight while chunk c is reduced.
         uint32_t s[128];
-        JL_TMEM_LD32(t_s + 0, s, 0);
-        JL_TMEM_LD32(t_s + 32, s, 32);
-        JL_TMEM_LD32(t_s + 64, s, 64);
-        JL_TMEM_LD32(t_s + 96, s, 96);
-        tmem_wait_ld();
-
-        // row maximum: 4 independent chains of 3-input max
         float mx;
-        if (!uniform) {
-          const int64_t lo64 = row_lo - tp0, hi64 = row_hi - tp0 + 1;
-          const int c_lo = lo64 < 0 ? 0 : (lo64 > 128 ? 128 : static_cast<int>(lo64));
-          const int c_hi = hi64 < 0 ? 0 : (hi64 > valid ? valid : static_cast<int>(hi64));
-#pragma unroll
-          for (int i = 0; i < 128; ++i)
-            if (!(i >= c_lo && i < c_hi)) s[i] = 0xff800000u;        // -inf
-        }
         {
           float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+          if (uniform) {
+            JL_TMEM_LD32(t_s + 0, s, 0);
+            tmem_wait_ld();
+            JL_TMEM_LD32(t_s + 32, s, 32);
 #pragma unroll
-          for (int i = 0; i < 64; ++i) m4[i & 3] = max3(m4[i & 3], __uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1]));
+            for (int i = 0; i < 16; ++i) m4[i & 3] = max3(m4[i & 3], __uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1]));
+            tmem_wait_ld();
+            JL_TMEM_LD32(t_s + 64, s, 64);
+#pragma unroll
+            for (int i = 16; i < 32; ++i) m4[i & 3] = max3(m4[i & 3], __uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1]));
+            tmem_wait_ld();
+            JL_TMEM_LD32(t_s + 96, s, 96);
+#pragma unroll
+            for (int i = 32; i < 48; ++i) m4[i & 3] = max3(m4[i & 3], __uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1]));
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 48; i < 64; ++i) m4[i & 3] = max3(m4[i & 3], __uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1]));
+          } else {
+            JL_TMEM_LD32(t_s + 0, s, 0);
+            JL_TMEM_LD32(t_s + 32, s, 32);
+            JL_TMEM_LD32(t_s + 64, s, 64);
+            JL_TMEM_LD32(t_s + 96, s, 96);
+            tmem_wait_ld();
+            const int64_t lo64 = row_lo - tp0, hi64 = row_hi - tp0 + 1;
+            const int c_lo = lo64 < 0 ? 0 : (lo64 > 128 ? 128 : static_cast<int>(lo64));
+            const int c_hi = hi64 < 0 ? 0 : (hi64 > valid ? valid : static_cast<int>(hi64));
+#pragma unroll
+            for (int i = 0; i < 128; ++i)
+              if (!(i >= c_lo && i < c_hi)) s[i] = 0xff800000u;        // -inf
+#pragma unroll
+            for (int i = 0; i < 64; ++i) m4[i & 3] = max3(m4[i & 3], __uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1]));
+          }
           mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
         }
         mx *= p.scale_log2;                                  // scale > 0: max commutes with the scaling

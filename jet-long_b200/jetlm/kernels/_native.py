@@ -46,6 +46,7 @@ class KvSegment(C.Structure):
         ("v_stride_b", C.c_int64), ("v_stride_s", C.c_int64), ("v_stride_h", C.c_int64),
         ("len_dev", C.c_void_p), ("pos0", C.c_int64),
         ("len", C.c_int32), ("q_class", C.c_int32), ("rotate", C.c_int32), ("reserved", C.c_int32),
+        ("pos_block", C.c_int64), ("pos_block_stride", C.c_int64),
     ]
 
 

@@ -154,6 +154,39 @@ def fused_jetlong_decode_cache(query_base, query_group, key_cache, value_cache, 
                          inv_freq, group_size, softmax_scale, return_lse)
 
 
+def fused_jetlong_decode_cache_stripe(query_base, query_group, key_stripe, value_stripe, *, boundary: int, inv_freq,
+                                      group_size: int, softmax_scale=None, return_lse: bool = False):
+    """Decode when every rank holds only its block-cyclic stripe of the base-rotated cache, as the
+    token-sharded prefill leaves it: key_stripe / value_stripe (B,Hk,S_loc,D), local row i at position
+    rank*blk + (i // blk) * world*blk + i % blk.  Local rows below `boundary` are the far class
+    (regrouped in-kernel at their true positions), the rest the near class; partial (O, LSE) pairs
+    are all-gathered and merged, so every rank returns the full (B,1,H,D) result."""
+    sh = _SHARD
+    if sh is None:
+        raise RuntimeError("fused_jetlong_decode_cache_stripe needs configure_sequence_sharding(...) first")
+    kc, vc = key_stripe.transpose(1, 2), value_stripe.transpose(1, 2)
+    n_far = min(sh.n_owned(int(boundary)), kc.shape[1])
+    B, _, H, D = query_base.shape
+
+    def part(out, lse):
+        segs = []
+        if n_far > 0:
+            segs.append(ops.KvSegment(kc[:, :n_far], vc[:, :n_far], q_class=1, rotate=True, pos0=sh.rank * sh.block,
+                                      pos_block=sh.block, pos_block_stride=sh.world * sh.block))
+        if n_far < kc.shape[1]:
+            segs.append(ops.KvSegment(kc[:, n_far:], vc[:, n_far:], q_class=0))
+        if not segs:                       # this rank owns no key yet: an empty partial
+            out.zero_()
+            lse.fill_(float("-inf"))
+            return out, lse
+        return ops.decode_segments([query_base, query_group], segs, inv_freq=inv_freq, group_size=int(group_size),
+                                   softmax_scale=softmax_scale, out=out, lse=lse)
+
+    buf = _partial_buffer(sh, (B, 1, H, D), (B, H, 1), query_base.dtype, query_base.device)
+    out, lse = sharded_attention(part, ops.merge_partials, sh, buf)
+    return (out, lse) if return_lse else out
+
+
 def _decode_range(query_base, query_group, kc, vc, b, pos0, inv_freq, group_size, softmax_scale, return_lse,
                   out=None, lse=None):
     """Decode over rows of a (B,S,Hk,D) cache view whose row 0 has absolute position pos0; rows < b are far."""

@@ -353,6 +353,8 @@ class KvSegment:
     rotate: bool = False       # regroup the keys in-kernel by (floor(p/G) - p) * inv_freq
     pos0: int = 0              # absolute position of row 0 (used when rotate)
     len_dev: Optional[torch.Tensor] = None   # optional int32 (B,) valid lengths
+    pos_block: int = 0         # > 0: rows are a block-cyclic stripe, position = pos0 + (row // pos_block) * stride + row % pos_block
+    pos_block_stride: int = 0
 
 
 def decode_segments(q_ops: Sequence[Optional[torch.Tensor]], segments: Sequence[KvSegment], *,
@@ -417,6 +419,7 @@ def decode_segments(q_ops: Sequence[Optional[torch.Tensor]], segments: Sequence[
             keep.append(s.len_dev.contiguous())
             g.len_dev = keep[-1].data_ptr()
         g.pos0, g.len, g.q_class, g.rotate = int(s.pos0), int(s.k.shape[1]), int(s.q_class), int(bool(s.rotate))
+        g.pos_block, g.pos_block_stride = int(s.pos_block), int(s.pos_block_stride)
         total += int(s.k.shape[1])
     if H % Hk != 0:
         raise ValueError(f"{op}: query heads must be divisible by kv heads")

@@ -44,8 +44,15 @@ def _worker(rank, world, port, results):
         q1, q1g = mk(B, 1, H, D), mk(B, 1, H, D)
         dk = dict(boundary=Skv - 1 - w0, inv_freq=inv, group_size=G, has_any_pad=False, training=False, return_lse=True)
         o_sh, l_sh = be.fused_jetlong_decode_cache(q1, q1g, kb, v, **dk)
+        # the same decode from block-cyclic cache stripes (what the token-sharded prefill leaves behind)
+        sh = SequenceShard(rank, world, block=256)
+        o_st, l_st = be.fused_jetlong_decode_cache_stripe(q1, q1g, sh.take_stripe(kb, dim=2), sh.take_stripe(v, dim=2),
+                                                           boundary=Skv - 1 - w0, inv_freq=inv, group_size=G, return_lse=True)
         be.configure_sequence_sharding(None)
         o_1, l_1 = be.fused_jetlong_decode_cache(q1, q1g, kb, v, **dk)
+        d_st, cos_st = orc.compare(o_st.float().cpu(), o_1.float().cpu())
+        d_lst, _ = orc.compare(l_st.cpu(), l_1.cpu())
+        assert d_st <= 2e-2 and cos_st >= 0.9999 and d_lst <= 1e-3, (rank, d_st, cos_st, d_lst)
         d_dec, cos_dec = orc.compare(o_sh.float().cpu(), o_1.float().cpu())
         d_lse, _ = orc.compare(l_sh.cpu(), l_1.cpu())
         # token-sharded (sequence-parallel) model forward vs the unsharded forward of the same weights
