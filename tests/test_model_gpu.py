@@ -84,3 +84,29 @@ def test_short_context_uses_stock_attention_and_decode_guard(golden):
     model.train()
     with pytest.raises(RuntimeError, match="inference-only"):
         model(input_ids=ids[:, :100])
+
+
+@torch.inference_mode()
+def test_hf_generate_with_chunked_prefill(golden):
+    """HF `generate` drives the model the way the reference's evaluation wrapper does (chunked prefill,
+    then one forward per token): in-window chunk -> extended chunks with a growing cache -> decode
+    steps off the cache.  Greedy tokens must equal a hand-rolled loop over the same model."""
+    from transformers import GenerationConfig
+    g = golden("model_tiny.npz")
+    model = _tiny_model(g)
+    ids = g["input_ids"].cuda()[:, :150]
+    gen_cfg = GenerationConfig(max_new_tokens=4, do_sample=False, prefill_chunk_size=50, disable_compile=True,
+                               pad_token_id=0, eos_token_id=None)
+    out = model.generate(ids, generation_config=gen_cfg)
+    assert out.shape == (1, 154)
+    cache = None
+    for lo in range(0, 150, 50):
+        res = model(input_ids=ids[:, lo:lo + 50], past_key_values=cache, use_cache=True)
+        cache = res.past_key_values
+    toks = []
+    nxt = res.logits[:, -1].argmax(-1, keepdim=True)
+    for _ in range(4):
+        toks.append(int(nxt))
+        res = model(input_ids=nxt, past_key_values=cache, use_cache=True)
+        nxt = res.logits[:, -1].argmax(-1, keepdim=True)
+    assert out[0, 150:].tolist() == toks

@@ -440,3 +440,55 @@ def test_decode_full_context_properties():
     eo, el = orc.jetlong_decode(q[:, :, :4].cpu(), qg[:, :, :4].cpu(), k[:, b:, :1].cpu(), v[:, b:, :1].cpu(),
                                 k[:, :b, :1].cpu(), v[:, :b, :1].cpu())
     _check(o_auto[:, :, :4], l_auto[:, :4], eo, el, "decode 128K spot heads")
+
+
+@pytest.mark.parametrize("kind", ["jetlong", "selfext", "dca"])
+def test_position_maps_at_long_positions(kind):
+    """The three position maps through the same rotate + prefill kernels at positions just below 131072
+    (large RoPE angles), 8 query / 2 kv heads, a key count that is not a tile multiple.  The rotation
+    kernels are checked against the fp32 rotation, the attention kernel against the oracle on the very
+    operands it consumed."""
+    ops = _ops()
+    torch.manual_seed(40)
+    B, S, H, Hk, D = 1, 2304 + 77, 8, 2, 128
+    P0 = 131072 - S
+    inv = orc.default_inv_freq()
+    dinv = inv.cuda()
+    q, k, v = torch.randn(B, S, H, D).bfloat16(), torch.randn(B, S, Hk, D).bfloat16(), torch.randn(B, S, Hk, D).bfloat16()
+    dq, dk, dv = q.cuda(), k.cuda(), v.cuda()
+    pos = torch.arange(S) + P0
+    if kind == "jetlong":
+        G, w0 = 4, 700
+        params, pm = dict(w_0=w0, G=G), ops.PositionMap.jetlong(w0)
+        qb, kb = ops.rope_base(dq, dinv, pos0=P0), ops.rope_base(dk, dinv, pos0=P0)
+        qo = [qb, ops.rope_regroup(qb, dinv, group_size=G, pos0=P0)]
+        ko = [kb, ops.rope_regroup(kb, dinv, group_size=G, pos0=P0)]
+    elif kind == "selfext":
+        Gs, W = 8, 512
+        params, pm = dict(window_size=W, group_size=Gs), ops.PositionMap.selfext(W)
+        qo = [ops.rope_base(dq, dinv, pos0=P0), ops.rope_rotate(dq, dinv, pos0=P0, div=Gs, add=W - W // Gs)]
+        ko = [ops.rope_base(dk, dinv, pos0=P0), ops.rope_rotate(dk, dinv, pos0=P0, div=Gs)]
+    else:
+        s, w = 1024, 128
+        params, pm = dict(chunk_size=s, local_window=w), ops.PositionMap.dca(s)
+        qo = [ops.rope_rotate(dq, dinv, pos0=P0, div_mul=0, mod=s, mod_mul=1),
+              ops.rope_rotate(dq, dinv, pos0=P0, div_mul=0, mod=s, mod_mul=1, add=s, t_max=s + w),
+              ops.rope_rotate(dq, dinv, pos0=P0, div_mul=0, add=s + w)]
+        kr = ops.rope_rotate(dk, dinv, pos0=P0, div_mul=0, mod=s, mod_mul=1)
+        ko = [kr, kr, kr]
+    _, qpos, kpos = orc.posmap_classes(kind, pos, pos, params)
+    if kind == "jetlong":      # operands follow the reference's two-step composition: base, then correction by floor(p/G) - p
+        exp_q = [orc.rotate_bshd(q.float(), pos.view(1, -1), inv)]
+        exp_q.append(orc.rotate_bshd(qo[0].float().cpu(), orc.regroup_delta(pos.view(1, -1), params["G"]), inv))
+        for got, exp in zip(qo, exp_q):
+            d, cos = orc.compare(got.float().cpu(), exp)
+            assert d <= 2 ** -5 and cos > 0.99999, (kind, d, cos)
+    else:
+        for got, pp in zip(qo, qpos):
+            d, cos = orc.compare(got.float().cpu(), orc.rotate_bshd(q.float(), pp.view(1, -1), inv))
+            assert d <= 2 ** -5 and cos > 0.99999, (kind, d, cos)
+    eo, el = orc.posmap_attention_from_operands(kind, [t.cpu() for t in qo], [t.cpu() for t in ko], v,
+                                                q_positions=pos, k_positions=pos, params=params)
+    for impl in (0, 1):
+        out, lse = ops.posmap_prefill(qo, ko, dv, pmap=pm, q_pos0=P0, k_pos0=P0, impl=impl)
+        _check(out, lse, eo, el, f"{kind} at positions ~131072, impl={impl}")
