@@ -108,9 +108,10 @@ typedef struct {
 } jl_prefill_args;
 
 int jl_prefill(const jl_prefill_args* args, void* cuda_stream);
-/* Diagnostic (synchronises the device): 0 if no bounded wait inside the prefill kernel has ever given
- * up on the current device, non-zero otherwise.  A kernel whose wait gives up drains and returns
- * instead of hanging; its output is then invalid.  No reference counterpart. */
+/* Diagnostic (synchronises the device): 0 if no bounded wait inside the prefill kernel has given up on
+ * the current device since the last call, non-zero otherwise (reading a raised status clears it).
+ * A kernel whose wait gives up (1 s) drains and returns instead of hanging; its output, and that of
+ * every prefill launched before the status is read, is invalid.  No reference counterpart. */
 int jl_prefill_status(void);
 
 /* ---------------------------------------------------------------------------------------------

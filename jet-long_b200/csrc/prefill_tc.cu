@@ -90,11 +90,11 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait.  A wait that has not been satisfied after kWaitLimitNs gives up and raises the CTA's
+// Bounded wait.  A wait that has not been satisfied after kWaitLimitNs (1 s) gives up and raises the CTA's
 // `failed` flag; from then on every wait of the CTA returns at once, so the kernel drains instead of
 // hanging (its output is then invalid and the status word tells the host).  CTAs that start after
 // the device status word has been raised skip their waits from the beginning.
-constexpr uint64_t kWaitLimitNs = 20ull * 1000 * 1000;
+constexpr uint64_t kWaitLimitNs = 1000ull * 1000 * 1000;      // 1 s: far beyond any legitimate wait, even on a time-sliced GPU
 __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, Smem& sm) {
   if (mbar_try_wait(bar, parity)) return;
   volatile int* failed = reinterpret_cast<volatile int*>(&sm.failed);
@@ -652,7 +652,10 @@ static int* status_word() {
 int prefill_tc_status() {
   int* w = status_word();
   int v = 0;
-  if (w != nullptr && cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) v = -1;
+  if (w != nullptr) {
+    if (cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (v != 0) cudaMemset(w, 0, sizeof(int));      // reading a raised status clears it, so later launches run again
+  }
   return v;
 }
 

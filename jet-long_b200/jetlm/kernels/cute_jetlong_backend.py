@@ -70,19 +70,51 @@ def fused_jetlong_prefill_token_sharded(query_base, key_base, key_group, value, 
             recv_o=torch.empty(N, B, S_loc, H, D, dtype=dt, device=dev),
             recv_l=torch.empty(N, B, H, S_loc, dtype=torch.float32, device=dev))
     q_all, q_grp = bufs["q_all"], bufs["q_grp"]
-    dist.all_gather_into_tensor(q_all.view(-1), query_base.contiguous().view(-1), group=sh.group)
+    send_o, send_l, recv_o, recv_l = bufs["send_o"], bufs["send_l"], bufs["recv_o"], bufs["recv_l"]
     pmap = ops.PositionMap.jetlong(int(window_size_left))
     stride = N * blk
-    for r in range(N):
-        qb = q_all[r]
+    me = sh.rank
+
+    def attend(qb, r, out, lse):
+        """Queries of rank r's stripe (base-rotated, (B,S_loc,H,D)) against the local key stripe."""
         ops.rope_regroup(qb, inv_freq, group_size=int(group_size), pos0=int(q_start) + r * blk, pos_block=blk,
                          pos_block_stride=stride, out=q_grp)
         ops.posmap_prefill([qb, q_grp], [key_base, key_group], value, pmap=pmap,
                            q_pos0=int(q_start) + r * blk, q_block=blk, q_block_stride=stride,
-                           k_pos0=sh.rank * blk, k_block=blk, k_block_stride=stride, softmax_scale=softmax_scale,
-                           out=bufs["send_o"][r], lse=bufs["send_l"][r])
-    dist.all_to_all_single(bufs["recv_o"].view(-1), bufs["send_o"].view(-1), group=sh.group)
-    dist.all_to_all_single(bufs["recv_l"].view(-1), bufs["send_l"].view(-1), group=sh.group)
+                           k_pos0=me * blk, k_block=blk, k_block_stride=stride, softmax_scale=softmax_scale,
+                           out=out, lse=lse)
+
+    def exchange(dests, async_op):
+        """Send the partials of the query stripes owned by `dests`; receive my rows' partials from the
+        ranks for which I am in the same phase (dest = source + k  <=>  source = dest - k)."""
+        ks = [(d - me) % N for d in dests]
+        srcs = {(me - k) % N for k in ks}
+        e_o, e_l = send_o.new_empty(0), send_l.new_empty(0)
+        works = []
+        works.append(dist.all_to_all([recv_o[s].view(-1) if s in srcs else e_o for s in range(N)],
+                                     [send_o[d].view(-1) if d in dests else e_o for d in range(N)],
+                                     group=sh.group, async_op=async_op))
+        works.append(dist.all_to_all([recv_l[s].view(-1) if s in srcs else e_l for s in range(N)],
+                                     [send_l[d].view(-1) if d in dests else e_l for d in range(N)],
+                                     group=sh.group, async_op=async_op))
+        return works
+
+    # 1. the query all-gather runs behind the attention of my own stripe (which needs no remote data)
+    gather = dist.all_gather_into_tensor(q_all.view(-1), query_base.contiguous().view(-1), group=sh.group, async_op=True)
+    attend(query_base, me, recv_o[me], recv_l[me])
+    gather.wait()
+    # 2. the other stripes in two phases; the first phase's partials travel while the second is computed
+    order = [(me + k) % N for k in range(1, N)]
+    first, second = order[: (N - 1 + 1) // 2], order[(N - 1 + 1) // 2:]
+    for r in first:
+        attend(q_all[r], r, send_o[r], send_l[r])
+    pending = exchange(set(first), async_op=bool(second))
+    for r in second:
+        attend(q_all[r], r, send_o[r], send_l[r])
+    if second:
+        for w in pending:
+            w.wait()
+        exchange(set(second), async_op=False)
     out = ops.merge_partials(list(bufs["recv_o"].unbind(0)), list(bufs["recv_l"].unbind(0)), return_lse=False)
     return out
 

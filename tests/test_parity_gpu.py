@@ -492,3 +492,10 @@ def test_position_maps_at_long_positions(kind):
     for impl in (0, 1):
         out, lse = ops.posmap_prefill(qo, ko, dv, pmap=pm, q_pos0=P0, k_pos0=P0, impl=impl)
         _check(out, lse, eo, el, f"{kind} at positions ~131072, impl={impl}")
+
+
+def test_prefill_status_word_is_clean():
+    """No bounded wait inside the tcgen05 kernel gave up during the tests above."""
+    from jetlm.kernels import _native
+    torch.cuda.synchronize()
+    assert _native.lib().jl_prefill_status() == 0
