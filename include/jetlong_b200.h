@@ -236,6 +236,33 @@ typedef struct {
 
 int jl_rotate(const jl_rotate_args* args, void* cuda_stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * jl_norm_rope — per-head RMSNorm, base RoPE and (optionally) the jetlong regroup of a projection
+ * output in ONE pass: replaces q_norm / k_norm (Qwen3RMSNorm: fp32 statistics, normalised value
+ * rounded to bf16, then multiplied by the bf16 weight), apply_rotary_pos_emb and
+ * correction_rotate_per_sample (modeling_qwen3_jetlong_fused.py:292-294, :171-176, :209-226).
+ *   y          = weight * bf16(x * rsqrt(mean(x^2) + eps))            (Qwen3RMSNorm's roundings)
+ *   out_base   = R(p) y                                               p from pos0 / pos_block / pos_block_stride
+ *   out_group  = R(floor(p / group_size) - p) R(p) y                  (fp32 composition, one rounding; may be NULL)
+ * x, out_base, out_group: (B, S, Hx, D) with element strides; out_base may point into a KV cache.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* x;
+  const void* weight;       /* (head_dim,) bf16 */
+  void* out_base;
+  void* out_group;          /* may be NULL */
+  int64_t x_stride_b, x_stride_s, x_stride_h;
+  int64_t b_stride_b, b_stride_s, b_stride_h;
+  int64_t g_stride_b, g_stride_s, g_stride_h;
+  int32_t batch, seqlen, heads, head_dim;
+  float eps;
+  int32_t group_size;
+  int64_t pos0, pos_block, pos_block_stride;
+  const float* inv_freq;    /* (head_dim/2,) fp32 device array */
+} jl_norm_rope_args;
+
+int jl_norm_rope(const jl_norm_rope_args* args, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

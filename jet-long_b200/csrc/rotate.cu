@@ -86,4 +86,103 @@ int launch_rotate(const jl_rotate_args* a, cudaStream_t stream) {
   return check_launch("jl_rotate");
 }
 
+// ---------------------------------------------------------------------------------------------
+// RMSNorm + base RoPE (+ regroup) of a projection output, one pass.  One warp per token row, looping
+// over the heads: lane l owns dims 2l, 2l+1 and their rotation partners 64+2l, 64+2l+1, so the four
+// sincos of the row (base angle and regroup angle for two frequencies) are computed once and reused
+// by every head, each half-row load is one coalesced 128-byte request, and the RMS statistic is a
+// five-step warp reduction.
+// ---------------------------------------------------------------------------------------------
+struct NormRopeParams {
+  const __nv_bfloat16* x;
+  const __nv_bfloat16* w;
+  __nv_bfloat16* ob;
+  __nv_bfloat16* og;
+  int64_t xs_b, xs_s, xs_h, bs_b, bs_s, bs_h, gs_b, gs_s, gs_h;
+  int batch, seqlen, heads, group_size;
+  float eps;
+  int64_t pos0, pos_block, pos_block_stride;
+  const float* inv_freq;
+};
+
+__global__ void __launch_bounds__(256) norm_rope_kernel(const NormRopeParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t rows = static_cast<int64_t>(p.batch) * p.seqlen;
+  const float f0 = p.inv_freq[2 * lane], f1 = p.inv_freq[2 * lane + 1];
+  const float2 w_lo = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(p.w + 2 * lane));
+  const float2 w_hi = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(p.w + 64 + 2 * lane));
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows;
+       row += static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5)) {
+    const int64_t s = row % p.seqlen, b = row / p.seqlen;
+    const int64_t pos = key_position(s, p.pos0, p.pos_block, p.pos_block_stride);
+    const float tb = static_cast<float>(pos), td = static_cast<float>(pos / p.group_size - pos);
+    float sb0, cb0, sb1, cb1, sd0 = 0.f, cd0 = 1.f, sd1 = 0.f, cd1 = 1.f;
+    sincosf(__fmul_rn(tb, f0), &sb0, &cb0);
+    sincosf(__fmul_rn(tb, f1), &sb1, &cb1);
+    if (p.og != nullptr) {
+      sincosf(__fmul_rn(td, f0), &sd0, &cd0);
+      sincosf(__fmul_rn(td, f1), &sd1, &cd1);
+    }
+    const __nv_bfloat16* xr = p.x + b * p.xs_b + s * p.xs_s;
+    __nv_bfloat16* br = p.ob + b * p.bs_b + s * p.bs_s;
+    __nv_bfloat16* gr = p.og != nullptr ? p.og + b * p.gs_b + s * p.gs_s : nullptr;
+    for (int h = 0; h < p.heads; ++h) {
+      const float2 lo = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(xr + h * p.xs_h + 2 * lane));
+      const float2 hi = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(xr + h * p.xs_h + 64 + 2 * lane));
+      float ss = lo.x * lo.x + lo.y * lo.y + hi.x * hi.x + hi.y * hi.y;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+      const float r = rsqrtf(ss * (1.f / kHeadDim) + p.eps);
+      // Qwen3RMSNorm: the normalised value is rounded to bf16 before the (bf16) weight multiply
+      auto rb = [](float v) { return __bfloat162float(__float2bfloat16(v)); };
+      const float y0 = rb(w_lo.x * rb(lo.x * r)), y1 = rb(w_lo.y * rb(lo.y * r));
+      const float z0 = rb(w_hi.x * rb(hi.x * r)), z1 = rb(w_hi.y * rb(hi.y * r));
+      const float bl0 = y0 * cb0 - z0 * sb0, bl1 = y1 * cb1 - z1 * sb1;      // base-rotated, fp32
+      const float bh0 = z0 * cb0 + y0 * sb0, bh1 = z1 * cb1 + y1 * sb1;
+      *reinterpret_cast<uint32_t*>(br + h * p.bs_h + 2 * lane) = pack_bf16x2(bl0, bl1);
+      *reinterpret_cast<uint32_t*>(br + h * p.bs_h + 64 + 2 * lane) = pack_bf16x2(bh0, bh1);
+      if (gr != nullptr) {
+        *reinterpret_cast<uint32_t*>(gr + h * p.gs_h + 2 * lane) = pack_bf16x2(bl0 * cd0 - bh0 * sd0, bl1 * cd1 - bh1 * sd1);
+        *reinterpret_cast<uint32_t*>(gr + h * p.gs_h + 64 + 2 * lane) = pack_bf16x2(bh0 * cd0 + bl0 * sd0, bh1 * cd1 + bl1 * sd1);
+      }
+    }
+  }
+}
+
+int launch_norm_rope(const jl_norm_rope_args* a, cudaStream_t stream) {
+  if (a->head_dim != kHeadDim) return fail(JL_ERR_UNSUPPORTED, "jl_norm_rope: head_dim must be 128, got %d", a->head_dim);
+  if (a->x == nullptr || a->weight == nullptr || a->out_base == nullptr || a->inv_freq == nullptr)
+    return fail(JL_ERR_BAD_ARG, "jl_norm_rope: NULL pointer");
+  if (a->batch < 0 || a->seqlen < 0 || a->heads < 0) return fail(JL_ERR_BAD_ARG, "jl_norm_rope: negative size");
+  if (a->out_group != nullptr && a->group_size < 1) return fail(JL_ERR_BAD_ARG, "jl_norm_rope: group_size must be >= 1");
+  const int64_t st[] = {a->x_stride_b, a->x_stride_s, a->x_stride_h, a->b_stride_b, a->b_stride_s, a->b_stride_h,
+                        a->g_stride_b, a->g_stride_s, a->g_stride_h};
+  for (int64_t v : st)
+    if (v % 2 != 0) return fail(JL_ERR_BAD_ARG, "jl_norm_rope: strides must be even (4-byte aligned rows)");
+  if ((reinterpret_cast<uintptr_t>(a->x) | reinterpret_cast<uintptr_t>(a->weight) | reinterpret_cast<uintptr_t>(a->out_base) |
+       reinterpret_cast<uintptr_t>(a->out_group)) & 3)
+    return fail(JL_ERR_BAD_ARG, "jl_norm_rope: pointers must be 4-byte aligned");
+  NormRopeParams p{};
+  p.x = static_cast<const __nv_bfloat16*>(a->x);
+  p.w = static_cast<const __nv_bfloat16*>(a->weight);
+  p.ob = static_cast<__nv_bfloat16*>(a->out_base);
+  p.og = static_cast<__nv_bfloat16*>(a->out_group);
+  p.xs_b = a->x_stride_b; p.xs_s = a->x_stride_s; p.xs_h = a->x_stride_h;
+  p.bs_b = a->b_stride_b; p.bs_s = a->b_stride_s; p.bs_h = a->b_stride_h;
+  p.gs_b = a->g_stride_b; p.gs_s = a->g_stride_s; p.gs_h = a->g_stride_h;
+  p.batch = a->batch; p.seqlen = a->seqlen; p.heads = a->heads;
+  p.group_size = a->group_size > 0 ? a->group_size : 1;
+  p.eps = a->eps;
+  p.pos0 = a->pos0;
+  p.pos_block = (a->pos_block > 0 && a->pos_block < a->seqlen) ? a->pos_block : 0;
+  p.pos_block_stride = a->pos_block_stride;
+  p.inv_freq = a->inv_freq;
+  const int64_t rows = static_cast<int64_t>(a->batch) * a->seqlen;
+  if (rows == 0 || a->heads == 0) return JL_OK;
+  const int64_t blocks = (rows + 7) / 8;
+  const int grid = static_cast<int>(blocks < 148 * 8 ? blocks : 148 * 8);
+  norm_rope_kernel<<<grid, 256, 0, stream>>>(p);
+  return check_launch("jl_norm_rope");
+}
+
 }  // namespace jl

@@ -82,6 +82,18 @@ class RotateArgs(C.Structure):
     ]
 
 
+class NormRopeArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("weight", C.c_void_p), ("out_base", C.c_void_p), ("out_group", C.c_void_p),
+        ("x_stride_b", C.c_int64), ("x_stride_s", C.c_int64), ("x_stride_h", C.c_int64),
+        ("b_stride_b", C.c_int64), ("b_stride_s", C.c_int64), ("b_stride_h", C.c_int64),
+        ("g_stride_b", C.c_int64), ("g_stride_s", C.c_int64), ("g_stride_h", C.c_int64),
+        ("batch", C.c_int32), ("seqlen", C.c_int32), ("heads", C.c_int32), ("head_dim", C.c_int32),
+        ("eps", C.c_float), ("group_size", C.c_int32),
+        ("pos0", C.c_int64), ("pos_block", C.c_int64), ("pos_block_stride", C.c_int64), ("inv_freq", C.c_void_p),
+    ]
+
+
 # Every symbol include/jetlong_b200.h declares: (name, restype, argtypes)
 EXPORTS = [
     ("jl_version", C.c_int, []),
@@ -96,6 +108,7 @@ EXPORTS = [
     ("jl_decode_static_scratch_bytes", C.c_size_t, []),
     ("jl_merge", C.c_int, [C.POINTER(MergeArgs), C.c_void_p]),
     ("jl_rotate", C.c_int, [C.POINTER(RotateArgs), C.c_void_p]),
+    ("jl_norm_rope", C.c_int, [C.POINTER(NormRopeArgs), C.c_void_p]),
 ]
 
 _LIB = None

@@ -62,8 +62,8 @@ def _st(t: torch.Tensor, i: int) -> int:
 
 # Instrumentation used by the benchmark: kernel launches issued through this module, and (when a list
 # is installed with set_event_sink) a CUDA event pair around every attention kernel launch.
-LAUNCHES = {"jl_prefill": 0, "jl_decode": 0, "jl_merge": 0, "jl_rotate": 0}
-KERNELS_PER_CALL = {"jl_prefill": 1, "jl_decode": 2, "jl_merge": 1, "jl_rotate": 1}
+LAUNCHES = {"jl_prefill": 0, "jl_decode": 0, "jl_merge": 0, "jl_rotate": 0, "jl_norm_rope": 0}
+KERNELS_PER_CALL = {"jl_prefill": 1, "jl_decode": 2, "jl_merge": 1, "jl_rotate": 1, "jl_norm_rope": 1}
 _EVENT_SINK: Optional[list] = None
 
 
@@ -171,6 +171,39 @@ def rope_regroup(x_base, inv_freq, *, group_size: int, pos0=0, pos_block=0, pos_
     """jetlong far-class operand from a base-rotated tensor: extra rotation by floor(p/G) - p."""
     return rope_rotate(x_base, inv_freq, pos0=pos0, div=int(group_size), div_mul=1, mod=_BIG, mod_mul=-1,
                        pos_block=pos_block, pos_block_stride=pos_block_stride, out=out)
+
+
+def norm_rope(x: torch.Tensor, weight: torch.Tensor, inv_freq: torch.Tensor, *, eps: float, pos0: int = 0,
+              group_size: Optional[int] = None, pos_block: int = 0, pos_block_stride: int = 0,
+              out_base: Optional[torch.Tensor] = None, out_group: Optional[torch.Tensor] = None):
+    """Per-head RMSNorm (Qwen3RMSNorm roundings) + base RoPE of a (B,S,H,D) projection output in one
+    pass; with group_size also the jetlong-regrouped operand.  Returns out_base or (out_base, out_group)."""
+    op = "norm_rope"
+    _check_view(op, "x", x)
+    if x.dtype not in _SUPPORTED_DTYPES or weight.dtype != x.dtype:
+        raise ValueError(f"{op}: x and weight must be torch.bfloat16")
+    _require_arch(op, x.device)
+    B, S, H, D = x.shape
+    if weight.numel() != D or not weight.is_contiguous():
+        raise ValueError(f"{op}: weight must be a contiguous ({D},) tensor")
+    if out_base is None:
+        out_base = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    want_group = group_size is not None
+    if want_group and out_group is None:
+        out_group = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    for name, t in (("out_base", out_base),) + ((("out_group", out_group),) if want_group else ()):
+        _check_view(op, name, t)
+        if t.shape != x.shape:
+            raise ValueError(f"{op}: {name} must have shape {tuple(x.shape)}")
+    inv_freq = inv_freq.to(device=x.device, dtype=torch.float32).contiguous()
+    a = N.NormRopeArgs(x.data_ptr(), weight.data_ptr(), out_base.data_ptr(), out_group.data_ptr() if want_group else None,
+                       _st(x, 0), _st(x, 1), _st(x, 2), _st(out_base, 0), _st(out_base, 1), _st(out_base, 2),
+                       *((_st(out_group, 0), _st(out_group, 1), _st(out_group, 2)) if want_group else (0, 0, 0)),
+                       B, S, H, D, float(eps), int(group_size) if want_group else 1,
+                       int(pos0), int(pos_block), int(pos_block_stride), inv_freq.data_ptr())
+    with torch.cuda.device(x.device):
+        _timed_call("jl_norm_rope", lambda: N.lib().jl_norm_rope(C.byref(a), _stream()))
+    return (out_base, out_group) if want_group else out_base
 
 
 # ----------------------------------------------------------------------------------------------

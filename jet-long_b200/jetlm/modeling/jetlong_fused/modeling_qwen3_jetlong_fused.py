@@ -144,12 +144,13 @@ class Qwen3JetLongFusedAttention(nn.Module):
         bsz, seq = hidden_states.shape[:2]
         out_shape = (bsz, seq)
         H, Hk, D = self.num_heads, self.num_kv_heads, self.head_dim
-        q = self.q_norm(self.q_proj(hidden_states).view(bsz, seq, H, D))
-        k = self.k_norm(self.k_proj(hidden_states).view(bsz, seq, Hk, D))
+        q = self.q_proj(hidden_states).view(bsz, seq, H, D)          # per-head RMSNorm is applied below
+        k = self.k_proj(hidden_states).view(bsz, seq, Hk, D)
         v = self.v_proj(hidden_states).view(bsz, seq, Hk, D)
 
         if len(position_embeddings) < 4:
-            return self._within_window(q, k, v, position_embeddings, attention_mask, past_key_values, out_shape, **kwargs)
+            return self._within_window(self.q_norm(q), self.k_norm(k), v, position_embeddings, attention_mask,
+                                       past_key_values, out_shape, **kwargs)
 
         # ---- extended (bifocal) paths -------------------------------------------------------------
         from jetlm.kernels import cute_jetlong_backend as backend      # resolved per call: the plugin seam
@@ -164,26 +165,34 @@ class Qwen3JetLongFusedAttention(nn.Module):
         if self.training:
             raise RuntimeError("JetLong backend 'fused' is inference-only")
         w_0 = self.jetlong_w_0
+        q_eps, k_eps = self.q_norm.variance_epsilon, self.k_norm.variance_epsilon
 
         if plan.token_shard is not None:
             return self._token_sharded_prefill(q, k, v, plan, group, inv_freq, past_key_values, out_shape, backend, ops)
 
-        # base RoPE in one fused pass each; K is written straight into (B, Hk, S, D) cache layout
-        q_base = ops.rope_base(q, inv_freq, pos0=plan.q_pos0)
+        # q/k RMSNorm + base RoPE (+ regroup) in one fused pass each; K lands straight in (B, Hk, S, D) cache layout
+        fresh = past_key_values is None or past_key_values.get_seq_length(self.layer_idx) == 0
+        q_base, q_group = ops.norm_rope(q, self.q_norm.weight, inv_freq, eps=q_eps, pos0=plan.q_pos0, group_size=group)
         k_new = torch.empty(bsz, Hk, seq, D, dtype=k.dtype, device=k.device)
-        ops.rope_base(k, inv_freq, pos0=plan.q_pos0, out=k_new.transpose(1, 2))
+        k_group = None
+        if fresh and seq > 1:        # no older keys: the regrouped keys of this call are all there is
+            k_group = torch.empty(bsz, Hk, seq, D, dtype=k.dtype, device=k.device)
+            ops.norm_rope(k, self.k_norm.weight, inv_freq, eps=k_eps, pos0=plan.q_pos0, group_size=group,
+                          out_base=k_new.transpose(1, 2), out_group=k_group.transpose(1, 2))
+        else:
+            ops.norm_rope(k, self.k_norm.weight, inv_freq, eps=k_eps, pos0=plan.q_pos0, out_base=k_new.transpose(1, 2))
         v_new = v.transpose(1, 2)
         if past_key_values is not None:
             k_all, v_all = past_key_values.update(k_new, v_new, self.layer_idx, {})
         else:
             k_all, v_all = k_new, v_new
         kv_len = k_all.shape[2]
-        q_group = ops.rope_regroup(q_base, inv_freq, group_size=group, pos0=plan.q_pos0)
 
         if seq > 1:
             # prefill / chunked prefill: regroup every cached key once for this call's G, then one kernel
-            k_group = torch.empty(bsz, Hk, kv_len, D, dtype=k_all.dtype, device=k_all.device)
-            ops.rope_regroup(k_all.transpose(1, 2), inv_freq, group_size=group, pos0=0, out=k_group.transpose(1, 2))
+            if k_group is None:      # chunked prefill: regroup every cached key for this call's G
+                k_group = torch.empty(bsz, Hk, kv_len, D, dtype=k_all.dtype, device=k_all.device)
+                ops.rope_regroup(k_all.transpose(1, 2), inv_freq, group_size=group, pos0=0, out=k_group.transpose(1, 2))
             if k_all.stride() != k_group.stride():           # a cache that hands out non-dense views
                 k_all = k_all.contiguous()
             attn = backend.fused_jetlong_prefill(
@@ -209,9 +218,11 @@ class Qwen3JetLongFusedAttention(nn.Module):
         bsz, seq = out_shape
         Hk, D = self.num_kv_heads, self.head_dim
         geo = dict(pos_block=sh.block, pos_block_stride=sh.world * sh.block)
-        q_base = ops.rope_base(q, inv_freq, pos0=plan.q_pos0 + sh.rank * sh.block, **geo)
+        pos0 = plan.q_pos0 + sh.rank * sh.block
+        q_base = ops.norm_rope(q, self.q_norm.weight, inv_freq, eps=self.q_norm.variance_epsilon, pos0=pos0, **geo)
         k_new = torch.empty(bsz, Hk, seq, D, dtype=k.dtype, device=k.device)
-        ops.rope_base(k, inv_freq, pos0=plan.q_pos0 + sh.rank * sh.block, out=k_new.transpose(1, 2), **geo)
+        ops.norm_rope(k, self.k_norm.weight, inv_freq, eps=self.k_norm.variance_epsilon, pos0=pos0,
+                      out_base=k_new.transpose(1, 2), **geo)
         if past_key_values is not None:
             k_all, v_all = past_key_values.update(k_new, v.transpose(1, 2), self.layer_idx, {})
         else:

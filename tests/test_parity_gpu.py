@@ -117,6 +117,42 @@ def test_rotate_strided_into_cache():
     assert torch.all(cache[:, :, :7] == 0) and torch.all(cache[:, :, 57:] == 0)
 
 
+def test_norm_rope_fused_pass():
+    """RMSNorm + base RoPE + regroup in one kernel == Qwen3RMSNorm (its bf16 roundings) followed by the
+    oracle's fp32 rotations; strided output straight into a (B,Hk,S,D) cache, block-cyclic positions."""
+    from transformers.models.qwen3.modeling_qwen3 import Qwen3RMSNorm
+    ops = _ops()
+    torch.manual_seed(17)
+    B, S, H, D, G, p0 = 2, 300, 6, 128, 4, 100000
+    inv = orc.default_inv_freq()
+    x = (torch.randn(B, S, H, D) * 3).bfloat16()
+    norm = Qwen3RMSNorm(D, eps=1e-6)
+    norm.weight.data = (1 + 0.2 * torch.randn(D)).bfloat16().float()
+    y = norm.bfloat16()(x)                                      # HF arithmetic on CPU, bf16 in / bf16 out
+    pos = (torch.arange(S) + p0).view(1, S).expand(B, -1)
+    eb = orc.rotate_bshd(y.float(), pos, inv)
+    eg = orc.rotate_bshd(eb, orc.regroup_delta(pos, G), inv)
+    base, grp = ops.norm_rope(x.cuda(), norm.weight.data.bfloat16().cuda(), inv.cuda(), eps=1e-6, pos0=p0, group_size=G)
+    for got, exp in ((base, eb), (grp, eg)):
+        d, cos = orc.compare(got.float().cpu(), exp)
+        assert d <= 2 ** -4 and cos > 0.99998, (d, cos)          # |y| up to ~8: one bf16 ulp there is 2^-5
+    cache = torch.zeros(B, H, S + 9, D, dtype=torch.bfloat16, device="cuda")
+    ops.norm_rope(x.cuda(), norm.weight.data.bfloat16().cuda(), inv.cuda(), eps=1e-6, pos0=p0,
+                  out_base=cache.transpose(1, 2)[:, 4:4 + S])
+    assert torch.equal(cache.transpose(1, 2)[:, 4:4 + S], base) and torch.all(cache[:, :, :4] == 0)
+    # block-cyclic stripe positions: rows of rank 1 of 2 with block 128
+    Sb = 256
+    rows = torch.cat([torch.arange(128, 256), torch.arange(384, 512)])
+    xs = x[:, :Sb]
+    ys = y[:, :Sb]
+    posb = (rows + p0).view(1, -1).expand(B, -1)
+    exp = orc.rotate_bshd(ys.float(), posb, inv)
+    got = ops.norm_rope(xs.cuda().contiguous(), norm.weight.data.bfloat16().cuda(), inv.cuda(), eps=1e-6, pos0=p0 + 128,
+                        pos_block=128, pos_block_stride=256)
+    d, cos = orc.compare(got.float().cpu(), exp)
+    assert d <= 2 ** -4 and cos > 0.99998, (d, cos)
+
+
 # ------------------------------------------------------------------------------------------------
 # prefill
 # ------------------------------------------------------------------------------------------------
