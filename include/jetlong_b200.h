@@ -263,6 +263,27 @@ typedef struct {
 
 int jl_norm_rope(const jl_norm_rope_args* args, void* cuda_stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * jl_rmsnorm — Qwen3RMSNorm over the hidden dimension in one pass, optionally fused with the residual
+ * add that precedes it in the decoder layer (transformers' Qwen3DecoderLayer, which the reference's
+ * modeling file inherits at modeling_qwen3_jetlong_fused.py:468-471):
+ *   h   = x (+ residual)                       (bf16; written to sum_out when residual != NULL)
+ *   out = weight * bf16(h * rsqrt(mean(h^2) + eps))
+ * x, residual, sum_out, out: (rows, hidden) contiguous bf16; hidden a multiple of 8 and <= 8192.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* x;
+  const void* residual;     /* may be NULL */
+  const void* weight;       /* (hidden,) bf16 */
+  void* sum_out;            /* required when residual != NULL; may alias residual or x */
+  void* out;
+  int64_t rows;
+  int32_t hidden;
+  float eps;
+} jl_rmsnorm_args;
+
+int jl_rmsnorm(const jl_rmsnorm_args* args, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -9,6 +9,7 @@ namespace jl {
 int launch_merge(const jl_merge_args* a, cudaStream_t stream);
 int launch_rotate(const jl_rotate_args* a, cudaStream_t stream);
 int launch_norm_rope(const jl_norm_rope_args* a, cudaStream_t stream);
+int launch_rmsnorm(const jl_rmsnorm_args* a, cudaStream_t stream);
 int launch_decode(const jl_decode_args* a, cudaStream_t stream);
 int launch_decode_static(const jl_decode_args* a, cudaStream_t stream);
 size_t decode_static_scratch_bytes();
@@ -114,6 +115,13 @@ int jl_rotate(const jl_rotate_args* args, void* cuda_stream) {
   int rc = jl::check_device_arch();
   if (rc != JL_OK) return rc;
   return jl::launch_rotate(args, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int jl_rmsnorm(const jl_rmsnorm_args* args, void* cuda_stream) {
+  if (args == nullptr) return jl::fail(JL_ERR_BAD_ARG, "jl_rmsnorm: args is NULL");
+  int rc = jl::check_device_arch();
+  if (rc != JL_OK) return rc;
+  return jl::launch_rmsnorm(args, static_cast<cudaStream_t>(cuda_stream));
 }
 
 int jl_norm_rope(const jl_norm_rope_args* args, void* cuda_stream) {

@@ -185,4 +185,106 @@ int launch_norm_rope(const jl_norm_rope_args* a, cudaStream_t stream) {
   return check_launch("jl_norm_rope");
 }
 
+// ---------------------------------------------------------------------------------------------
+// RMSNorm over the hidden dimension (+ fused residual add): one CTA of 256 threads per row at a time,
+// the row lives in registers (up to four 16-byte vectors per thread), one block reduction.
+// ---------------------------------------------------------------------------------------------
+struct RmsParams {
+  const uint4* x;
+  const uint4* res;
+  const uint4* w;
+  uint4* sum_out;
+  uint4* out;
+  int64_t rows;
+  int n_vec;        // hidden / 8
+  float inv_hidden, eps;
+};
+
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const RmsParams p) {
+  __shared__ float s_part[8];
+  const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+  uint4 wv[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    if (t + i * 256 < p.n_vec) wv[i] = p.w[t + i * 256];
+  for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
+    uint4 v[4];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = t + i * 256;
+      if (c < p.n_vec) {
+        v[i] = p.x[row * p.n_vec + c];
+        uint32_t* u = reinterpret_cast<uint32_t*>(&v[i]);
+        if (p.res != nullptr) {
+          const uint4 r = p.res[row * p.n_vec + c];
+          const uint32_t* ur = reinterpret_cast<const uint32_t*>(&r);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 a = unpack_bf16x2(u[j]), b = unpack_bf16x2(ur[j]);
+            u[j] = pack_bf16x2(a.x + b.x, a.y + b.y);
+          }
+          p.sum_out[row * p.n_vec + c] = v[i];
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 a = unpack_bf16x2(u[j]);
+          ss = fmaf(a.x, a.x, fmaf(a.y, a.y, ss));
+        }
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    if (lane == 0) s_part[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += s_part[i];
+    __syncthreads();
+    const float r = rsqrtf(tot * p.inv_hidden + p.eps);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = t + i * 256;
+      if (c < p.n_vec) {
+        const uint32_t* u = reinterpret_cast<const uint32_t*>(&v[i]);
+        const uint32_t* uw = reinterpret_cast<const uint32_t*>(&wv[i]);
+        uint4 o;
+        uint32_t* uo = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 a = unpack_bf16x2(u[j]), w2 = unpack_bf16x2(uw[j]);
+          const float2 n = unpack_bf16x2(pack_bf16x2(a.x * r, a.y * r));      // normalised value rounded to bf16 first
+          uo[j] = pack_bf16x2(w2.x * n.x, w2.y * n.y);
+        }
+        p.out[row * p.n_vec + c] = o;
+      }
+    }
+  }
+}
+
+int launch_rmsnorm(const jl_rmsnorm_args* a, cudaStream_t stream) {
+  if (a->x == nullptr || a->weight == nullptr || a->out == nullptr) return fail(JL_ERR_BAD_ARG, "jl_rmsnorm: NULL pointer");
+  if (a->residual != nullptr && a->sum_out == nullptr) return fail(JL_ERR_BAD_ARG, "jl_rmsnorm: sum_out is required with a residual");
+  if (a->hidden <= 0 || a->hidden % 8 != 0 || a->hidden > 8192)
+    return fail(JL_ERR_UNSUPPORTED, "jl_rmsnorm: hidden must be a multiple of 8 and <= 8192, got %d", a->hidden);
+  if (a->rows < 0) return fail(JL_ERR_BAD_ARG, "jl_rmsnorm: negative row count");
+  if ((reinterpret_cast<uintptr_t>(a->x) | reinterpret_cast<uintptr_t>(a->residual) | reinterpret_cast<uintptr_t>(a->weight) |
+       reinterpret_cast<uintptr_t>(a->sum_out) | reinterpret_cast<uintptr_t>(a->out)) & 15)
+    return fail(JL_ERR_BAD_ARG, "jl_rmsnorm: pointers must be 16-byte aligned");
+  if (a->rows == 0) return JL_OK;
+  RmsParams p{};
+  p.x = static_cast<const uint4*>(a->x);
+  p.res = static_cast<const uint4*>(a->residual);
+  p.w = static_cast<const uint4*>(a->weight);
+  p.sum_out = static_cast<uint4*>(a->sum_out);
+  p.out = static_cast<uint4*>(a->out);
+  p.rows = a->rows;
+  p.n_vec = a->hidden / 8;
+  p.inv_hidden = 1.f / static_cast<float>(a->hidden);
+  p.eps = a->eps;
+  const int grid = static_cast<int>(a->rows < 148 * 8 ? a->rows : 148 * 8);
+  rmsnorm_kernel<<<grid, 256, 0, stream>>>(p);
+  return check_launch("jl_rmsnorm");
+}
+
 }  // namespace jl

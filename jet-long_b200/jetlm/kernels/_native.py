@@ -94,6 +94,11 @@ class NormRopeArgs(C.Structure):
     ]
 
 
+class RmsNormArgs(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("residual", C.c_void_p), ("weight", C.c_void_p), ("sum_out", C.c_void_p),
+                ("out", C.c_void_p), ("rows", C.c_int64), ("hidden", C.c_int32), ("eps", C.c_float)]
+
+
 # Every symbol include/jetlong_b200.h declares: (name, restype, argtypes)
 EXPORTS = [
     ("jl_version", C.c_int, []),
@@ -109,6 +114,7 @@ EXPORTS = [
     ("jl_merge", C.c_int, [C.POINTER(MergeArgs), C.c_void_p]),
     ("jl_rotate", C.c_int, [C.POINTER(RotateArgs), C.c_void_p]),
     ("jl_norm_rope", C.c_int, [C.POINTER(NormRopeArgs), C.c_void_p]),
+    ("jl_rmsnorm", C.c_int, [C.POINTER(RmsNormArgs), C.c_void_p]),
 ]
 
 _LIB = None

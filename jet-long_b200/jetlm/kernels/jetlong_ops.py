@@ -62,8 +62,8 @@ def _st(t: torch.Tensor, i: int) -> int:
 
 # Instrumentation used by the benchmark: kernel launches issued through this module, and (when a list
 # is installed with set_event_sink) a CUDA event pair around every attention kernel launch.
-LAUNCHES = {"jl_prefill": 0, "jl_decode": 0, "jl_merge": 0, "jl_rotate": 0, "jl_norm_rope": 0}
-KERNELS_PER_CALL = {"jl_prefill": 1, "jl_decode": 2, "jl_merge": 1, "jl_rotate": 1, "jl_norm_rope": 1}
+LAUNCHES = {"jl_prefill": 0, "jl_decode": 0, "jl_merge": 0, "jl_rotate": 0, "jl_norm_rope": 0, "jl_rmsnorm": 0}
+KERNELS_PER_CALL = {"jl_prefill": 1, "jl_decode": 2, "jl_merge": 1, "jl_rotate": 1, "jl_norm_rope": 1, "jl_rmsnorm": 1}
 _EVENT_SINK: Optional[list] = None
 
 
@@ -171,6 +171,29 @@ def rope_regroup(x_base, inv_freq, *, group_size: int, pos0=0, pos_block=0, pos_
     """jetlong far-class operand from a base-rotated tensor: extra rotation by floor(p/G) - p."""
     return rope_rotate(x_base, inv_freq, pos0=pos0, div=int(group_size), div_mul=1, mod=_BIG, mod_mul=-1,
                        pos_block=pos_block, pos_block_stride=pos_block_stride, out=out)
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, *, eps: float, residual: Optional[torch.Tensor] = None):
+    """Qwen3RMSNorm over the last dimension in one pass.  With `residual`, returns (x + residual, norm(x + residual));
+    otherwise norm(x).  x / residual: contiguous bf16 (..., hidden)."""
+    op = "rmsnorm"
+    if x.dtype not in _SUPPORTED_DTYPES or weight.dtype != x.dtype or not x.is_cuda:
+        raise ValueError(f"{op}: x and weight must be CUDA torch.bfloat16 tensors")
+    _require_contiguous(op, "x", x)
+    _require_arch(op, x.device)
+    hidden = x.shape[-1]
+    out = torch.empty_like(x)
+    a = N.RmsNormArgs(x.data_ptr(), None, weight.data_ptr(), None, out.data_ptr(), x.numel() // hidden, hidden, float(eps))
+    summed = None
+    if residual is not None:
+        if residual.shape != x.shape or residual.dtype != x.dtype:
+            raise ValueError(f"{op}: residual must match x")
+        _require_contiguous(op, "residual", residual)
+        summed = torch.empty_like(x)
+        a.residual, a.sum_out = residual.data_ptr(), summed.data_ptr()
+    with torch.cuda.device(x.device):
+        _timed_call("jl_rmsnorm", lambda: N.lib().jl_rmsnorm(C.byref(a), _stream()))
+    return (summed, out) if residual is not None else out
 
 
 def norm_rope(x: torch.Tensor, weight: torch.Tensor, inv_freq: torch.Tensor, *, eps: float, pos0: int = 0,

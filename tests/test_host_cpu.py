@@ -34,13 +34,13 @@ def test_library_exports_every_declared_symbol():
 def test_struct_layout_matches_header(tmp_path):
     n = _native()
     src = tmp_path / "sz.c"
-    src.write_text('#include <stdio.h>\n#include "jetlong_b200.h"\nint main(){printf("%zu %zu %zu %zu %zu %zu %zu\\n",'
+    src.write_text('#include <stdio.h>\n#include "jetlong_b200.h"\nint main(){printf("%zu %zu %zu %zu %zu %zu %zu %zu\\n",'
                    "sizeof(jl_posmap),sizeof(jl_prefill_args),sizeof(jl_kv_segment),sizeof(jl_decode_args),"
-                   "sizeof(jl_merge_args),sizeof(jl_rotate_args),sizeof(jl_norm_rope_args));return 0;}\n")
+                   "sizeof(jl_merge_args),sizeof(jl_rotate_args),sizeof(jl_norm_rope_args),sizeof(jl_rmsnorm_args));return 0;}\n")
     exe = tmp_path / "sz"
     subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), "-o", str(exe), str(src)])
     sizes = [int(x) for x in subprocess.check_output([str(exe)]).split()]
-    assert sizes == [C.sizeof(t) for t in (n.PosMap, n.PrefillArgs, n.KvSegment, n.DecodeArgs, n.MergeArgs, n.RotateArgs, n.NormRopeArgs)]
+    assert sizes == [C.sizeof(t) for t in (n.PosMap, n.PrefillArgs, n.KvSegment, n.DecodeArgs, n.MergeArgs, n.RotateArgs, n.NormRopeArgs, n.RmsNormArgs)]
 
 
 def test_host_only_entry_points():

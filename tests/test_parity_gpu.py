@@ -117,6 +117,27 @@ def test_rotate_strided_into_cache():
     assert torch.all(cache[:, :, :7] == 0) and torch.all(cache[:, :, 57:] == 0)
 
 
+@pytest.mark.parametrize("hidden", [2048, 2560, 4096])
+def test_rmsnorm_fused_pass(hidden):
+    """One-pass RMSNorm (+ residual add) reproduces Qwen3RMSNorm's bf16 results."""
+    from transformers.models.qwen3.modeling_qwen3 import Qwen3RMSNorm
+    ops = _ops()
+    torch.manual_seed(hidden)
+    x = (torch.randn(3, 37, hidden) * 2).bfloat16()
+    res = torch.randn(3, 37, hidden).bfloat16()
+    norm = Qwen3RMSNorm(hidden, eps=1e-6).bfloat16()
+    norm.weight.data = (1 + 0.3 * torch.randn(hidden)).bfloat16()
+    exp = norm(x)
+    got = ops.rmsnorm(x.cuda(), norm.weight.data.cuda(), eps=1e-6).cpu()
+    diff = (got.float() - exp.float()).abs()
+    assert float((diff > 0).float().mean()) < 0.01 and float(diff.max()) <= 2 ** -5      # rsqrt last-bit differences only
+    s_exp = res + x
+    summed, got2 = ops.rmsnorm(x.cuda(), norm.weight.data.cuda(), eps=1e-6, residual=res.cuda())
+    assert torch.equal(summed.cpu(), s_exp)
+    diff = (got2.cpu().float() - norm(s_exp).float()).abs()
+    assert float((diff > 0).float().mean()) < 0.01 and float(diff.max()) <= 2 ** -5
+
+
 def test_norm_rope_fused_pass():
     """RMSNorm + base RoPE + regroup in one kernel == Qwen3RMSNorm (its bf16 roundings) followed by the
     oracle's fp32 rotations; strided output straight into a (B,Hk,S,D) cache, block-cyclic positions."""
