@@ -228,8 +228,9 @@ def decode_microbench(peaks, shard, iters=20):
         if shard is None:
             segs = [ops.KvSegment(kv[:, :boundary], vv[:, :boundary], 1), ops.KvSegment(kv[:, boundary:], vv[:, boundary:], 0)]
             fn_pre = lambda: ops.decode_segments([q, qg], segs, return_lse=False)
-        else:
-            fn_pre = None
+        else:       # sharded: every rank streams its contiguous range; kc doubles as the regrouped cache (same bytes moved)
+            fn_pre = lambda: backend.fused_jetlong_decode_cache(q, qg, kc, vc, boundary=boundary, inv_freq=inv, group_size=G,
+                                                                has_any_pad=False, training=False, key_cache_group=kc)
         fn_inplace = lambda: backend.fused_jetlong_decode_cache(q, qg, kc, vc, boundary=boundary, inv_freq=inv, group_size=G,
                                                                 has_any_pad=False, training=False)
         res = {}

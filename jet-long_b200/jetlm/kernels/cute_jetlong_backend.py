@@ -162,28 +162,31 @@ def fused_jetlong_decode(query_base, query_group, key_near, value_near, key_dist
 
 def fused_jetlong_decode_cache(query_base, query_group, key_cache, value_cache, *, boundary: int, inv_freq,
                                group_size: int, softmax_scale=None, has_any_pad: bool, training: bool,
-                               cache_pos0: int = 0, return_lse: bool = False):
+                               cache_pos0: int = 0, return_lse: bool = False, key_cache_group=None):
     """Decode straight off a base-rotated (B,Hk,S,D) cache: keys [0, boundary) are the far class and are
     regrouped inside the kernel while they stream, keys [boundary, S) are the near class.  Replaces the
     reference's per-token host-side regroup of the whole distant cache plus its slice / pad copies
     (modeling :428-440, backend :143-155).  cache_pos0 is the absolute position of cache row 0 (non-zero
-    for a sequence shard)."""
+    for a sequence shard).  key_cache_group, if given, is a (B,Hk,S,D) cache of already regrouped keys: the far
+    class then reads it as stored (the reference's contract) instead of regrouping key_cache in-kernel."""
     if training:
         raise RuntimeError("JetLong backend 'fused' is inference-only")
     if has_any_pad:
         raise RuntimeError("JetLong backend 'fused' does not support left-padded decode batches")
     kc, vc = key_cache.transpose(1, 2), value_cache.transpose(1, 2)        # (B,S,Hk,D) views
+    kg = key_cache_group.transpose(1, 2) if key_cache_group is not None else None
     if _SHARD is not None and cache_pos0 == 0:
         sh = _SHARD
         lo, hi = sh.contiguous_range(kc.shape[1])
         B, _, H, D = query_base.shape
         part = lambda out, lse: _decode_range(query_base, query_group, kc[:, lo:hi], vc[:, lo:hi], int(boundary) - lo, lo,
-                                              inv_freq, group_size, softmax_scale, True, out=out, lse=lse)
+                                              inv_freq, group_size, softmax_scale, True, out=out, lse=lse,
+                                              kg=kg[:, lo:hi] if kg is not None else None)
         buf = _partial_buffer(sh, (B, 1, H, D), (B, H, 1), query_base.dtype, query_base.device)
         out, lse = sharded_attention(part, ops.merge_partials, sh, buf)
         return (out, lse) if return_lse else out
     return _decode_range(query_base, query_group, kc, vc, int(boundary) - int(cache_pos0), int(cache_pos0),
-                         inv_freq, group_size, softmax_scale, return_lse)
+                         inv_freq, group_size, softmax_scale, return_lse, kg=kg)
 
 
 def fused_jetlong_decode_cache_stripe(query_base, query_group, key_stripe, value_stripe, *, boundary: int, inv_freq,
@@ -220,11 +223,13 @@ def fused_jetlong_decode_cache_stripe(query_base, query_group, key_stripe, value
 
 
 def _decode_range(query_base, query_group, kc, vc, b, pos0, inv_freq, group_size, softmax_scale, return_lse,
-                  out=None, lse=None):
+                  out=None, lse=None, kg=None):
     """Decode over rows of a (B,S,Hk,D) cache view whose row 0 has absolute position pos0; rows < b are far."""
     b = max(0, min(b, kc.shape[1]))
     segs = []
-    if b > 0:
+    if b > 0 and kg is not None:
+        segs.append(ops.KvSegment(kg[:, :b], vc[:, :b], q_class=1))
+    elif b > 0:
         segs.append(ops.KvSegment(kc[:, :b], vc[:, :b], q_class=1, rotate=True, pos0=int(pos0)))
     if b < kc.shape[1]:
         segs.append(ops.KvSegment(kc[:, b:], vc[:, b:], q_class=0))
