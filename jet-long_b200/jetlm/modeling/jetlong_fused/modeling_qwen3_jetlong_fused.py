@@ -58,7 +58,8 @@ class BifocalPlan:
     q_pos0: int              # absolute position of the first query token
     max_q_pos: int           # absolute position of the last query token
     has_any_pad: bool        # a left-padded batch (unsupported by the fused kernels)
-    token_shard: object = None   # SequenceShard when this rank holds a block-cyclic stripe of the tokens
+    token_shard: object = None   # SequenceShard when this rank holds a block-cyclic stripe of the KV cache
+    replicated: bool = False     # sharded cache, but every rank runs all tokens of this call (decode)
 
 
 class Qwen3JetLongFusedRotaryEmbedding(Qwen3RotaryEmbedding):
@@ -78,14 +79,17 @@ class Qwen3JetLongFusedRotaryEmbedding(Qwen3RotaryEmbedding):
 
     @torch.no_grad()
     def forward(self, x, position_ids, max_position: Optional[int] = None, kv_len: Optional[int] = None,
-                first_position: Optional[int] = None, token_shard=None):
+                first_position: Optional[int] = None, token_shard=None, replicated: bool = False,
+                kernels_within_window: bool = False):
+        """kernels_within_window: return the extended tuple (with G = 1) inside the pretrained window too, so
+        that the attention runs on the bifocal kernels there as well (both classes then score alike)."""
         cos, sin = super().forward(x, position_ids)
         if not self.jetlong_enabled:
             return cos, sin
         if max_position is None:
             max_position = int(position_ids.max().item())      # caller-supplied positions: read them back
         l_curr = max_position + 1
-        if l_curr <= self.jetlong_w:
+        if l_curr <= self.jetlong_w and not kernels_within_window:
             return cos, sin
         group = max(1, math.ceil(l_curr / self.jetlong_w))
         seq = position_ids.shape[-1]
@@ -93,7 +97,7 @@ class Qwen3JetLongFusedRotaryEmbedding(Qwen3RotaryEmbedding):
         if position_ids.shape[0] > 1 and kv_len is not None:
             has_pad = bool(((kv_len - 1 - position_ids[:, -1]) > 0).any().item())
         first = first_position if first_position is not None else max_position - seq + 1
-        plan = BifocalPlan(group, first, max_position, has_pad, token_shard)
+        plan = BifocalPlan(group, first, max_position, has_pad, token_shard, replicated)
         return cos, sin, group, self.inv_freq.to(device=x.device, dtype=torch.float32), position_ids, plan
 
 
@@ -168,70 +172,128 @@ class Qwen3JetLongFusedAttention(nn.Module):
         q_eps, k_eps = self.q_norm.variance_epsilon, self.k_norm.variance_epsilon
 
         if plan.token_shard is not None:
-            return self._token_sharded_prefill(q, k, v, plan, group, inv_freq, past_key_values, out_shape, backend, ops)
+            return self._token_sharded(q, k, v, plan, group, inv_freq, past_key_values, out_shape, backend, ops)
 
-        # q/k RMSNorm + base RoPE (+ regroup) in one fused pass each; K lands straight in (B, Hk, S, D) cache layout
-        fresh = past_key_values is None or past_key_values.get_seq_length(self.layer_idx) == 0
-        q_base, q_group = ops.norm_rope(q, self.q_norm.weight, inv_freq, eps=q_eps, pos0=plan.q_pos0, group_size=group)
-        k_new = torch.empty(bsz, Hk, seq, D, dtype=k.dtype, device=k.device)
+        from jetlm.kernels.kv_cache import BifocalKVCache
+        slot = past_key_values.layers[self.layer_idx] if isinstance(past_key_values, BifocalKVCache) else None
+        if slot is not None:
+            seen = slot.get_seq_length()
+        else:
+            seen = past_key_values.get_seq_length(self.layer_idx) if past_key_values is not None else 0
+        regroup = group > 1          # G = 1 (inside the pretrained window): both classes score alike
+        # q/k RMSNorm + base RoPE (+ regroup) in one fused pass each; K lands straight in its cache rows
+        if regroup:
+            q_base, q_group = ops.norm_rope(q, self.q_norm.weight, inv_freq, eps=q_eps, pos0=plan.q_pos0, group_size=group)
+        else:
+            q_base = q_group = ops.norm_rope(q, self.q_norm.weight, inv_freq, eps=q_eps, pos0=plan.q_pos0)
+        if slot is not None:
+            k_new, v_dst = slot.reserve(seq)                           # (B, seq, Hk, D) rows of the static cache
+        else:
+            k_new = torch.empty(bsz, Hk, seq, D, dtype=k.dtype, device=k.device).transpose(1, 2)
         k_group = None
-        if fresh and seq > 1:        # no older keys: the regrouped keys of this call are all there is
-            k_group = torch.empty(bsz, Hk, seq, D, dtype=k.dtype, device=k.device)
+        if seen == 0 and seq > 1 and regroup:      # no older keys: the regrouped keys of this call are all there is
+            k_group = (past_key_values.group_scratch(seq) if slot is not None
+                       else torch.empty(bsz, Hk, seq, D, dtype=k.dtype, device=k.device).transpose(1, 2))
             ops.norm_rope(k, self.k_norm.weight, inv_freq, eps=k_eps, pos0=plan.q_pos0, group_size=group,
-                          out_base=k_new.transpose(1, 2), out_group=k_group.transpose(1, 2))
+                          out_base=k_new, out_group=k_group)
         else:
-            ops.norm_rope(k, self.k_norm.weight, inv_freq, eps=k_eps, pos0=plan.q_pos0, out_base=k_new.transpose(1, 2))
-        v_new = v.transpose(1, 2)
-        if past_key_values is not None:
-            k_all, v_all = past_key_values.update(k_new, v_new, self.layer_idx, {})
+            ops.norm_rope(k, self.k_norm.weight, inv_freq, eps=k_eps, pos0=plan.q_pos0, out_base=k_new)
+        if slot is not None:
+            v_dst.copy_(v)
+            slot.commit(seq)
+            k_all, v_all = slot.key_rows(), slot.value_rows()         # (B, len, Hk, D) views
+        elif past_key_values is not None:
+            k_all, v_all = past_key_values.update(k_new.transpose(1, 2), v.transpose(1, 2), self.layer_idx, {})
+            k_all, v_all = k_all.transpose(1, 2), v_all.transpose(1, 2)
         else:
-            k_all, v_all = k_new, v_new
-        kv_len = k_all.shape[2]
+            k_all, v_all = k_new, v
+        kv_len = k_all.shape[1]
 
         if seq > 1:
             # prefill / chunked prefill: regroup every cached key once for this call's G, then one kernel
-            if k_group is None:      # chunked prefill: regroup every cached key for this call's G
-                k_group = torch.empty(bsz, Hk, kv_len, D, dtype=k_all.dtype, device=k_all.device)
-                ops.rope_regroup(k_all.transpose(1, 2), inv_freq, group_size=group, pos0=0, out=k_group.transpose(1, 2))
+            if not regroup:
+                k_group = k_all
+            elif k_group is None:
+                k_group = (past_key_values.group_scratch(kv_len) if slot is not None
+                           else torch.empty(bsz, Hk, kv_len, D, dtype=k_all.dtype, device=k_all.device).transpose(1, 2))
+                ops.rope_regroup(k_all, inv_freq, group_size=group, pos0=0, out=k_group)
             if k_all.stride() != k_group.stride():           # a cache that hands out non-dense views
                 k_all = k_all.contiguous()
             attn = backend.fused_jetlong_prefill(
-                q_base.transpose(1, 2), q_group.transpose(1, 2), k_all, k_group, v_all,
-                seqstart_q=kv_len - seq, window_size_left=w_0, softmax_scale=self.scaling,
+                q_base.transpose(1, 2), q_group.transpose(1, 2), k_all.transpose(1, 2), k_group.transpose(1, 2),
+                v_all.transpose(1, 2), seqstart_q=kv_len - seq, window_size_left=w_0, softmax_scale=self.scaling,
                 has_any_pad=plan.has_any_pad, training=self.training)
         else:
             boundary = max(plan.max_q_pos - w_0, 0)
-            if boundary == 0:
+            if boundary == 0 and regroup:
                 raise RuntimeError(
                     f"jetlong_fused requires a non-empty distant decode region (decode context must exceed "
                     f"w_0={w_0}); use the 'jetlong' method for short contexts.")
             attn = backend.fused_jetlong_decode_cache(
-                q_base, q_group, k_all, v_all, boundary=boundary, inv_freq=inv_freq, group_size=group,
-                softmax_scale=self.scaling, has_any_pad=plan.has_any_pad, training=self.training)
+                q_base, q_group, k_all.transpose(1, 2), v_all.transpose(1, 2), boundary=boundary, inv_freq=inv_freq,
+                group_size=group, softmax_scale=self.scaling, has_any_pad=plan.has_any_pad, training=self.training)
         return self.o_proj(attn.reshape(*out_shape, -1)), None
 
-
-    def _token_sharded_prefill(self, q, k, v, plan, group, inv_freq, past_key_values, out_shape, backend, ops):
-        """This rank ran the projections for a block-cyclic stripe of the prompt only; it keeps that
-        stripe of the KV cache, and the attention exchanges Q and partial (O, LSE) between ranks."""
+    def _token_sharded(self, q, k, v, plan, group, inv_freq, past_key_values, out_shape, backend, ops):
+        """Sequence-parallel attention over a cache of which this rank keeps a block-cyclic stripe.
+        Prefill chunk (plan.replicated False): this rank ran the projections for its stripe of the chunk
+        only; the attention exchanges Q and partial (O, LSE) between ranks.  Decode (plan.replicated True):
+        every rank ran the one new token; its key and value are stored by the rank that owns the position,
+        every rank attends the query to its stripe and the partials are all-gathered and merged."""
+        from jetlm.kernels.kv_cache import BifocalKVCache
         sh = plan.token_shard
         bsz, seq = out_shape
         Hk, D = self.num_kv_heads, self.head_dim
+        slot = past_key_values.layers[self.layer_idx] if isinstance(past_key_values, BifocalKVCache) else None
+        q_eps, k_eps = self.q_norm.variance_epsilon, self.k_norm.variance_epsilon
+
+        if plan.replicated:
+            if slot is None:
+                raise RuntimeError("token-sharded decode needs a BifocalKVCache built with the same SequenceShard")
+            if seq != 1:
+                raise ValueError("token-sharded decode takes one token per call")
+            if group > 1:
+                q_base, q_group = ops.norm_rope(q, self.q_norm.weight, inv_freq, eps=q_eps, pos0=plan.q_pos0, group_size=group)
+            else:
+                q_base = q_group = ops.norm_rope(q, self.q_norm.weight, inv_freq, eps=q_eps, pos0=plan.q_pos0)
+            k_dst, v_dst = slot.reserve(1)
+            if k_dst.shape[1] == 1:                                   # this rank owns the new position
+                ops.norm_rope(k, self.k_norm.weight, inv_freq, eps=k_eps, pos0=plan.q_pos0, out_base=k_dst)
+                v_dst.copy_(v)
+            slot.commit(1)
+            attn = backend.fused_jetlong_decode_cache_stripe(
+                q_base, q_group, slot.key_rows().transpose(1, 2), slot.value_rows().transpose(1, 2),
+                boundary=max(plan.max_q_pos - self.jetlong_w_0, 0), inv_freq=inv_freq, group_size=group,
+                softmax_scale=self.scaling)
+            return self.o_proj(attn.reshape(bsz, seq, -1)), None
+
         geo = dict(pos_block=sh.block, pos_block_stride=sh.world * sh.block)
         pos0 = plan.q_pos0 + sh.rank * sh.block
-        q_base = ops.norm_rope(q, self.q_norm.weight, inv_freq, eps=self.q_norm.variance_epsilon, pos0=pos0, **geo)
-        k_new = torch.empty(bsz, Hk, seq, D, dtype=k.dtype, device=k.device)
-        ops.norm_rope(k, self.k_norm.weight, inv_freq, eps=self.k_norm.variance_epsilon, pos0=pos0,
-                      out_base=k_new.transpose(1, 2), **geo)
-        if past_key_values is not None:
-            k_all, v_all = past_key_values.update(k_new, v.transpose(1, 2), self.layer_idx, {})
+        q_base = ops.norm_rope(q, self.q_norm.weight, inv_freq, eps=q_eps, pos0=pos0, **geo)
+        if slot is not None:
+            k_new, v_dst = slot.reserve(seq * sh.world)
+            if k_new.shape[1] != seq:
+                raise RuntimeError("token-sharded prefill chunks must start on a multiple of world * block tokens")
         else:
-            k_all, v_all = k_new, v.transpose(1, 2)
-        k_group = torch.empty(k_all.shape, dtype=k_all.dtype, device=k_all.device)
-        ops.rope_regroup(k_all.transpose(1, 2), inv_freq, group_size=group, pos0=sh.rank * sh.block,
-                         out=k_group.transpose(1, 2), **geo)
+            k_new = torch.empty(bsz, Hk, seq, D, dtype=k.dtype, device=k.device).transpose(1, 2)
+        ops.norm_rope(k, self.k_norm.weight, inv_freq, eps=k_eps, pos0=pos0, out_base=k_new, **geo)
+        if slot is not None:
+            v_dst.copy_(v)
+            slot.commit(seq * sh.world)
+            k_all, v_all = slot.key_rows(), slot.value_rows()
+        elif past_key_values is not None:
+            k_all, v_all = past_key_values.update(k_new.transpose(1, 2), v.transpose(1, 2), self.layer_idx, {})
+            k_all, v_all = k_all.transpose(1, 2), v_all.transpose(1, 2)
+        else:
+            k_all, v_all = k_new, v
+        if group > 1:
+            k_group = (past_key_values.group_scratch(k_all.shape[1]) if slot is not None
+                       else torch.empty(bsz, Hk, k_all.shape[1], D, dtype=k_all.dtype, device=k_all.device).transpose(1, 2))
+            ops.rope_regroup(k_all, inv_freq, group_size=group, pos0=sh.rank * sh.block, out=k_group, **geo)
+        else:
+            k_group = k_all
         attn = backend.fused_jetlong_prefill_token_sharded(
-            q_base, k_all.transpose(1, 2), k_group.transpose(1, 2), v_all.transpose(1, 2), q_start=plan.q_pos0,
+            q_base, k_all, k_group, v_all, q_start=plan.q_pos0,
             inv_freq=inv_freq, group_size=group, window_size_left=self.jetlong_w_0, softmax_scale=self.scaling)
         return self.o_proj(attn.reshape(bsz, seq, -1)), None
 
@@ -303,7 +365,9 @@ class Qwen3JetLongFusedModel(Qwen3PreTrainedModel):
                 position_ids = (torch.arange(seq, device=inputs_embeds.device) + seen).unsqueeze(0)
                 host_max = seen + seq - 1                     # known without touching the device
         hidden = inputs_embeds
-        position_embeddings = self.rotary_emb(hidden, position_ids, max_position=host_max, kv_len=seen + seq)
+        kww = bool(getattr(self, "kernels_within_window", False)) and hidden.is_cuda and not self.training
+        position_embeddings = self.rotary_emb(hidden, position_ids, max_position=host_max, kv_len=seen + seq,
+                                              kernels_within_window=kww)
         extended = len(position_embeddings) >= 4
 
         mask_map = attention_mask if isinstance(attention_mask, dict) else None
@@ -325,24 +389,34 @@ class Qwen3JetLongFusedModel(Qwen3PreTrainedModel):
 
 
     def _forward_token_sharded(self, input_ids, past_key_values, use_cache, shard, **kwargs) -> BaseModelOutputWithPast:
-        """Sequence-parallel prefill: `input_ids` is the whole (B, S) chunk on every rank; this rank embeds,
-        projects and stores only its block-cyclic stripe of the tokens (S must be a multiple of
-        world * block).  Returns the hidden states of the local stripe, in stripe order."""
+        """Sequence-parallel forward; `input_ids` is the whole (B, S) call on every rank.
+        S a multiple of world * block (a prefill chunk): this rank embeds, projects and stores only its
+        block-cyclic stripe of the tokens and returns the hidden states of that stripe, in stripe order.
+        S = 1 (decode, needs a BifocalKVCache): every rank runs the token; the rank that owns its position
+        stores its key and value; every rank returns the same hidden state."""
+        from jetlm.kernels.kv_cache import BifocalKVCache
         if input_ids is None:
-            raise ValueError("token-sharded prefill takes input_ids")
+            raise ValueError("token-sharded forward takes input_ids")
         seq = input_ids.shape[1]
-        if seq % (shard.world * shard.block) != 0:
+        replicated = seq == 1
+        if not replicated and seq % (shard.world * shard.block) != 0:
             raise ValueError(f"token-sharded prefill needs a multiple of {shard.world * shard.block} tokens, got {seq}")
         if use_cache and past_key_values is None:
             past_key_values = DynamicCache(config=self.config)
-        seen = (past_key_values.get_seq_length() if past_key_values is not None else 0) * shard.world
-        rows = shard.owned_rows(seq).to(input_ids.device)
-        hidden = self.embed_tokens(input_ids[:, rows])
-        position_ids = (rows + seen).unsqueeze(0)
+        if isinstance(past_key_values, BifocalKVCache):
+            seen = past_key_values.get_seq_length()
+        else:       # a cache that only knows this rank's rows (whole stripes so far)
+            seen = (past_key_values.get_seq_length() if past_key_values is not None else 0) * shard.world
+        if replicated:
+            hidden = self.embed_tokens(input_ids)
+            position_ids = torch.full((1, 1), seen, dtype=torch.long, device=input_ids.device)
+        else:
+            rows = shard.owned_rows(seq).to(input_ids.device)
+            hidden = self.embed_tokens(input_ids[:, rows])
+            position_ids = (rows + seen).unsqueeze(0)
         position_embeddings = self.rotary_emb(hidden, position_ids, max_position=seen + seq - 1, kv_len=None,
-                                              first_position=seen, token_shard=shard)
-        if len(position_embeddings) < 4:
-            raise RuntimeError("token-sharded prefill is implemented for the extended (L > w) path only")
+                                              first_position=seen, token_shard=shard, replicated=replicated,
+                                              kernels_within_window=True)
         for layer in self.layers[: self.config.num_hidden_layers]:
             hidden = layer(hidden, attention_mask=None, position_embeddings=position_embeddings,
                            position_ids=position_ids, past_key_values=past_key_values, use_cache=use_cache, **kwargs)
@@ -396,6 +470,45 @@ class Qwen3JetLongFusedForCausalLM(Qwen3PreTrainedModel, GenerationMixin):
             loss = self.loss_function(logits=logits, labels=labels, vocab_size=self.config.vocab_size, **kwargs)
         return CausalLMOutputWithPast(loss=loss, logits=logits, past_key_values=outputs.past_key_values,
                                       hidden_states=outputs.hidden_states, attentions=outputs.attentions)
+
+
+    @torch.no_grad()
+    def generate_long(self, input_ids, max_new_tokens: int, chunk_tokens: int = 32768, past_key_values=None):
+        """Greedy continuation of a long prompt: chunked prefill into a preallocated BifocalKVCache, then
+        one-token steps on the same cache.  G is recomputed per call from the length reached so far, as in
+        the reference (:145-158), so the result depends on the chunk schedule exactly as the reference's does.
+
+        With `model.token_sharded = True` and sequence sharding configured, every rank calls this with the
+        same arguments: each keeps a block-cyclic stripe of the cache (the prompt length and chunk_tokens
+        must then be multiples of world * block) and all ranks return the same tokens.
+        Returns (B, max_new_tokens) token ids."""
+        import torch.distributed as dist
+        from jetlm.kernels import cute_jetlong_backend as backend
+        from jetlm.kernels.kv_cache import BifocalKVCache
+        shard = backend.sequence_shard() if getattr(self.model, "token_sharded", False) else None
+        bsz, n_prompt = input_ids.shape
+        if past_key_values is None:
+            past_key_values = BifocalKVCache(self.config, n_prompt + max_new_tokens, batch=bsz, device=input_ids.device,
+                                             dtype=self.lm_head.weight.dtype, shard=shard)
+
+        def rank_of(r):
+            return dist.get_global_rank(shard.group, r) if shard.group is not None else r
+
+        hidden = None
+        for lo in range(0, n_prompt, chunk_tokens):
+            hidden = self.model(input_ids=input_ids[:, lo: lo + chunk_tokens], past_key_values=past_key_values,
+                                use_cache=True).last_hidden_state
+        token = self.lm_head(hidden[:, -1:, :]).argmax(-1)               # (B, 1)
+        if shard is not None:        # the prompt's last block lives on the last rank
+            dist.broadcast(token, src=rank_of(shard.world - 1), group=shard.group)
+        out = [token]
+        for _ in range(max_new_tokens - 1):
+            hidden = self.model(input_ids=token, past_key_values=past_key_values, use_cache=True).last_hidden_state
+            token = self.lm_head(hidden[:, -1:, :]).argmax(-1)
+            if shard is not None:    # ranks compute the same logits; one source keeps them in lock-step regardless
+                dist.broadcast(token, src=rank_of(0), group=shard.group)
+            out.append(token)
+        return torch.cat(out, dim=1)
 
 
 __all__ = ["Qwen3JetLongFusedForCausalLM", "Qwen3JetLongFusedModel", "Qwen3JetLongFusedRotaryEmbedding"]

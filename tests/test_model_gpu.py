@@ -110,3 +110,66 @@ def test_hf_generate_with_chunked_prefill(golden):
         res = model(input_ids=nxt, past_key_values=cache, use_cache=True)
         nxt = res.logits[:, -1].argmax(-1, keepdim=True)
     assert out[0, 150:].tolist() == toks
+
+
+def _drive(model, ids, cache, chunks, n_dec):
+    """Chunked prefill then teacher-forced one-token steps; returns the logits of every call, concatenated."""
+    logits, lo = [], 0
+    for n in chunks:
+        logits.append(model(input_ids=ids[:, lo: lo + n], past_key_values=cache, use_cache=True).logits.float())
+        lo += n
+    for t in range(lo, lo + n_dec):
+        logits.append(model(input_ids=ids[:, t: t + 1], past_key_values=cache, use_cache=True).logits.float())
+    return torch.cat(logits, dim=1)
+
+
+@torch.inference_mode()
+def test_static_cache_reproduces_dynamic_cache_logits(golden):
+    """Keys written straight into the preallocated cache by the fused norm -> RoPE pass, regrouped keys in
+    the shared scratch, decode off the in-place rows: the same kernels see the same operands as with
+    DynamicCache, so the logits agree to the last bit.  Chunks: in-window (40), extended (60 + 50)."""
+    from transformers import DynamicCache
+    from jetlm.kernels.kv_cache import BifocalKVCache
+    g = golden("model_tiny.npz")
+    model = _tiny_model(g)
+    ids = g["input_ids"].cuda()
+    want = _drive(model, ids, DynamicCache(config=model.config), (40, 60, 50), 5)
+    cache = BifocalKVCache(model.config, 160, device="cuda", dtype=torch.bfloat16)
+    got = _drive(model, ids, cache, (40, 60, 50), 5)
+    assert cache.get_seq_length() == 155
+    assert torch.equal(got, want)
+    cache.reset()                                     # fresh extended prefill (keys regrouped by the fused pass)
+    assert torch.equal(_drive(model, ids, cache, (150,), 3), _drive(model, ids, DynamicCache(config=model.config), (150,), 3))
+
+
+@torch.inference_mode()
+def test_kernels_within_window_match_stock_attention(golden):
+    """With `kernels_within_window` the bifocal kernels also serve L <= w (G = 1: one effective class).
+    Logits must agree with the stock attention path to bf16 accuracy, through prefill, the crossing of
+    the window and decode."""
+    from jetlm.kernels.kv_cache import BifocalKVCache
+    g = golden("model_tiny.npz")
+    model = _tiny_model(g)
+    ids = g["input_ids"].cuda()
+    want = _drive(model, ids, BifocalKVCache(model.config, 128, device="cuda", dtype=torch.bfloat16), (30, 20), 20)
+    model.model.kernels_within_window = True
+    got = _drive(model, ids, BifocalKVCache(model.config, 128, device="cuda", dtype=torch.bfloat16), (30, 20), 20)
+    d, cos = orc.compare(got.cpu(), want.cpu())
+    assert cos >= 0.9995 and d <= 0.1, (d, cos)
+
+
+@torch.inference_mode()
+def test_generate_long_equals_a_hand_rolled_greedy_loop(golden):
+    from transformers import DynamicCache
+    g = golden("model_tiny.npz")
+    model = _tiny_model(g)
+    ids = g["input_ids"].cuda()[:, :150]
+    out = model.generate_long(ids, max_new_tokens=5, chunk_tokens=64)
+    cache = DynamicCache(config=model.config)
+    for lo in range(0, 150, 64):
+        res = model(input_ids=ids[:, lo: lo + 64], past_key_values=cache, use_cache=True)
+    toks, nxt = [], res.logits[:, -1].argmax(-1, keepdim=True)
+    for _ in range(5):
+        toks.append(int(nxt))
+        nxt = model(input_ids=nxt, past_key_values=cache, use_cache=True).logits[:, -1].argmax(-1, keepdim=True)
+    assert out.tolist() == [toks]

@@ -81,6 +81,41 @@ def _worker(rank, world, port, results):
             model.model.token_sharded = False
         rows = shard.owned_rows(ids.shape[1]).cuda()
         d_tok, cos_tok = orc.compare(local.cpu(), full[:, rows].cpu())
+        # chunked prefill (first chunk inside the window) + decode steps on a striped static cache vs the
+        # same schedule on one GPU; then the greedy driver, which must return the same tokens on every rank
+        from jetlm.kernels.kv_cache import BifocalKVCache
+        chunk, n_dec = 256 * world, 6
+        model.model.rotary_emb.jetlong_w = chunk + 44          # chunk 1 inside the window (G=1), then G = 2, 3
+        ids2 = torch.randint(0, 256, (1, 3 * chunk + n_dec), device="cuda")
+
+        def drive(cache):
+            outs = [model(input_ids=ids2[:, c * chunk: (c + 1) * chunk], past_key_values=cache, use_cache=True).logits.float()
+                    for c in range(3)]
+            steps = [model(input_ids=ids2[:, t: t + 1], past_key_values=cache, use_cache=True).logits.float()
+                     for t in range(3 * chunk, 3 * chunk + n_dec)]
+            return torch.cat(outs, 1), torch.cat(steps, 1)
+
+        with torch.inference_mode():
+            model.model.kernels_within_window = True
+            pre_1, dec_1 = drive(BifocalKVCache(cfg, ids2.shape[1], device="cuda", dtype=torch.bfloat16))
+            toks_1 = model.generate_long(ids2[:, : 3 * chunk], max_new_tokens=4, chunk_tokens=chunk)
+            be.configure_sequence_sharding(shard)
+            model.model.token_sharded = True
+            cache = BifocalKVCache(cfg, ids2.shape[1], device="cuda", dtype=torch.bfloat16, shard=shard)
+            pre_n, dec_n = drive(cache)
+            toks_n = model.generate_long(ids2[:, : 3 * chunk], max_new_tokens=4, chunk_tokens=chunk)
+            gathered = [torch.empty_like(toks_n) for _ in range(world)]
+            dist.all_gather(gathered, toks_n)
+            be.configure_sequence_sharding(None)
+            model.model.token_sharded = False
+        assert cache.get_seq_length() == ids2.shape[1]
+        assert cache.layers[0].rows == shard.n_owned(ids2.shape[1])
+        assert all(torch.equal(t, toks_n) for t in gathered)
+        rows_c = torch.cat([shard.owned_rows(chunk) + c * chunk for c in range(3)]).cuda()
+        d_cpre, cos_cpre = orc.compare(pre_n.cpu(), pre_1[:, rows_c].cpu())
+        d_cdec, cos_cdec = orc.compare(dec_n.cpu(), dec_1.cpu())
+        assert cos_cpre >= 0.999 and d_cpre <= 0.15, (rank, d_cpre, cos_cpre)
+        assert cos_cdec >= 0.999 and d_cdec <= 0.15, (rank, d_cdec, cos_cdec)
         results[rank] = (d_pre, cos_pre, d_dec, cos_dec, d_lse, d_tok, cos_tok)
     finally:
         dist.destroy_process_group()
