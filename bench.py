@@ -283,6 +283,74 @@ def decode_microbench(peaks, shard, iters=20):
 # main arm
 # --------------------------------------------------------------------------------------------------
 
+@torch.inference_mode()
+def long_generate(args, cfg, model, shard, world):
+    """Chunked prefill of a long prompt into the preallocated KV cache (every rank keeps a block-cyclic stripe
+    when N > 1), then greedy one-token steps on the same cache.  Times are device times, max over ranks."""
+    import torch.distributed as dist
+    from jetlm.kernels.kv_cache import BifocalKVCache
+    T, steps = args.long_generate, args.decode_steps
+    model.model.kernels_within_window = True                  # the first chunk (L <= w) runs on the same kernels
+    gen = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, cfg.vocab_size, (1, T), generator=gen).cuda()
+    cache = BifocalKVCache(cfg, T + steps, device="cuda", dtype=torch.bfloat16, shard=shard)
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def device_ms(fn):
+        sync()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        r = fn()
+        e.record()
+        sync()
+        ms = torch.tensor([s.elapsed_time(e)], device="cuda")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms), r
+
+    def prefill():
+        hidden = None
+        for lo in range(0, T, args.chunk):
+            hidden = model.model(input_ids=ids[:, lo: lo + args.chunk], past_key_values=cache, use_cache=True).last_hidden_state
+        token = model.lm_head(hidden[:, -1:, :]).argmax(-1)
+        if world > 1:
+            dist.broadcast(token, src=world - 1)
+        return token
+
+    def decode(token):
+        out = []
+        for _ in range(steps):
+            hidden = model.model(input_ids=token, past_key_values=cache, use_cache=True).last_hidden_state
+            token = model.lm_head(hidden[:, -1:, :]).argmax(-1)
+            if world > 1:
+                dist.broadcast(token, src=0)
+            out.append(token)
+        return torch.cat(out, 1)
+
+    # warm-up on a short prompt (same code paths, allocator and NCCL set-up), then the measured run
+    warm = min(T, 2 * args.chunk)
+    for lo in range(0, warm, args.chunk):
+        model.model(input_ids=ids[:, lo: lo + args.chunk], past_key_values=cache, use_cache=True)
+    model.model(input_ids=ids[:, :1], past_key_values=cache, use_cache=True)
+    cache.reset()
+    pre_ms, token = device_ms(prefill)
+    dec_ms, toks = device_ms(lambda: decode(token))
+    layer = cache.layers[0]
+    return dict(metric="long_generate", n_gpus=world, prompt_tokens=T, chunk=args.chunk, decode_steps=steps,
+                prefill_s=round(pre_ms / 1e3, 3), prefill_tok_per_s=round(T / (pre_ms / 1e3), 1),
+                decode_ms_per_token=round(dec_ms / steps, 3), decode_tok_per_s=round(steps / (dec_ms / 1e3), 2),
+                group_size_at_end=max(1, math.ceil((T + steps) / args.w)),
+                kv_cache_gb_per_rank=round(2 * layer.keys.numel() * 2 * cfg.num_hidden_layers / 1e9, 2),
+                kv_rows_per_rank=layer.rows, tokens_in_cache=cache.get_seq_length(),
+                first_tokens=toks[0, :8].tolist(),
+                config=dict(model=args.model, w=args.w, w_0=args.w0, layers=cfg.num_hidden_layers,
+                            cache="preallocated, block-cyclic stripes of 1024 tokens over ranks" if world > 1 else "preallocated"))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -298,6 +366,11 @@ def main():
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--only-decode", action="store_true", help="run just the decode-attention microbench (profiling aid)")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--long-generate", type=int, default=0, metavar="TOKENS",
+                    help="instead of the default workload: chunked prefill of TOKENS tokens into the preallocated "
+                         "(sequence-sharded when N > 1) KV cache, then --decode-steps greedy tokens")
+    ap.add_argument("--chunk", type=int, default=32768)
+    ap.add_argument("--decode-steps", type=int, default=256)
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -344,6 +417,14 @@ def main():
     if shard is not None:
         # sequence parallel: every rank embeds / projects / stores only its block-cyclic stripe of the prompt
         model.model.token_sharded = True
+
+    if args.long_generate:
+        line = long_generate(args, cfg, model, shard, world)
+        if rank == 0:
+            print(json.dumps(line), flush=True)
+        if world > 1:
+            torch.distributed.destroy_process_group()
+        return
 
     gen = torch.Generator().manual_seed(1)
     ids_host = torch.randint(0, cfg.vocab_size, (1, args.seq), generator=gen).pin_memory()
