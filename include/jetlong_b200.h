@@ -124,7 +124,9 @@ int jl_prefill_status(void);
  *
  * q[c]: (B, 1, H, D)   seg[s].k / .v: (B, len, Hk, D)   out: (B, 1, H, D)   lse: (B, H) fp32.
  * seg[s].len_dev, if not NULL, is an int32 device array (B,) of per-sequence valid lengths
- * (<= len).  workspace holds the fp32 split partials; size it with jl_decode_workspace_bytes.
+ * (<= len).  With len_dev and row0_dev a launch whose host arguments never change (a CUDA-graph node)
+ * follows a growing cache: see jl_step_advance.  workspace holds the fp32 split partials; size it with
+ * jl_decode_workspace_bytes.
  * ------------------------------------------------------------------------------------------- */
 typedef struct {
   const void* k;
@@ -139,6 +141,8 @@ typedef struct {
   int32_t reserved;
   int64_t pos_block;        /* <= 0 means contiguous positions; else a multiple of 8 */
   int64_t pos_block_stride;
+  const int64_t* row0_dev;  /* optional device scalar: the segment starts at row *row0_dev of k / v (len and
+                               len_dev count from there; positions are those of the shifted rows) */
 } jl_kv_segment;
 
 typedef struct {
@@ -283,6 +287,66 @@ typedef struct {
 } jl_rmsnorm_args;
 
 int jl_rmsnorm(const jl_rmsnorm_args* args, void* cuda_stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Decode-step state on the device, so that one captured CUDA graph can be replayed for every new
+ * token.  The reference's decode step reads positions back to the host in every layer
+ * (modeling_qwen3_jetlong_fused.py:145, :342, :406) and cannot be captured; here the per-token facts
+ * live in device memory and kernels whose host arguments are fixed read them.  No reference counterpart.
+ *
+ * state: int64[JL_STEP_STATE_WORDS] = { pos, row, own, n_far, n_near }
+ *   pos    absolute position of the token being decoded
+ *   row    cache row (of this rank's stripe) the token's key / value go to
+ *   own    1 if this rank stores the token (always 1 without sharding)
+ *   n_far  rows of this rank's cache in the far class: positions < pos - w_0
+ *   n_near rows in the near class, the new token included when owned
+ * jl_step_advance: pos <- pos + 1, the other words recomputed for a cache sharded block-cyclically
+ * (block `block`, this rank `rank` of `world`; world = 1: contiguous).  lens, if not NULL, is an
+ * int32[2 * batch] device array that receives n_far (first batch entries) and n_near (next batch
+ * entries) for jl_kv_segment.len_dev.  Initialise state[0] to (next position - 1) from the host.
+ * ------------------------------------------------------------------------------------------- */
+#define JL_STEP_STATE_WORDS 5
+typedef struct {
+  int64_t* state;
+  int32_t* lens;            /* may be NULL */
+  int32_t batch;
+  int32_t rank, world;
+  int32_t reserved;
+  int64_t block;
+  int64_t w_0;
+} jl_step_advance_args;
+
+int jl_step_advance(const jl_step_advance_args* args, void* cuda_stream);
+
+/* jl_decode_append — everything between the q/k/v projections and the attention of one decode step, in
+ * one launch: per-head RMSNorm of q and k, base RoPE at state->pos, the regrouped query, and the
+ * write of the new key (base-rotated) and value into row state->row of the cache when state->own
+ * (replaces q_norm / k_norm, apply_rotary_pos_emb, correction_rotate_per_sample on q and the
+ * DynamicCache update, modeling_qwen3_jetlong_fused.py:292-294, :329-340, :375-376).  Same roundings as
+ * jl_norm_rope.  q: (B, H, D), k / v: (B, Hk, D) rows with strides; q_base / q_group: (B, H, D)
+ * contiguous; k_cache / v_cache: (B, rows, Hk, D) with strides. */
+typedef struct {
+  const void* q;
+  const void* k;
+  const void* v;
+  int64_t q_stride_b, q_stride_h, k_stride_b, k_stride_h, v_stride_b, v_stride_h;
+  const void* q_weight;     /* (head_dim,) bf16 */
+  const void* k_weight;
+  float q_eps, k_eps;
+  void* q_base;
+  void* q_group;
+  void* k_cache;
+  void* v_cache;
+  int64_t kc_stride_b, kc_stride_s, kc_stride_h, vc_stride_b, vc_stride_s, vc_stride_h;
+  int32_t batch, heads, kv_heads, head_dim;
+  int32_t group_size;
+  int32_t reserved;
+  int64_t cache_rows;       /* capacity: a row index at or past it is never written */
+  const float* inv_freq;    /* (head_dim/2,) fp32 device array */
+  const int64_t* state;     /* device, JL_STEP_STATE_WORDS words */
+} jl_decode_append_args;
+
+int jl_decode_append(const jl_decode_append_args* args, void* cuda_stream);
 
 #ifdef __cplusplus
 }

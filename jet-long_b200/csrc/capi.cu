@@ -10,6 +10,8 @@ int launch_merge(const jl_merge_args* a, cudaStream_t stream);
 int launch_rotate(const jl_rotate_args* a, cudaStream_t stream);
 int launch_norm_rope(const jl_norm_rope_args* a, cudaStream_t stream);
 int launch_rmsnorm(const jl_rmsnorm_args* a, cudaStream_t stream);
+int launch_step_advance(const jl_step_advance_args* a, cudaStream_t stream);
+int launch_decode_append(const jl_decode_append_args* a, cudaStream_t stream);
 int launch_decode(const jl_decode_args* a, cudaStream_t stream);
 int launch_decode_static(const jl_decode_args* a, cudaStream_t stream);
 size_t decode_static_scratch_bytes();
@@ -129,6 +131,20 @@ int jl_norm_rope(const jl_norm_rope_args* args, void* cuda_stream) {
   int rc = jl::check_device_arch();
   if (rc != JL_OK) return rc;
   return jl::launch_norm_rope(args, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int jl_step_advance(const jl_step_advance_args* args, void* cuda_stream) {
+  if (args == nullptr) return jl::fail(JL_ERR_BAD_ARG, "jl_step_advance: args is NULL");
+  int rc = jl::check_device_arch();
+  if (rc != JL_OK) return rc;
+  return jl::launch_step_advance(args, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int jl_decode_append(const jl_decode_append_args* args, void* cuda_stream) {
+  if (args == nullptr) return jl::fail(JL_ERR_BAD_ARG, "jl_decode_append: args is NULL");
+  int rc = jl::check_device_arch();
+  if (rc != JL_OK) return rc;
+  return jl::launch_decode_append(args, static_cast<cudaStream_t>(cuda_stream));
 }
 
 size_t jl_decode_workspace_bytes(int32_t batch, int32_t heads, int32_t head_dim, int32_t max_splits) {

@@ -25,6 +25,7 @@ struct DecSeg {
   const __nv_bfloat16* v;
   int64_t ks_b, ks_s, ks_h, vs_b, vs_s, vs_h;
   const int32_t* len_dev;
+  const int64_t* row0_dev;
   int64_t pos0, pos_block, pos_block_stride;
   int len, q_class, rotate;
 };
@@ -67,15 +68,22 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) decode_kernel(const DecPara
 
   // ---- this CTA's key range in the virtual concatenation of the segments ----
   int seg_len[JL_MAX_SEGMENTS];
+  int64_t seg_row0[JL_MAX_SEGMENTS];      // first row of the segment inside its k / v tensors (device-side shift)
   int64_t total = 0;
 #pragma unroll
   for (int s = 0; s < JL_MAX_SEGMENTS; ++s) {
     int len = 0;
+    int64_t r0 = 0;
     if (s < p.n_seg) {
       len = p.seg[s].len;
       if (p.seg[s].len_dev != nullptr) len = min(len, max(p.seg[s].len_dev[b], 0));
+      if (p.seg[s].row0_dev != nullptr) {        // never read past the rows the host described
+        r0 = min(max(*p.seg[s].row0_dev, static_cast<int64_t>(0)), static_cast<int64_t>(p.seg[s].len));
+        len = min(len, static_cast<int>(p.seg[s].len - r0));
+      }
     }
     seg_len[s] = len;
+    seg_row0[s] = r0;
     total += len;
   }
   int64_t per = (total + p.num_splits - 1) / p.num_splits;
@@ -107,6 +115,12 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) decode_kernel(const DecPara
     row0 = seg_lo[s] + t * kDecTile;
     valid = min(kDecTile, seg_hi[s] - row0);
   };
+  auto shift_of = [&](int s) {
+    int64_t r0 = seg_row0[0];
+#pragma unroll
+    for (int i = 1; i < JL_MAX_SEGMENTS; ++i) r0 = s == i ? seg_row0[i] : r0;
+    return r0;
+  };
 
   // Each warp copies rows [16*warp, 16*warp+16) of a tile: lane -> (row = lane/16 + 2*j, chunk = lane%16).
   auto issue = [&](int t) {
@@ -114,6 +128,7 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) decode_kernel(const DecPara
       int s, row0, valid;
       locate(t, s, row0, valid);
       const DecSeg& sg = p.seg[s];
+      const int64_t shift = shift_of(s);
       const int stage = t % kDecStages;
       const __nv_bfloat16* kb = sg.k + b * sg.ks_b + kvh * sg.ks_h;
       const __nv_bfloat16* vb = sg.v + b * sg.vs_b + kvh * sg.vs_h;
@@ -123,7 +138,7 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) decode_kernel(const DecPara
       for (int j = 0; j < 8; ++j) {
         const int r = warp * 16 + (lane >> 4) + 2 * j;
         const bool ok = r < valid;
-        const int64_t grow = ok ? row0 + r : row0;      // keep the address in range when zero-filling
+        const int64_t grow = shift + (ok ? row0 + r : row0);      // keep the address in range when zero-filling
         cp_async_16(ks + swz256(r, chunk), kb + grow * sg.ks_s + chunk * 8, ok);
         cp_async_16(vs + swz256(r, chunk), vb + grow * sg.vs_s + chunk * 8, ok);
       }
@@ -178,7 +193,8 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) decode_kernel(const DecPara
       // its rotation partner d + 64 sits in kf[kk + 4][i].
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        const int64_t pos = key_position(row0 + warp * 16 + half * 8 + (lane >> 2), sg.pos0, sg.pos_block, sg.pos_block_stride);
+        const int64_t pos = key_position(shift_of(s) + row0 + warp * 16 + half * 8 + (lane >> 2), sg.pos0, sg.pos_block,
+                                         sg.pos_block_stride);
         const float tf = static_cast<float>(pos / p.group_size - pos);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
@@ -386,6 +402,7 @@ int launch_decode(const jl_decode_args* a, cudaStream_t stream) {
     d.ks_b = g.k_stride_b; d.ks_s = g.k_stride_s; d.ks_h = g.k_stride_h;
     d.vs_b = g.v_stride_b; d.vs_s = g.v_stride_s; d.vs_h = g.v_stride_h;
     d.len_dev = g.len_dev;
+    d.row0_dev = g.row0_dev;
     d.pos0 = g.pos0;
     d.pos_block = g.pos_block > 0 ? g.pos_block : 0;
     d.pos_block_stride = g.pos_block_stride;

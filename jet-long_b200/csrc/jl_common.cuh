@@ -88,4 +88,22 @@ __device__ __host__ __forceinline__ int64_t key_position(int64_t j, int64_t pos0
   return pos0 + (j / block) * block_stride + (j % block);
 }
 
+// One head row of "per-head Qwen3RMSNorm -> base RoPE", for the lane that holds dims (2l, 2l+1) in lo and
+// (64+2l, 64+2l+1) in hi.  Qwen3RMSNorm rounds the normalised value to bf16 before the (bf16) weight
+// multiply; the rotation is fp32 and the caller rounds once when it stores.  Shared by the prefill-side
+// pass and the decode-step kernel so that both produce the same bits.
+__device__ __forceinline__ void norm_rope_head(float2 lo, float2 hi, float2 w_lo, float2 w_hi, float eps,
+                                               float sb0, float cb0, float sb1, float cb1,
+                                               float& bl0, float& bl1, float& bh0, float& bh1) {
+  float ss = lo.x * lo.x + lo.y * lo.y + hi.x * hi.x + hi.y * hi.y;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  const float r = rsqrtf(ss * (1.f / 128.f) + eps);
+  auto rb = [](float v) { return __bfloat162float(__float2bfloat16(v)); };
+  const float y0 = rb(w_lo.x * rb(lo.x * r)), y1 = rb(w_lo.y * rb(lo.y * r));
+  const float z0 = rb(w_hi.x * rb(hi.x * r)), z1 = rb(w_hi.y * rb(hi.y * r));
+  bl0 = y0 * cb0 - z0 * sb0; bl1 = y1 * cb1 - z1 * sb1;
+  bh0 = z0 * cb0 + y0 * sb0; bh1 = z1 * cb1 + y1 * sb1;
+}
+
 }  // namespace jl

@@ -129,16 +129,8 @@ __global__ void __launch_bounds__(256) norm_rope_kernel(const NormRopeParams p) 
     for (int h = 0; h < p.heads; ++h) {
       const float2 lo = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(xr + h * p.xs_h + 2 * lane));
       const float2 hi = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(xr + h * p.xs_h + 64 + 2 * lane));
-      float ss = lo.x * lo.x + lo.y * lo.y + hi.x * hi.x + hi.y * hi.y;
-#pragma unroll
-      for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
-      const float r = rsqrtf(ss * (1.f / kHeadDim) + p.eps);
-      // Qwen3RMSNorm: the normalised value is rounded to bf16 before the (bf16) weight multiply
-      auto rb = [](float v) { return __bfloat162float(__float2bfloat16(v)); };
-      const float y0 = rb(w_lo.x * rb(lo.x * r)), y1 = rb(w_lo.y * rb(lo.y * r));
-      const float z0 = rb(w_hi.x * rb(hi.x * r)), z1 = rb(w_hi.y * rb(hi.y * r));
-      const float bl0 = y0 * cb0 - z0 * sb0, bl1 = y1 * cb1 - z1 * sb1;      // base-rotated, fp32
-      const float bh0 = z0 * cb0 + y0 * sb0, bh1 = z1 * cb1 + y1 * sb1;
+      float bl0, bl1, bh0, bh1;
+      norm_rope_head(lo, hi, w_lo, w_hi, p.eps, sb0, cb0, sb1, cb1, bl0, bl1, bh0, bh1);
       *reinterpret_cast<uint32_t*>(br + h * p.bs_h + 2 * lane) = pack_bf16x2(bl0, bl1);
       *reinterpret_cast<uint32_t*>(br + h * p.bs_h + 64 + 2 * lane) = pack_bf16x2(bh0, bh1);
       if (gr != nullptr) {

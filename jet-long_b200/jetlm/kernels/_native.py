@@ -46,7 +46,7 @@ class KvSegment(C.Structure):
         ("v_stride_b", C.c_int64), ("v_stride_s", C.c_int64), ("v_stride_h", C.c_int64),
         ("len_dev", C.c_void_p), ("pos0", C.c_int64),
         ("len", C.c_int32), ("q_class", C.c_int32), ("rotate", C.c_int32), ("reserved", C.c_int32),
-        ("pos_block", C.c_int64), ("pos_block_stride", C.c_int64),
+        ("pos_block", C.c_int64), ("pos_block_stride", C.c_int64), ("row0_dev", C.c_void_p),
     ]
 
 
@@ -99,6 +99,29 @@ class RmsNormArgs(C.Structure):
                 ("out", C.c_void_p), ("rows", C.c_int64), ("hidden", C.c_int32), ("eps", C.c_float)]
 
 
+JL_STEP_STATE_WORDS = 5
+
+
+class StepAdvanceArgs(C.Structure):
+    _fields_ = [("state", C.c_void_p), ("lens", C.c_void_p), ("batch", C.c_int32), ("rank", C.c_int32),
+                ("world", C.c_int32), ("reserved", C.c_int32), ("block", C.c_int64), ("w_0", C.c_int64)]
+
+
+class DecodeAppendArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p),
+        ("q_stride_b", C.c_int64), ("q_stride_h", C.c_int64), ("k_stride_b", C.c_int64), ("k_stride_h", C.c_int64),
+        ("v_stride_b", C.c_int64), ("v_stride_h", C.c_int64),
+        ("q_weight", C.c_void_p), ("k_weight", C.c_void_p), ("q_eps", C.c_float), ("k_eps", C.c_float),
+        ("q_base", C.c_void_p), ("q_group", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p),
+        ("kc_stride_b", C.c_int64), ("kc_stride_s", C.c_int64), ("kc_stride_h", C.c_int64),
+        ("vc_stride_b", C.c_int64), ("vc_stride_s", C.c_int64), ("vc_stride_h", C.c_int64),
+        ("batch", C.c_int32), ("heads", C.c_int32), ("kv_heads", C.c_int32), ("head_dim", C.c_int32),
+        ("group_size", C.c_int32), ("reserved", C.c_int32), ("cache_rows", C.c_int64),
+        ("inv_freq", C.c_void_p), ("state", C.c_void_p),
+    ]
+
+
 # Every symbol include/jetlong_b200.h declares: (name, restype, argtypes)
 EXPORTS = [
     ("jl_version", C.c_int, []),
@@ -115,6 +138,8 @@ EXPORTS = [
     ("jl_rotate", C.c_int, [C.POINTER(RotateArgs), C.c_void_p]),
     ("jl_norm_rope", C.c_int, [C.POINTER(NormRopeArgs), C.c_void_p]),
     ("jl_rmsnorm", C.c_int, [C.POINTER(RmsNormArgs), C.c_void_p]),
+    ("jl_step_advance", C.c_int, [C.POINTER(StepAdvanceArgs), C.c_void_p]),
+    ("jl_decode_append", C.c_int, [C.POINTER(DecodeAppendArgs), C.c_void_p]),
 ]
 
 _LIB = None

@@ -62,8 +62,9 @@ def _st(t: torch.Tensor, i: int) -> int:
 
 # Instrumentation used by the benchmark: kernel launches issued through this module, and (when a list
 # is installed with set_event_sink) a CUDA event pair around every attention kernel launch.
-LAUNCHES = {"jl_prefill": 0, "jl_decode": 0, "jl_merge": 0, "jl_rotate": 0, "jl_norm_rope": 0, "jl_rmsnorm": 0}
-KERNELS_PER_CALL = {"jl_prefill": 1, "jl_decode": 2, "jl_merge": 1, "jl_rotate": 1, "jl_norm_rope": 1, "jl_rmsnorm": 1}
+KERNELS_PER_CALL = {"jl_prefill": 1, "jl_decode": 2, "jl_merge": 1, "jl_rotate": 1, "jl_norm_rope": 1, "jl_rmsnorm": 1,
+                    "jl_step_advance": 1, "jl_decode_append": 1}
+LAUNCHES = {name: 0 for name in KERNELS_PER_CALL}
 _EVENT_SINK: Optional[list] = None
 
 
@@ -411,6 +412,7 @@ class KvSegment:
     len_dev: Optional[torch.Tensor] = None   # optional int32 (B,) valid lengths
     pos_block: int = 0         # > 0: rows are a block-cyclic stripe, position = pos0 + (row // pos_block) * stride + row % pos_block
     pos_block_stride: int = 0
+    row0_dev: Optional[torch.Tensor] = None  # optional int64 device scalar: the segment starts at that row of k / v
 
 
 def decode_segments(q_ops: Sequence[Optional[torch.Tensor]], segments: Sequence[KvSegment], *,
@@ -476,6 +478,10 @@ def decode_segments(q_ops: Sequence[Optional[torch.Tensor]], segments: Sequence[
             g.len_dev = keep[-1].data_ptr()
         g.pos0, g.len, g.q_class, g.rotate = int(s.pos0), int(s.k.shape[1]), int(s.q_class), int(bool(s.rotate))
         g.pos_block, g.pos_block_stride = int(s.pos_block), int(s.pos_block_stride)
+        if s.row0_dev is not None:
+            if s.row0_dev.numel() != 1 or s.row0_dev.dtype != torch.int64 or s.row0_dev.device != q0.device:
+                raise ValueError(f"{op}: segment row offset must be one int64 on {q0.device}")
+            g.row0_dev = s.row0_dev.data_ptr()
         total += int(s.k.shape[1])
     if H % Hk != 0:
         raise ValueError(f"{op}: query heads must be divisible by kv heads")
@@ -502,6 +508,83 @@ def decode_segments(q_ops: Sequence[Optional[torch.Tensor]], segments: Sequence[
     with torch.cuda.device(q0.device):
         _timed_call("jl_decode", lambda: lib.jl_decode(C.byref(a), _stream()), dict(B=B, keys=total, Hk=Hk))
     return (out, lse) if return_lse else out
+
+
+class StepState:
+    """Decode-step facts kept on the device (see jl_step_advance): `state` int64 (5,) =
+    [pos, row, own, n_far, n_near] and `lens` int32 (2, B) = [n_far] * B, [n_near] * B.  Kernels whose host
+    arguments never change read them, so one captured CUDA graph serves every new token."""
+
+    def __init__(self, batch: int, device, w_0: int, shard=None):
+        self.batch, self.w_0, self.shard = int(batch), int(w_0), shard
+        self.state = torch.zeros(N.JL_STEP_STATE_WORDS, dtype=torch.int64, device=device)
+        self.lens = torch.zeros(2, batch, dtype=torch.int32, device=device)
+
+    def set_next_position(self, pos: int) -> None:
+        """The next advance() will describe the token at absolute position `pos`."""
+        self.state[0] = int(pos) - 1
+
+    def advance(self) -> None:
+        sh = self.shard
+        a = N.StepAdvanceArgs(self.state.data_ptr(), self.lens.data_ptr(), self.batch,
+                              sh.rank if sh is not None else 0, sh.world if sh is not None else 1, 0,
+                              sh.block if sh is not None else 1, self.w_0)
+        with torch.cuda.device(self.state.device):
+            _timed_call("jl_step_advance", lambda: N.lib().jl_step_advance(C.byref(a), _stream()))
+
+    # views the kernels take
+    @property
+    def position(self) -> torch.Tensor:
+        return self.state[0:1]
+
+    @property
+    def n_far(self) -> torch.Tensor:
+        return self.state[3:4]
+
+    @property
+    def far_lens(self) -> torch.Tensor:
+        return self.lens[0]
+
+    @property
+    def near_lens(self) -> torch.Tensor:
+        return self.lens[1]
+
+
+def decode_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_weight: torch.Tensor, k_weight: torch.Tensor,
+                  inv_freq: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, step: StepState, *,
+                  q_eps: float, k_eps: float, group_size: int = 1):
+    """One launch between the projections and the attention of a decode step: per-head RMSNorm + RoPE of
+    q (B,1,H,D) and k (B,1,Hk,D) at the device-side position, the regrouped query when group_size > 1, and
+    the write of the new key / value into row step.state[1] of k_cache / v_cache (B,rows,Hk,D) on the rank
+    that owns the position.  Returns (q_base, q_group), each (B,1,H,D); q_group is q_base when group_size == 1."""
+    op = "decode_append"
+    for name, t in (("q", q), ("k", k), ("v", v), ("k_cache", k_cache), ("v_cache", v_cache)):
+        _check_view(op, name, t)
+        if t.dtype not in _SUPPORTED_DTYPES:
+            raise ValueError(f"{op}: {name} must be torch.bfloat16")
+    _require_arch(op, q.device)
+    B, one, H, D = q.shape
+    Hk = k.shape[2]
+    if one != 1 or k.shape != (B, 1, Hk, D) or v.shape != (B, 1, Hk, D):
+        raise ValueError(f"{op}: expects q (B,1,H,D) and k, v (B,1,Hk,D)")
+    if k_cache.shape[0] != B or k_cache.shape[2:] != (Hk, D) or v_cache.shape != k_cache.shape:
+        raise ValueError(f"{op}: caches must be (B, rows, Hk, D)")
+    for name, w in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if w.numel() != D or not w.is_contiguous() or w.dtype != q.dtype:
+            raise ValueError(f"{op}: {name} must be a contiguous ({D},) tensor of the query dtype")
+    inv_freq = inv_freq.to(device=q.device, dtype=torch.float32).contiguous()
+    q_base = torch.empty(B, 1, H, D, dtype=q.dtype, device=q.device)
+    q_group = torch.empty(B, 1, H, D, dtype=q.dtype, device=q.device) if group_size > 1 else None
+    a = N.DecodeAppendArgs(q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                           _st(q, 0), _st(q, 2), _st(k, 0), _st(k, 2), _st(v, 0), _st(v, 2),
+                           q_weight.data_ptr(), k_weight.data_ptr(), float(q_eps), float(k_eps),
+                           q_base.data_ptr(), q_group.data_ptr() if q_group is not None else None,
+                           k_cache.data_ptr(), v_cache.data_ptr(),
+                           _st(k_cache, 0), _st(k_cache, 1), _st(k_cache, 2), _st(v_cache, 0), _st(v_cache, 1), _st(v_cache, 2),
+                           B, H, Hk, D, int(group_size), 0, int(k_cache.shape[1]), inv_freq.data_ptr(), step.state.data_ptr())
+    with torch.cuda.device(q.device):
+        _timed_call("jl_decode_append", lambda: N.lib().jl_decode_append(C.byref(a), _stream()))
+    return q_base, (q_group if q_group is not None else q_base)
 
 
 def _require_output(op, name, t, shape, dtype, device):

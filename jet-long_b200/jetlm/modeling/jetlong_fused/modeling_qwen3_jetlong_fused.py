@@ -60,6 +60,7 @@ class BifocalPlan:
     has_any_pad: bool        # a left-padded batch (unsupported by the fused kernels)
     token_shard: object = None   # SequenceShard when this rank holds a block-cyclic stripe of the KV cache
     replicated: bool = False     # sharded cache, but every rank runs all tokens of this call (decode)
+    step: object = None          # ops.StepState: positions and cache rows come from device memory (graph replay)
 
 
 class Qwen3JetLongFusedRotaryEmbedding(Qwen3RotaryEmbedding):
@@ -170,6 +171,17 @@ class Qwen3JetLongFusedAttention(nn.Module):
             raise RuntimeError("JetLong backend 'fused' is inference-only")
         w_0 = self.jetlong_w_0
         q_eps, k_eps = self.q_norm.variance_epsilon, self.k_norm.variance_epsilon
+
+        if plan.step is not None:
+            # decode step whose position, cache row and class lengths live on the device: two launches
+            # (norm -> RoPE -> cache write, attention) with token-independent host arguments
+            slot = past_key_values.layers[self.layer_idx]
+            q_base, q_group = ops.decode_append(q, k, v, self.q_norm.weight, self.k_norm.weight, inv_freq,
+                                                slot.keys, slot.values, plan.step, q_eps=q_eps, k_eps=k_eps,
+                                                group_size=group)
+            attn = backend.fused_jetlong_decode_step(q_base, q_group, slot.keys, slot.values, step=plan.step,
+                                                     inv_freq=inv_freq, group_size=group, softmax_scale=self.scaling)
+            return self.o_proj(attn.reshape(*out_shape, -1)), None
 
         if plan.token_shard is not None:
             return self._token_sharded(q, k, v, plan, group, inv_freq, past_key_values, out_shape, backend, ops)
@@ -388,6 +400,20 @@ class Qwen3JetLongFusedModel(Qwen3PreTrainedModel):
                                        past_key_values=past_key_values if use_cache else None)
 
 
+    def decode_step(self, token, cache, step, group: int):
+        """One-token forward with no host-side dependence on the position: `step` (ops.StepState) was advanced
+        on the device for this token, `cache` is the BifocalKVCache the step was built for and `group` the
+        group size G of this call.  Safe to capture in a CUDA graph.  Returns the final hidden state (B,1,hidden);
+        the caller commits the token to the cache's host-side counters."""
+        inv_freq = self.rotary_emb.inv_freq.to(device=token.device, dtype=torch.float32)
+        plan = BifocalPlan(int(group), -1, -1, False, step.shard, True, step)
+        position_embeddings = (None, None, int(group), inv_freq, None, plan)
+        hidden = self.embed_tokens(token)
+        for layer in self.layers[: self.config.num_hidden_layers]:
+            hidden = layer(hidden, attention_mask=None, position_embeddings=position_embeddings,
+                           position_ids=None, past_key_values=cache, use_cache=True)
+        return self.norm(hidden)
+
     def _forward_token_sharded(self, input_ids, past_key_values, use_cache, shard, **kwargs) -> BaseModelOutputWithPast:
         """Sequence-parallel forward; `input_ids` is the whole (B, S) call on every rank.
         S a multiple of world * block (a prefill chunk): this rank embeds, projects and stores only its
@@ -473,7 +499,8 @@ class Qwen3JetLongFusedForCausalLM(Qwen3PreTrainedModel, GenerationMixin):
 
 
     @torch.no_grad()
-    def generate_long(self, input_ids, max_new_tokens: int, chunk_tokens: int = 32768, past_key_values=None):
+    def generate_long(self, input_ids, max_new_tokens: int, chunk_tokens: int = 32768, past_key_values=None,
+                      cuda_graph: bool = False):
         """Greedy continuation of a long prompt: chunked prefill into a preallocated BifocalKVCache, then
         one-token steps on the same cache.  G is recomputed per call from the length reached so far, as in
         the reference (:145-158), so the result depends on the chunk schedule exactly as the reference's does.
@@ -481,7 +508,8 @@ class Qwen3JetLongFusedForCausalLM(Qwen3PreTrainedModel, GenerationMixin):
         With `model.token_sharded = True` and sequence sharding configured, every rank calls this with the
         same arguments: each keeps a block-cyclic stripe of the cache (the prompt length and chunk_tokens
         must then be multiples of world * block) and all ranks return the same tokens.
-        Returns (B, max_new_tokens) token ids."""
+        cuda_graph: replay one captured graph per decoded token (jetlm.kernels.decode_graph) instead of
+        launching the step from Python.  Returns (B, max_new_tokens) token ids."""
         import torch.distributed as dist
         from jetlm.kernels import cute_jetlong_backend as backend
         from jetlm.kernels.kv_cache import BifocalKVCache
@@ -502,6 +530,12 @@ class Qwen3JetLongFusedForCausalLM(Qwen3PreTrainedModel, GenerationMixin):
         if shard is not None:        # the prompt's last block lives on the last rank
             dist.broadcast(token, src=rank_of(shard.world - 1), group=shard.group)
         out = [token]
+        if cuda_graph and max_new_tokens > 1:
+            from jetlm.kernels.decode_graph import GraphedDecodeStep
+            step = GraphedDecodeStep(self, past_key_values)
+            for i in range(max_new_tokens - 1):
+                out.append(step(token if i == 0 else None).clone())
+            return torch.cat(out, dim=1)
         for _ in range(max_new_tokens - 1):
             hidden = self.model(input_ids=token, past_key_values=past_key_values, use_cache=True).last_hidden_state
             token = self.lm_head(hidden[:, -1:, :]).argmax(-1)

@@ -104,6 +104,8 @@ def _worker(rank, world, port, results):
             cache = BifocalKVCache(cfg, ids2.shape[1], device="cuda", dtype=torch.bfloat16, shard=shard)
             pre_n, dec_n = drive(cache)
             toks_n = model.generate_long(ids2[:, : 3 * chunk], max_new_tokens=4, chunk_tokens=chunk)
+            toks_g = model.generate_long(ids2[:, : 3 * chunk], max_new_tokens=4, chunk_tokens=chunk, cuda_graph=True)
+            assert toks_g.tolist() == toks_n.tolist(), (rank, toks_g.tolist(), toks_n.tolist())
             gathered = [torch.empty_like(toks_n) for _ in range(world)]
             dist.all_gather(gathered, toks_n)
             be.configure_sequence_sharding(None)
