@@ -243,6 +243,48 @@ def fused_jetlong_decode_step(query_base, query_group, key_rows, value_rows, *, 
     return out
 
 
+# ---------------------------------------------------------------------------------------------------
+# jetlong_freq: same band map, far class rotated per frequency by delta_inv_freq, softmax with a temperature
+# ---------------------------------------------------------------------------------------------------
+
+_NO_GROUPING = 1 << 30      # floor(p / G) = 0 for every position: the in-kernel regroup angle becomes -p * inv_freq
+
+
+def fused_jetlong_freq_prefill(query_base, key_base, value, *, delta_inv_freq, attn_scale: float, seqstart_q: int,
+                               window_size_left: int):
+    """PATH 2 of the reference's jetlong_freq attention (modeling_qwen3_jetlong_freq.py:380-443) in one
+    kernel pass instead of three flash-attn calls and a subtractive merge: base scores where
+    0 <= pq - pk <= w_0, corrected scores elsewhere, one softmax with scale attn_scale.
+    query_base (B,H,S,D) / key_base, value (B,Hk,Skv,D): base-rotated views, keys from position 0.
+    Returns (B,S,H,D).  (Queries at positions <= w_0 have no far keys, so their corrected operand is never
+    read; it is formed at pq - w_0 without the reference's clamp at 0.)"""
+    t = lambda x: x.transpose(1, 2)
+    w_0 = int(window_size_left)
+    like = lambda x: torch.empty_strided(x.shape, x.stride(), dtype=x.dtype, device=x.device)   # operands share strides
+    q_dist = ops.rope_rotate(t(query_base), delta_inv_freq, pos0=int(seqstart_q), add=-w_0, out=like(t(query_base)))
+    k_yarn = ops.rope_rotate(t(key_base), delta_inv_freq, pos0=0, out=like(t(key_base)))
+    return ops.posmap_prefill([t(query_base), q_dist], [t(key_base), k_yarn], t(value), pmap=ops.PositionMap.jetlong(w_0),
+                              q_pos0=int(seqstart_q), softmax_scale=float(attn_scale), return_lse=False)
+
+
+def fused_jetlong_freq_decode(query_base, key_cache, value_cache, *, delta_inv_freq, attn_scale: float, max_q_pos: int,
+                              window_size_left: int, return_lse: bool = False):
+    """PATH 3 (modeling_qwen3_jetlong_freq.py:445-503) straight off the base-rotated (B,Hk,S,D) cache:
+    keys [0, boundary) are corrected inside the kernel while they stream (angle p * delta_inv_freq),
+    keys [boundary, S) are scored as stored; boundary = max(max_q_pos - w_0, 0).  query_base (B,1,H,D)."""
+    boundary = max(int(max_q_pos) - int(window_size_left), 0)
+    kc, vc = key_cache.transpose(1, 2), value_cache.transpose(1, 2)
+    q_dist = ops.rope_rotate(query_base, delta_inv_freq, pos0=boundary) if boundary > 0 else query_base
+    segs = []
+    if boundary > 0:
+        segs.append(ops.KvSegment(kc[:, :boundary], vc[:, :boundary], q_class=1, rotate=True, pos0=0))
+    if boundary < kc.shape[1]:
+        segs.append(ops.KvSegment(kc[:, boundary:], vc[:, boundary:], q_class=0))
+    neg = -delta_inv_freq.to(device=query_base.device, dtype=torch.float32)
+    return ops.decode_segments([query_base, q_dist], segs, inv_freq=neg, group_size=_NO_GROUPING,
+                               softmax_scale=float(attn_scale), return_lse=return_lse)
+
+
 def _decode_range(query_base, query_group, kc, vc, b, pos0, inv_freq, group_size, softmax_scale, return_lse,
                   out=None, lse=None, kg=None):
     """Decode over rows of a (B,S,Hk,D) cache view whose row 0 has absolute position pos0; rows < b are far."""

@@ -273,9 +273,10 @@ def main():
     gen_rotate(ref_tests, ref_model, "rotate.npz", seed=5, B=1, S=96, H=2, D=128)
     gen_merge(ref_decode, ref_tests, "merge_nway.npz", seed=13, N=5, B=2, S=3, H=4, D=128)
     gen_model(root, ref_tests, "model_tiny.npz", seed=123, S_prefill=200, n_decode=3, w=64, w0=16)
-    from make_golden_posmaps import gen_selfext, gen_dca  # noqa: E402  (sibling script)
+    from make_golden_posmaps import gen_selfext, gen_dca, gen_jetlong_freq  # noqa: E402  (sibling script)
     gen_selfext(root, "selfext_tiny.npz")
     gen_dca(root, "dca_tiny.npz")
+    gen_jetlong_freq(root, "jetlong_freq_tiny.npz")
     print("wrote fixtures to", HERE)
 
 

@@ -126,6 +126,25 @@ def test_posmap_dca(golden):
     _posmap_case(g, "dca", dict(chunk_size=g.meta["chunk_size"], local_window=g.meta["local_window"]))
 
 
+def test_jetlong_freq_against_the_reference_module(golden):
+    """Fixture: the reference's jetlong_freq attention module (fp32, eager stand-in for its flash-attn calls)."""
+    g = golden("jetlong_freq_tiny.npz")
+    S, w, w0 = g.meta["S"], g.meta["w"], g.meta["w_0"]
+    inv = g["inv_freq"]
+    ramp = orc.yarn_ramp(128, w, 1.0e6)
+    _close(ramp, g["ntk_ramp"], 1e-7)
+    q, k, v = g["q_raw"], g["k_raw"], g["v"]
+    pos = torch.arange(S + 1).view(1, -1)
+    for tag, l_curr, qs, ks, want in (("prefill", S, slice(0, S), slice(0, S), g["out_prefill"]),
+                                      ("decode", S + 1, slice(S, S + 1), slice(0, S + 1), g["out_decode"])):
+        delta, scale = orc.jetlong_freq_params(l_curr, w, w0, inv, ramp)
+        _close(delta, g[f"delta_inv_freq_{tag}"], 1e-9)
+        assert abs(scale - g.meta[f"attn_scale_{tag}"]) < 1e-7
+        out, _ = orc.jetlong_freq_attention(q[:, qs], k[:, ks], v[:, ks], q_positions=pos[:, qs], k_positions=pos[:, ks],
+                                            w_0=w0, inv_freq=inv, delta_inv_freq=delta, scale=scale)
+        _close(out, want, 2e-5)
+
+
 def test_posmap_jetlong_equals_two_branch(golden):
     g = golden("model_tiny.npz")
     S, w, w0 = g.meta["S_prefill"], g.meta["w"], g.meta["w0"]

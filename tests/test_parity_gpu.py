@@ -469,6 +469,47 @@ def test_posmap_dca(golden):
     _check(out, lse, eo, el, "dca decode kernel")
 
 
+def test_jetlong_freq_prefill_and_decode(golden):
+    """jetlong_freq through the band map: operands from jl_rotate with delta_inv_freq, one kernel pass with
+    the temperature scale; decode corrects the far keys in-kernel.  Checked against the oracle on the very
+    bf16 operands and, end to end, against the reference module's fp32 output."""
+    from jetlm.kernels import cute_jetlong_backend as be
+    g = golden("jetlong_freq_tiny.npz")
+    ops = _ops()
+    S, w, w0 = g.meta["S"], g.meta["w"], g.meta["w_0"]
+    inv = g["inv_freq"]
+    ramp = orc.yarn_ramp(128, w, 1.0e6)
+    pos = torch.arange(S + 1).view(1, -1)
+    q, k, v = g["q_raw"].bfloat16(), g["k_raw"].bfloat16(), g["v"].bfloat16()
+    dq, dk, dv = _dev(q, k, v)
+    qb = ops.rope_base(dq, inv.cuda())                      # (B,S+1,H,D) base-rotated, as the model caches them
+    kb = ops.rope_base(dk, inv.cuda())
+    bhsd = lambda x: x.transpose(1, 2)
+    # prefill of S tokens
+    delta, scale = orc.jetlong_freq_params(S, w, w0, inv, ramp)
+    out = be.fused_jetlong_freq_prefill(bhsd(qb[:, :S]), bhsd(kb[:, :S]), bhsd(dv[:, :S]), delta_inv_freq=delta.cuda(),
+                                        attn_scale=scale, seqstart_q=0, window_size_left=w0)
+    qd = orc.rotate_bshd(qb[:, :S].float().cpu(), (pos[:, :S] - w0), delta)
+    ky = orc.rotate_bshd(kb[:, :S].float().cpu(), pos[:, :S], delta)
+    eo, _ = orc.posmap_attention_from_operands("jetlong", [qb[:, :S].cpu(), qd.bfloat16()], [kb[:, :S].cpu(), ky.bfloat16()],
+                                               v[:, :S].bfloat16(), q_positions=pos[0, :S], k_positions=pos[0, :S],
+                                               params=dict(w_0=w0, G=1), scale=scale)
+    _check(out, None, eo, None, "jetlong_freq prefill")
+    d, cos = orc.compare(out.float().cpu(), g["out_prefill"])
+    assert d < 3e-2 and cos > 0.999, (d, cos)
+    # decode of token S over S + 1 cached keys
+    delta, scale = orc.jetlong_freq_params(S + 1, w, w0, inv, ramp)
+    out, lse = be.fused_jetlong_freq_decode(qb[:, S:], bhsd(kb), bhsd(dv), delta_inv_freq=delta.cuda(), attn_scale=scale,
+                                            max_q_pos=S, window_size_left=w0, return_lse=True)
+    b = S - w0
+    qd = orc.rotate_bshd(qb[:, S:].float().cpu(), torch.tensor([[b]]), delta).bfloat16()
+    ky = orc.rotate_bshd(kb[:, :b].float().cpu(), pos[:, :b], delta)
+    eo, el = orc.jetlong_decode(qb[:, S:].cpu(), qd, kb[:, b:].cpu(), v[:, b:].bfloat16(), ky, v[:, :b].bfloat16(), scale=scale)
+    _check(out, lse, eo, el, "jetlong_freq decode")
+    d, cos = orc.compare(out.float().cpu(), g["out_decode"])
+    assert d < 3e-2 and cos > 0.999, (d, cos)
+
+
 # ------------------------------------------------------------------------------------------------
 # size-independent properties at full benchmark sizes
 # ------------------------------------------------------------------------------------------------
