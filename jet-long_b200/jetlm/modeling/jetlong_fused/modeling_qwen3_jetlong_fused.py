@@ -57,10 +57,11 @@ class BifocalPlan:
     group_size: int          # G = ceil(L_curr / w)
     q_pos0: int              # absolute position of the first query token
     max_q_pos: int           # absolute position of the last query token
-    has_any_pad: bool        # a left-padded batch (unsupported by the fused kernels)
+    has_any_pad: bool        # a left-padded batch
     token_shard: object = None   # SequenceShard when this rank holds a block-cyclic stripe of the KV cache
     replicated: bool = False     # sharded cache, but every rank runs all tokens of this call (decode)
     step: object = None          # ops.StepState: positions and cache rows come from device memory (graph replay)
+    pads: Optional[list] = None  # left-padded batch: number of leading pad rows of every sample's cache
 
 
 class Qwen3JetLongFusedRotaryEmbedding(Qwen3RotaryEmbedding):
@@ -94,11 +95,12 @@ class Qwen3JetLongFusedRotaryEmbedding(Qwen3RotaryEmbedding):
             return cos, sin
         group = max(1, math.ceil(l_curr / self.jetlong_w))
         seq = position_ids.shape[-1]
-        has_pad = False
+        has_pad, pads = False, None
         if position_ids.shape[0] > 1 and kv_len is not None:
-            has_pad = bool(((kv_len - 1 - position_ids[:, -1]) > 0).any().item())
+            pads = (kv_len - 1 - position_ids[:, -1]).tolist()       # the last token of sample b sits at kv_len-1-pad_b
+            has_pad = any(n > 0 for n in pads)
         first = first_position if first_position is not None else max_position - seq + 1
-        plan = BifocalPlan(group, first, max_position, has_pad, token_shard, replicated)
+        plan = BifocalPlan(group, first, max_position, has_pad, token_shard, replicated, None, pads if has_pad else None)
         return cos, sin, group, self.inv_freq.to(device=x.device, dtype=torch.float32), position_ids, plan
 
 
@@ -192,6 +194,9 @@ class Qwen3JetLongFusedAttention(nn.Module):
             seen = slot.get_seq_length()
         else:
             seen = past_key_values.get_seq_length(self.layer_idx) if past_key_values is not None else 0
+        if plan.pads is not None and getattr(self.config, "jetlong_allow_left_padding", True):
+            return self._extended_left_padded(q, k, v, plan, group, inv_freq, past_key_values, slot, seen, out_shape,
+                                              backend, ops)
         regroup = group > 1          # G = 1 (inside the pretrained window): both classes score alike
         # q/k RMSNorm + base RoPE (+ regroup) in one fused pass each; K lands straight in its cache rows
         if regroup:
@@ -245,6 +250,66 @@ class Qwen3JetLongFusedAttention(nn.Module):
                 q_base, q_group, k_all.transpose(1, 2), v_all.transpose(1, 2), boundary=boundary, inv_freq=inv_freq,
                 group_size=group, softmax_scale=self.scaling, has_any_pad=plan.has_any_pad, training=self.training)
         return self.o_proj(attn.reshape(*out_shape, -1)), None
+
+    def _extended_left_padded(self, q, k, v, plan, group, inv_freq, past_key_values, slot, seen, out_shape, backend, ops):
+        """Left-padded batch (the reference's fused backend rejects it, cute_jetlong_backend.py:57-58, :124-125;
+        its non-fused method serves it through varlen attention, modeling_qwen3_jetlong.py:403-460).
+        Sample b carries plan.pads[b] leading pad rows in the cache; its real tokens are positions 0, 1, ... .
+        Every sample is attended on the row slices that skip its pads — views, no copies — with its own
+        position origin, so the kernels see B unpadded sequences.  Pad rows produce zeros."""
+        bsz, seq = out_shape
+        H, Hk, D = self.num_heads, self.num_kv_heads, self.head_dim
+        w_0 = self.jetlong_w_0
+        q_eps, k_eps = self.q_norm.variance_epsilon, self.k_norm.variance_epsilon
+        regroup = group > 1
+        pads = [int(n) for n in plan.pads]
+        first = [min(max(n - seen, 0), seq) for n in pads]          # first real query row of this call, per sample
+        q_base = torch.zeros(bsz, seq, H, D, dtype=q.dtype, device=q.device)
+        q_group = torch.zeros_like(q_base) if regroup else q_base
+        if slot is not None:
+            k_new, v_dst = slot.reserve(seq)
+        else:
+            k_new = torch.zeros(bsz, Hk, seq, D, dtype=k.dtype, device=k.device).transpose(1, 2)
+        for b, r0 in enumerate(first):
+            if r0 >= seq:
+                continue
+            pos0 = seen + r0 - pads[b]
+            kw = dict(group_size=group, out_group=q_group[b: b + 1, r0:]) if regroup else {}
+            ops.norm_rope(q[b: b + 1, r0:], self.q_norm.weight, inv_freq, eps=q_eps, pos0=pos0,
+                          out_base=q_base[b: b + 1, r0:], **kw)
+            ops.norm_rope(k[b: b + 1, r0:], self.k_norm.weight, inv_freq, eps=k_eps, pos0=pos0,
+                          out_base=k_new[b: b + 1, r0:])
+        if slot is not None:
+            v_dst.copy_(v)
+            slot.commit(seq)
+            k_all, v_all = slot.key_rows(), slot.value_rows()
+        elif past_key_values is not None:
+            k_all, v_all = past_key_values.update(k_new.transpose(1, 2), v.transpose(1, 2), self.layer_idx, {})
+            k_all, v_all = k_all.transpose(1, 2), v_all.transpose(1, 2)
+        else:
+            k_all, v_all = k_new, v
+        kv_len = k_all.shape[1]
+        attn = torch.zeros(bsz, seq, H, D, dtype=q.dtype, device=q.device)
+        pmap = ops.PositionMap.jetlong(w_0)
+        for b, r0 in enumerate(first):
+            if r0 >= seq:
+                continue
+            kb, vb = k_all[b: b + 1, pads[b]:], v_all[b: b + 1, pads[b]:]
+            qb, qg = q_base[b: b + 1, r0:], q_group[b: b + 1, r0:]
+            if seq > 1:
+                kg = kb
+                if regroup:
+                    kg = torch.empty_strided(kb.shape, kb.stride(), dtype=kb.dtype, device=kb.device)
+                    ops.rope_regroup(kb, inv_freq, group_size=group, pos0=0, out=kg)
+                out_b = ops.posmap_prefill([qb, qg], [kb, kg], vb, pmap=pmap, q_pos0=seen + r0 - pads[b],
+                                           softmax_scale=self.scaling, return_lse=False)
+            else:
+                boundary = max(kv_len - 1 - pads[b] - w_0, 0)
+                out_b = backend.fused_jetlong_decode_cache(
+                    qb, qg, kb.transpose(1, 2), vb.transpose(1, 2), boundary=boundary, inv_freq=inv_freq,
+                    group_size=group, softmax_scale=self.scaling, has_any_pad=False, training=self.training)
+            attn[b: b + 1, r0:] = out_b
+        return self.o_proj(attn.reshape(bsz, seq, -1)), None
 
     def _token_sharded(self, q, k, v, plan, group, inv_freq, past_key_values, out_shape, backend, ops):
         """Sequence-parallel attention over a cache of which this rank keeps a block-cyclic stripe.

@@ -173,3 +173,38 @@ def test_generate_long_equals_a_hand_rolled_greedy_loop(golden):
         toks.append(int(nxt))
         nxt = model(input_ids=nxt, past_key_values=cache, use_cache=True).logits[:, -1].argmax(-1, keepdim=True)
     assert out.tolist() == [toks]
+
+
+@torch.inference_mode()
+@pytest.mark.parametrize("static_cache", [False, True])
+def test_left_padded_batch_matches_unpadded_samples(golden, static_cache):
+    """A left-padded batch of two prompts (150 and 130 tokens; same G in every call) through chunked prefill
+    (100 + 50 rows) and two decode steps gives, on the real rows, the logits of each prompt run alone."""
+    from transformers import DynamicCache
+    from jetlm.kernels.kv_cache import BifocalKVCache
+    g = golden("model_tiny.npz")
+    model = _tiny_model(g)
+    ids = g["input_ids"].cuda()
+    a, b, pad = ids[:, :152], ids[:, 30:162], 20
+    batch = torch.cat([a, torch.cat([torch.zeros(1, pad, dtype=ids.dtype, device="cuda"), b], 1)], 0)      # (2, 152)
+    mask = torch.ones_like(batch)
+    mask[1, :pad] = 0
+    pos = (mask.cumsum(-1) - 1).clamp(min=0)
+    new = lambda n: (BifocalKVCache(model.config, 256, batch=n, device="cuda", dtype=torch.bfloat16) if static_cache
+                     else DynamicCache(config=model.config))
+
+    def run(tokens, cuts, mask=None, pos=None):
+        cache, outs, lo = new(tokens.shape[0]), [], 0
+        for hi in cuts:
+            kw = {} if mask is None else dict(attention_mask=mask[:, :hi], position_ids=pos[:, lo:hi])
+            outs.append(model(input_ids=tokens[:, lo:hi], past_key_values=cache, use_cache=True, **kw).logits.float())
+            lo = hi
+        return torch.cat(outs, 1)
+
+    got = run(batch, (100, 150, 151, 152), mask, pos)
+    want_a = run(a, (100, 150, 151, 152))
+    want_b = run(b, (80, 130, 131, 132))
+    for name, x, y in (("a", got[0], want_a[0]), ("b", got[1, pad:], want_b[0])):
+        d, cos = orc.compare(x.cpu(), y.cpu())
+        assert cos >= 0.9995 and d <= 0.1, (name, d, cos)
+    assert torch.isfinite(got).all()
