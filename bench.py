@@ -293,7 +293,8 @@ def long_generate(args, cfg, model, shard, world):
     model.model.kernels_within_window = True                  # the first chunk (L <= w) runs on the same kernels
     gen = torch.Generator().manual_seed(1)
     ids = torch.randint(0, cfg.vocab_size, (1, T), generator=gen).cuda()
-    cache = BifocalKVCache(cfg, T + steps, device="cuda", dtype=torch.bfloat16, shard=shard)
+    cache = BifocalKVCache(cfg, T + steps, device="cuda", dtype=torch.bfloat16, shard=shard,
+                           regrouped_far_keys=args.regrouped_far_keys and not args.eager_decode)
 
     def sync():
         if world > 1:
@@ -365,7 +366,9 @@ def long_generate(args, cfg, model, shard, world):
                 decode_mode="one CUDA graph replay per token (capture excluded from the time)" if replay_ms[0] is not None
                 else "Python-launched steps",
                 group_size_at_end=max(1, math.ceil((T + steps) / args.w)),
-                kv_cache_gb_per_rank=round(2 * layer.keys.numel() * 2 * cfg.num_hidden_layers / 1e9, 2),
+                kv_cache_gb_per_rank=round((3 if layer.group_keys is not None else 2) * layer.keys.numel() * 2
+                                           * cfg.num_hidden_layers / 1e9, 2),
+                regrouped_far_keys=layer.group_keys is not None,
                 kv_rows_per_rank=layer.rows, tokens_in_cache=cache.get_seq_length(),
                 first_tokens=toks[0, :8].tolist(),
                 config=dict(model=args.model, w=args.w, w_0=args.w0, layers=cfg.num_hidden_layers,
@@ -392,6 +395,8 @@ def main():
                          "(sequence-sharded when N > 1) KV cache, then --decode-steps greedy tokens")
     ap.add_argument("--chunk", type=int, default=32768)
     ap.add_argument("--decode-steps", type=int, default=256)
+    ap.add_argument("--regrouped-far-keys", action="store_true", help="--long-generate: keep regrouped copies of the far "
+                    "keys in a second cache buffer (+50 %% KV memory) so decode streams them as stored")
     ap.add_argument("--eager-decode", action="store_true", help="--long-generate: launch every decode step from Python "
                     "instead of replaying one CUDA graph per token")
     args = ap.parse_args()

@@ -324,7 +324,12 @@ int jl_step_advance(const jl_step_advance_args* args, void* cuda_stream);
  * (replaces q_norm / k_norm, apply_rotary_pos_emb, correction_rotate_per_sample on q and the
  * DynamicCache update, modeling_qwen3_jetlong_fused.py:292-294, :329-340, :375-376).  Same roundings as
  * jl_norm_rope.  q: (B, H, D), k / v: (B, Hk, D) rows with strides; q_base / q_group: (B, H, D)
- * contiguous; k_cache / v_cache: (B, rows, Hk, D) with strides. */
+ * contiguous; k_cache / v_cache: (B, rows, Hk, D) with strides.
+ * k_group_cache (optional, same shape and strides as k_cache) holds REGROUPED copies of the far rows, so
+ * that the attention reads them as stored instead of rotating them for every token: each call rewrites
+ * row n_far - 1 (the row that may just have crossed into the far class) as
+ * R(floor(p / group_size) - p) k_cache[row], p = pos0 + row or the block-cyclic
+ * pos0 + (row / pos_block) * pos_block_stride + row % pos_block, with jl_rotate's arithmetic. */
 typedef struct {
   const void* q;
   const void* k;
@@ -344,6 +349,10 @@ typedef struct {
   int64_t cache_rows;       /* capacity: a row index at or past it is never written */
   const float* inv_freq;    /* (head_dim/2,) fp32 device array */
   const int64_t* state;     /* device, JL_STEP_STATE_WORDS words */
+  void* k_group_cache;      /* may be NULL */
+  int64_t pos0;
+  int64_t pos_block;        /* <= 0 means contiguous */
+  int64_t pos_block_stride;
 } jl_decode_append_args;
 
 int jl_decode_append(const jl_decode_append_args* args, void* cuda_stream);

@@ -43,17 +43,37 @@ struct AppendParams {
   int64_t cache_rows;
   const float* inv_freq;
   const int64_t* state;
+  __nv_bfloat16* kg;           // optional regrouped copy of the far rows (strides of kc)
+  int64_t pos0, pos_block, pos_block_stride;
 };
 
-// One warp per (batch, head) row of 128 values: query heads, then key heads, then value heads.
+// One warp per (batch, head) row of 128 values: query heads, then key heads, then value heads, then (with a
+// regrouped far-key cache) the key heads of the newest far row.
 __global__ void __launch_bounds__(128) decode_append_kernel(const AppendParams p) {
   const int lane = threadIdx.x & 31;
-  const int per_b = p.heads + 2 * p.kv_heads;
+  const int per_b = p.heads + 2 * p.kv_heads + (p.kg != nullptr ? p.kv_heads : 0);
   const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (item >= p.batch * per_b) return;
   const int b = item / per_b, h = item % per_b;
   const int64_t pos = p.state[0], row = p.state[1];
   const bool own = p.state[2] != 0 && row >= 0 && row < p.cache_rows;
+
+  if (h >= p.heads + 2 * p.kv_heads) {                  // regroup the last far row: R(floor(p/G) - p) k_cache[row]
+    const int64_t far_row = p.state[3] - 1;
+    if (far_row < 0 || far_row >= p.cache_rows) return;
+    const int hk = h - p.heads - 2 * p.kv_heads;
+    const int64_t kp = key_position(far_row, p.pos0, p.pos_block, p.pos_block_stride);
+    const float tf = static_cast<float>(kp / p.group_size - kp);
+    float s0, c0, s1, c1;
+    sincosf(__fmul_rn(tf, p.inv_freq[2 * lane]), &s0, &c0);
+    sincosf(__fmul_rn(tf, p.inv_freq[2 * lane + 1]), &s1, &c1);
+    const int64_t off = b * p.kcs_b + far_row * p.kcs_s + hk * p.kcs_h;
+    const float2 a = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(p.kc + off + 2 * lane));
+    const float2 bb = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(p.kc + off + 64 + 2 * lane));
+    *reinterpret_cast<uint32_t*>(p.kg + off + 2 * lane) = pack_bf16x2(a.x * c0 - bb.x * s0, a.y * c1 - bb.y * s1);
+    *reinterpret_cast<uint32_t*>(p.kg + off + 64 + 2 * lane) = pack_bf16x2(bb.x * c0 + a.x * s0, bb.y * c1 + a.y * s1);
+    return;
+  }
 
   if (h >= p.heads + p.kv_heads) {                      // value head: plain copy into the cache row
     if (!own) return;
@@ -143,7 +163,12 @@ int launch_decode_append(const jl_decode_append_args* a, cudaStream_t stream) {
   p.group_size = a->group_size > 0 ? a->group_size : 1;
   p.cache_rows = a->cache_rows;
   p.inv_freq = a->inv_freq; p.state = a->state;
-  const int items = a->batch * (a->heads + 2 * a->kv_heads);
+  p.kg = static_cast<__nv_bfloat16*>(a->k_group_cache);
+  p.pos0 = a->pos0;
+  p.pos_block = a->pos_block > 0 ? a->pos_block : 0;
+  p.pos_block_stride = a->pos_block_stride;
+  if (reinterpret_cast<uintptr_t>(a->k_group_cache) & 7) return fail(JL_ERR_BAD_ARG, "jl_decode_append: pointers must be 8-byte aligned");
+  const int items = a->batch * (a->heads + 2 * a->kv_heads + (p.kg != nullptr ? a->kv_heads : 0));
   decode_append_kernel<<<(items + 3) / 4, 128, 0, stream>>>(p);
   return check_launch("jl_decode_append");
 }

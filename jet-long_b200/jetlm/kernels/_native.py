@@ -119,6 +119,7 @@ class DecodeAppendArgs(C.Structure):
         ("batch", C.c_int32), ("heads", C.c_int32), ("kv_heads", C.c_int32), ("head_dim", C.c_int32),
         ("group_size", C.c_int32), ("reserved", C.c_int32), ("cache_rows", C.c_int64),
         ("inv_freq", C.c_void_p), ("state", C.c_void_p),
+        ("k_group_cache", C.c_void_p), ("pos0", C.c_int64), ("pos_block", C.c_int64), ("pos_block_stride", C.c_int64),
     ]
 
 

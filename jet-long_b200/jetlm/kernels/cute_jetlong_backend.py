@@ -223,16 +223,20 @@ def fused_jetlong_decode_cache_stripe(query_base, query_group, key_stripe, value
 
 
 def fused_jetlong_decode_step(query_base, query_group, key_rows, value_rows, *, step, inv_freq, group_size: int,
-                              softmax_scale=None):
+                              softmax_scale=None, key_group_rows=None):
     """Decode whose token-dependent facts come from device memory (ops.StepState), so the launch can sit in
     a CUDA graph that is replayed for every new token.  key_rows / value_rows: this rank's WHOLE
     (B, capacity, Hk, D) cache buffers; the far class is rows [0, n_far) (regrouped in-kernel when
-    group_size > 1), the near class rows [n_far, n_far + n_near), both read from `step`.  With a sharded
+    group_size > 1, or read as stored from key_group_rows when that regrouped copy is given), the near class
+    rows [n_far, n_far + n_near), both read from `step`.  With a sharded
     step the partial (O, LSE) pairs are all-gathered and merged as in fused_jetlong_decode_cache_stripe."""
     sh = step.shard if step.shard is not None and step.shard.world > 1 else None
     geo = dict(pos0=sh.rank * sh.block, pos_block=sh.block, pos_block_stride=sh.world * sh.block) if sh is not None else {}
-    segs = [ops.KvSegment(key_rows, value_rows, q_class=1, rotate=int(group_size) > 1, len_dev=step.far_lens, **geo),
-            ops.KvSegment(key_rows, value_rows, q_class=0, len_dev=step.near_lens, row0_dev=step.n_far)]
+    if key_group_rows is not None and int(group_size) > 1:
+        far = ops.KvSegment(key_group_rows, value_rows, q_class=1, len_dev=step.far_lens)
+    else:
+        far = ops.KvSegment(key_rows, value_rows, q_class=1, rotate=int(group_size) > 1, len_dev=step.far_lens, **geo)
+    segs = [far, ops.KvSegment(key_rows, value_rows, q_class=0, len_dev=step.near_lens, row0_dev=step.n_far)]
     B, _, H, D = query_base.shape
     run = lambda out, lse: ops.decode_segments([query_base, query_group], segs, inv_freq=inv_freq,
                                                group_size=int(group_size), softmax_scale=softmax_scale, out=out, lse=lse)

@@ -45,7 +45,23 @@ class GraphedDecodeStep:
             dist.broadcast(nxt, src=src, group=self.shard.group)
         self.token.copy_(nxt)
 
+    def _refresh_group_keys(self, group: int, pos: int) -> None:
+        """With a regrouped far-key cache: regroup every row that is far for the token at `pos` with this G
+        (one pass per layer; afterwards every step adds the one row that may have crossed the boundary)."""
+        if group <= 1 or self.cache.layers[0].group_keys is None:
+            return
+        sh = self.shard
+        boundary = max(pos - self.w_0, 0)
+        n_far = sh.n_owned(boundary) if sh is not None else boundary
+        if n_far <= 0:
+            return
+        geo = dict(pos0=sh.rank * sh.block, pos_block=sh.block, pos_block_stride=sh.world * sh.block) if sh is not None else {}
+        inv_freq = self.lm.model.rotary_emb.inv_freq
+        for layer in self.cache.layers:
+            ops.rope_regroup(layer.keys[:, :n_far], inv_freq, group_size=group, out=layer.group_keys[:, :n_far], **geo)
+
     def _capture(self, group: int, pos: int) -> None:
+        self._refresh_group_keys(group, pos)
         keep = self.token.clone()
         cur = torch.cuda.current_stream(self.device)
         side = torch.cuda.Stream(self.device)
@@ -75,6 +91,7 @@ class GraphedDecodeStep:
             self._capture(group, pos)
         elif self._device_pos != pos:      # the cache moved without us (eager steps, reset): re-seed the device state
             self.step.set_next_position(pos)
+            self._refresh_group_keys(group, pos)
         self._graph.replay()
         for layer in self.cache.layers:
             layer.commit(1)

@@ -552,11 +552,13 @@ class StepState:
 
 def decode_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_weight: torch.Tensor, k_weight: torch.Tensor,
                   inv_freq: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, step: StepState, *,
-                  q_eps: float, k_eps: float, group_size: int = 1):
+                  q_eps: float, k_eps: float, group_size: int = 1, k_group_cache: Optional[torch.Tensor] = None):
     """One launch between the projections and the attention of a decode step: per-head RMSNorm + RoPE of
     q (B,1,H,D) and k (B,1,Hk,D) at the device-side position, the regrouped query when group_size > 1, and
     the write of the new key / value into row step.state[1] of k_cache / v_cache (B,rows,Hk,D) on the rank
-    that owns the position.  Returns (q_base, q_group), each (B,1,H,D); q_group is q_base when group_size == 1."""
+    that owns the position.  k_group_cache (same shape and strides as k_cache), if given, keeps regrouped
+    copies of the far rows: the call rewrites the newest far row (row n_far - 1) from k_cache.
+    Returns (q_base, q_group), each (B,1,H,D); q_group is q_base when group_size == 1."""
     op = "decode_append"
     for name, t in (("q", q), ("k", k), ("v", v), ("k_cache", k_cache), ("v_cache", v_cache)):
         _check_view(op, name, t)
@@ -572,6 +574,10 @@ def decode_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_weight: t
     for name, w in (("q_weight", q_weight), ("k_weight", k_weight)):
         if w.numel() != D or not w.is_contiguous() or w.dtype != q.dtype:
             raise ValueError(f"{op}: {name} must be a contiguous ({D},) tensor of the query dtype")
+    if k_group_cache is not None and (k_group_cache.shape != k_cache.shape or k_group_cache.stride() != k_cache.stride()
+                                      or k_group_cache.dtype != k_cache.dtype):
+        raise ValueError(f"{op}: k_group_cache must match k_cache in shape, strides and dtype")
+    sh = step.shard if step.shard is not None and step.shard.world > 1 else None
     inv_freq = inv_freq.to(device=q.device, dtype=torch.float32).contiguous()
     q_base = torch.empty(B, 1, H, D, dtype=q.dtype, device=q.device)
     q_group = torch.empty(B, 1, H, D, dtype=q.dtype, device=q.device) if group_size > 1 else None
@@ -581,7 +587,10 @@ def decode_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_weight: t
                            q_base.data_ptr(), q_group.data_ptr() if q_group is not None else None,
                            k_cache.data_ptr(), v_cache.data_ptr(),
                            _st(k_cache, 0), _st(k_cache, 1), _st(k_cache, 2), _st(v_cache, 0), _st(v_cache, 1), _st(v_cache, 2),
-                           B, H, Hk, D, int(group_size), 0, int(k_cache.shape[1]), inv_freq.data_ptr(), step.state.data_ptr())
+                           B, H, Hk, D, int(group_size), 0, int(k_cache.shape[1]), inv_freq.data_ptr(), step.state.data_ptr(),
+                           k_group_cache.data_ptr() if k_group_cache is not None else None,
+                           sh.rank * sh.block if sh is not None else 0, sh.block if sh is not None else 0,
+                           sh.world * sh.block if sh is not None else 0)
     with torch.cuda.device(q.device):
         _timed_call("jl_decode_append", lambda: N.lib().jl_decode_append(C.byref(a), _stream()))
     return q_base, (q_group if q_group is not None else q_base)

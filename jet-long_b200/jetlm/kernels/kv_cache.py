@@ -30,12 +30,14 @@ class BifocalStaticLayer(CacheLayerMixin):
     is_compileable = False
 
     def __init__(self, batch: int, capacity: int, kv_heads: int, head_dim: int, dtype, device,
-                 shard: Optional[SequenceShard] = None):
+                 shard: Optional[SequenceShard] = None, regrouped_far_keys: bool = False):
         super().__init__()
         self.shard = shard
         self.capacity = int(capacity)                 # rows this rank can hold
         self.keys = torch.empty(batch, self.capacity, kv_heads, head_dim, dtype=dtype, device=device)
         self.values = torch.empty_like(self.keys)
+        # optional second key buffer: regrouped copies of the far rows, maintained by the graph decode driver
+        self.group_keys = torch.empty_like(self.keys) if regrouped_far_keys else None
         self.dtype, self.device = dtype, self.keys.device
         self.is_initialized = True
         self.tokens = 0                                # tokens seen by this layer (all ranks)
@@ -94,15 +96,20 @@ class BifocalStaticLayer(CacheLayerMixin):
 
 class BifocalKVCache(Cache):
     """One BifocalStaticLayer per decoder layer plus one shared scratch buffer of a layer's size, which
-    holds the regrouped keys of the layer being attended during a (chunked) prefill call."""
+    holds the regrouped keys of the layer being attended during a (chunked) prefill call.
+    regrouped_far_keys=True adds a second key buffer per layer (+50 % cache memory): the CUDA-graph decode
+    driver keeps regrouped copies of the far rows there, so a decode step streams the far keys as stored
+    instead of rotating them for every token (the reference regroups the whole distant cache per token,
+    modeling_qwen3_jetlong_fused.py:428-440)."""
 
     def __init__(self, config, max_tokens: int, batch: int = 1, device=None, dtype=torch.bfloat16,
-                 shard: Optional[SequenceShard] = None):
+                 shard: Optional[SequenceShard] = None, regrouped_far_keys: bool = False):
         head_dim = getattr(config, "head_dim", None) or config.hidden_size // config.num_attention_heads
         world = shard.world if shard is not None else 1
         block = shard.block if shard is not None else 128
         per_rank = -(-int(max_tokens) // (world * block)) * block        # whole blocks, so every stripe fits
-        layers = [BifocalStaticLayer(batch, per_rank, config.num_key_value_heads, head_dim, dtype, device, shard)
+        layers = [BifocalStaticLayer(batch, per_rank, config.num_key_value_heads, head_dim, dtype, device, shard,
+                                     regrouped_far_keys)
                   for _ in range(config.num_hidden_layers)]
         super().__init__(layers=layers)
         self.shard = shard

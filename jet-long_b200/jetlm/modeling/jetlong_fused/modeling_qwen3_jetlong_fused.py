@@ -178,11 +178,13 @@ class Qwen3JetLongFusedAttention(nn.Module):
             # decode step whose position, cache row and class lengths live on the device: two launches
             # (norm -> RoPE -> cache write, attention) with token-independent host arguments
             slot = past_key_values.layers[self.layer_idx]
+            kg = slot.group_keys if group > 1 else None      # regrouped copies of the far rows, when the cache keeps them
             q_base, q_group = ops.decode_append(q, k, v, self.q_norm.weight, self.k_norm.weight, inv_freq,
                                                 slot.keys, slot.values, plan.step, q_eps=q_eps, k_eps=k_eps,
-                                                group_size=group)
+                                                group_size=group, k_group_cache=kg)
             attn = backend.fused_jetlong_decode_step(q_base, q_group, slot.keys, slot.values, step=plan.step,
-                                                     inv_freq=inv_freq, group_size=group, softmax_scale=self.scaling)
+                                                     inv_freq=inv_freq, group_size=group, softmax_scale=self.scaling,
+                                                     key_group_rows=kg)
             return self.o_proj(attn.reshape(*out_shape, -1)), None
 
         if plan.token_shard is not None:

@@ -136,3 +136,28 @@ def test_graphed_step_hidden_state_equals_eager_forward(golden):
     d, cos = orc.compare(got.cpu(), want.cpu())
     assert cos >= 0.99999 and d <= 2e-2, (d, cos)
     assert torch.equal(caches[1].layers[0].keys[:, 150], caches[0].layers[0].keys[:, 150])
+
+
+@torch.inference_mode()
+def test_graphed_decode_with_regrouped_far_key_cache(golden):
+    """The far rows are kept regrouped in a second key buffer (bulk pass at capture, one row per step): same
+    greedy tokens as the eager steps, and the buffer equals a fresh regroup of the base keys, bit for bit,
+    also after G changed (prompt 186 -> G 3, 4)."""
+    from jetlm.kernels.kv_cache import BifocalKVCache
+    g = golden("model_tiny.npz")
+    model = _tiny_model(g)
+    ids = g["input_ids"].cuda()
+    ops = _ops()
+    w, w0 = g.meta["w"], g.meta["w0"]
+    for prompt, new in ((186, 12), (150, 6)):
+        eager = model.generate_long(ids[:, :prompt], max_new_tokens=new, chunk_tokens=64)
+        cache = BifocalKVCache(model.config, 256, device="cuda", dtype=torch.bfloat16, regrouped_far_keys=True)
+        graphed = model.generate_long(ids[:, :prompt], max_new_tokens=new, chunk_tokens=64, past_key_values=cache,
+                                      cuda_graph=True)
+        assert graphed.tolist() == eager.tolist()
+        last = cache.get_seq_length() - 1                     # position of the last decoded-from token
+        G, n_far = -(-(last + 1) // w), last - w0
+        inv = model.model.rotary_emb.inv_freq
+        for layer in cache.layers:
+            want = ops.rope_regroup(layer.keys[:, :n_far], inv, group_size=G)
+            assert torch.equal(layer.group_keys[:, :n_far], want)
