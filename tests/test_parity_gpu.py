@@ -245,6 +245,35 @@ def test_prefill_impls_agree_large():
     _check(o0, l0, o1.float().cpu(), l1.cpu(), "impl 0 vs impl 1")
 
 
+@pytest.mark.parametrize("S,H,Hk,w0", [(65536, 16, 8, 32768), (131072, 32, 8, 32768)])
+def test_prefill_full_size_spot_rows(S, H, Hk, w0):
+    """The benchmark geometries (Qwen3-1.7B at 65536 tokens, Qwen3-4B/8B at 131072 tokens, w_0 = 32768) in one
+    launch; sampled (row, head) pairs — first rows, both sides of the class boundary, tile edges, the last
+    row — are recomputed by the fp32 oracle from the same bf16 operands."""
+    ops = _ops()
+    torch.manual_seed(S // 1024 + H)
+    D = 128
+    mk = lambda h: torch.randn(1, S, h, D, device="cuda").bfloat16()
+    qb, qg, kb, kg, v = mk(H), mk(H), mk(Hk), mk(Hk), mk(Hk)
+    out, lse = ops.posmap_prefill([qb, qg], [kb, kg], v, pmap=ops.PositionMap.jetlong(w0), q_pos0=0)
+    assert _native_status_clean()
+    rows = [0, 1, 127, 128, 255, 256, w0 - 1, w0, w0 + 1, w0 + 129, S // 2 + 77, S - w0 - 1, S - 257, S - 1]
+    rep = H // Hk
+    for i, r in enumerate(rows):
+        h = (7 * i + 3) % H
+        kvh = h // rep
+        sl = lambda t, hh: t[:, : r + 1, hh: hh + 1].float().cpu()
+        eo, el = orc.jetlong_prefill(qb[:, r: r + 1, h: h + 1].float().cpu(), qg[:, r: r + 1, h: h + 1].float().cpu(),
+                                     sl(kb, kvh), sl(kg, kvh), sl(v, kvh), seqstart=r, w0=w0)
+        _check(out[:, r: r + 1, h: h + 1], lse[:, h: h + 1, r: r + 1], eo, el, f"S={S} row {r} head {h}")
+
+
+def _native_status_clean():
+    from jetlm.kernels import _native
+    torch.cuda.synchronize()
+    return _native.lib().jl_prefill_status() == 0
+
+
 def test_prefill_block_cyclic_keys():
     """A rank's block-cyclic stripe of the keys + merge of the stripes == attention over all keys."""
     ops = _ops()
