@@ -288,6 +288,18 @@ typedef struct {
 
 int jl_rmsnorm(const jl_rmsnorm_args* args, void* cuda_stream);
 
+/* jl_silu_mul — out = silu(gate) * up over `count` contiguous bf16 values (a multiple of 8), the elementwise
+ * part of the Qwen3 MLP the decoder layer runs between its projections (transformers' Qwen3MLP, inherited at
+ * modeling_qwen3_jetlong_fused.py:468-471), in one pass; roundings as torch's two bf16 ops.  out may alias gate or up. */
+typedef struct {
+  const void* gate;
+  const void* up;
+  void* out;
+  int64_t count;
+} jl_silu_mul_args;
+
+int jl_silu_mul(const jl_silu_mul_args* args, void* cuda_stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Decode-step state on the device, so that one captured CUDA graph can be replayed for every new
  * token.  The reference's decode step reads positions back to the host in every layer

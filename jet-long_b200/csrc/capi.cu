@@ -10,6 +10,7 @@ int launch_merge(const jl_merge_args* a, cudaStream_t stream);
 int launch_rotate(const jl_rotate_args* a, cudaStream_t stream);
 int launch_norm_rope(const jl_norm_rope_args* a, cudaStream_t stream);
 int launch_rmsnorm(const jl_rmsnorm_args* a, cudaStream_t stream);
+int launch_silu_mul(const jl_silu_mul_args* a, cudaStream_t stream);
 int launch_step_advance(const jl_step_advance_args* a, cudaStream_t stream);
 int launch_decode_append(const jl_decode_append_args* a, cudaStream_t stream);
 int launch_decode(const jl_decode_args* a, cudaStream_t stream);
@@ -131,6 +132,13 @@ int jl_norm_rope(const jl_norm_rope_args* args, void* cuda_stream) {
   int rc = jl::check_device_arch();
   if (rc != JL_OK) return rc;
   return jl::launch_norm_rope(args, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int jl_silu_mul(const jl_silu_mul_args* args, void* cuda_stream) {
+  if (args == nullptr) return jl::fail(JL_ERR_BAD_ARG, "jl_silu_mul: args is NULL");
+  int rc = jl::check_device_arch();
+  if (rc != JL_OK) return rc;
+  return jl::launch_silu_mul(args, static_cast<cudaStream_t>(cuda_stream));
 }
 
 int jl_step_advance(const jl_step_advance_args* args, void* cuda_stream) {

@@ -279,4 +279,41 @@ int launch_rmsnorm(const jl_rmsnorm_args* a, cudaStream_t stream) {
   return check_launch("jl_rmsnorm");
 }
 
+// ---------------------------------------------------------------------------------------------
+// SiLU(gate) * up of the Qwen3 MLP in one pass (torch runs two: the activation, then the product).
+// Roundings as torch's bf16 ops: silu evaluated in fp32 and rounded to bf16, product rounded again.
+__global__ void __launch_bounds__(256) silu_mul_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ up,
+                                                       uint4* __restrict__ out, int64_t n_vec) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const uint4 g = gate[i], u = up[i];
+    const uint32_t* gw = reinterpret_cast<const uint32_t*>(&g);
+    const uint32_t* uw = reinterpret_cast<const uint32_t*>(&u);
+    uint4 r;
+    uint32_t* rw = reinterpret_cast<uint32_t*>(&r);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 a = unpack_bf16x2(gw[j]), b = unpack_bf16x2(uw[j]);
+      auto rb = [](float v) { return __bfloat162float(__float2bfloat16(v)); };
+      const float s0 = rb(a.x / (1.f + expf(-a.x))), s1 = rb(a.y / (1.f + expf(-a.y)));
+      rw[j] = pack_bf16x2(s0 * b.x, s1 * b.y);
+    }
+    out[i] = r;
+  }
+}
+
+int launch_silu_mul(const jl_silu_mul_args* a, cudaStream_t stream) {
+  if (a->gate == nullptr || a->up == nullptr || a->out == nullptr) return fail(JL_ERR_BAD_ARG, "jl_silu_mul: NULL pointer");
+  if (a->count < 0 || a->count % 8 != 0) return fail(JL_ERR_BAD_ARG, "jl_silu_mul: count must be a non-negative multiple of 8");
+  if ((reinterpret_cast<uintptr_t>(a->gate) | reinterpret_cast<uintptr_t>(a->up) | reinterpret_cast<uintptr_t>(a->out)) & 15)
+    return fail(JL_ERR_BAD_ARG, "jl_silu_mul: pointers must be 16-byte aligned");
+  if (a->count == 0) return JL_OK;
+  const int64_t n_vec = a->count / 8;
+  const int64_t blocks = (n_vec + 255) / 256;
+  const int grid = static_cast<int>(blocks < 148 * 16 ? blocks : 148 * 16);
+  silu_mul_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint4*>(a->gate), static_cast<const uint4*>(a->up),
+                                            static_cast<uint4*>(a->out), n_vec);
+  return check_launch("jl_silu_mul");
+}
+
 }  // namespace jl

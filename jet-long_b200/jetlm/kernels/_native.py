@@ -99,6 +99,10 @@ class RmsNormArgs(C.Structure):
                 ("out", C.c_void_p), ("rows", C.c_int64), ("hidden", C.c_int32), ("eps", C.c_float)]
 
 
+class SiluMulArgs(C.Structure):
+    _fields_ = [("gate", C.c_void_p), ("up", C.c_void_p), ("out", C.c_void_p), ("count", C.c_int64)]
+
+
 JL_STEP_STATE_WORDS = 5
 
 
@@ -139,6 +143,7 @@ EXPORTS = [
     ("jl_rotate", C.c_int, [C.POINTER(RotateArgs), C.c_void_p]),
     ("jl_norm_rope", C.c_int, [C.POINTER(NormRopeArgs), C.c_void_p]),
     ("jl_rmsnorm", C.c_int, [C.POINTER(RmsNormArgs), C.c_void_p]),
+    ("jl_silu_mul", C.c_int, [C.POINTER(SiluMulArgs), C.c_void_p]),
     ("jl_step_advance", C.c_int, [C.POINTER(StepAdvanceArgs), C.c_void_p]),
     ("jl_decode_append", C.c_int, [C.POINTER(DecodeAppendArgs), C.c_void_p]),
 ]

@@ -63,7 +63,7 @@ def _st(t: torch.Tensor, i: int) -> int:
 # Instrumentation used by the benchmark: kernel launches issued through this module, and (when a list
 # is installed with set_event_sink) a CUDA event pair around every attention kernel launch.
 KERNELS_PER_CALL = {"jl_prefill": 1, "jl_decode": 2, "jl_merge": 1, "jl_rotate": 1, "jl_norm_rope": 1, "jl_rmsnorm": 1,
-                    "jl_step_advance": 1, "jl_decode_append": 1}
+                    "jl_step_advance": 1, "jl_decode_append": 1, "jl_silu_mul": 1}
 LAUNCHES = {name: 0 for name in KERNELS_PER_CALL}
 _EVENT_SINK: Optional[list] = None
 
@@ -195,6 +195,21 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, *, eps: float, residual: Opti
     with torch.cuda.device(x.device):
         _timed_call("jl_rmsnorm", lambda: N.lib().jl_rmsnorm(C.byref(a), _stream()))
     return (summed, out) if residual is not None else out
+
+
+def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """silu(gate) * up in one pass (contiguous bf16 tensors of one shape, numel a multiple of 8)."""
+    op = "silu_mul"
+    if gate.dtype not in _SUPPORTED_DTYPES or up.dtype != gate.dtype or not gate.is_cuda or gate.shape != up.shape:
+        raise ValueError(f"{op}: gate and up must be CUDA torch.bfloat16 tensors of one shape")
+    _require_contiguous(op, "gate", gate)
+    _require_contiguous(op, "up", up)
+    _require_arch(op, gate.device)
+    out = torch.empty_like(gate)
+    a = N.SiluMulArgs(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel())
+    with torch.cuda.device(gate.device):
+        _timed_call("jl_silu_mul", lambda: N.lib().jl_silu_mul(C.byref(a), _stream()))
+    return out
 
 
 def norm_rope(x: torch.Tensor, weight: torch.Tensor, inv_freq: torch.Tensor, *, eps: float, pos0: int = 0,

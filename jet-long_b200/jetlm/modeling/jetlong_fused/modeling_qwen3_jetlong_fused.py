@@ -402,7 +402,11 @@ class Qwen3JetLongFusedDecoderLayer(Qwen3DecoderLayer):
                               position_embeddings=position_embeddings, **kwargs)
         residual, h = ops.rmsnorm(h.contiguous(), self.post_attention_layernorm.weight,
                                   eps=self.post_attention_layernorm.variance_epsilon, residual=residual)
-        h = self.mlp(h)
+        mlp = self.mlp
+        if self.self_attn.config.hidden_act == "silu" and mlp.intermediate_size % 8 == 0:
+            h = mlp.down_proj(ops.silu_mul(mlp.gate_proj(h), mlp.up_proj(h)))       # one elementwise pass, not two
+        else:
+            h = mlp(h)
         return residual + h
 
 

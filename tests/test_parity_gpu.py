@@ -138,6 +138,20 @@ def test_rmsnorm_fused_pass(hidden):
     assert float((diff > 0).float().mean()) < 0.01 and float(diff.max()) <= 2 ** -5
 
 
+def test_silu_mul_fused_pass():
+    """silu(gate) * up in one pass against torch's two bf16 ops: at most one bf16 step apart, and only rarely."""
+    ops = _ops()
+    torch.manual_seed(8)
+    g = (torch.randn(3, 1000, 1536, device="cuda") * 3).bfloat16()
+    u = torch.randn(3, 1000, 1536, device="cuda").bfloat16()
+    got = ops.silu_mul(g, u).float()
+    want = (torch.nn.functional.silu(g) * u).float()
+    diff = (got - want).abs()
+    assert float((diff > 0).float().mean()) < 0.01 and float((diff / want.abs().clamp_min(1e-6)).max()) <= 2 ** -7
+    with pytest.raises(ValueError):
+        ops.silu_mul(g, u[:, :, :8])
+
+
 def test_norm_rope_fused_pass():
     """RMSNorm + base RoPE + regroup in one kernel == Qwen3RMSNorm (its bf16 roundings) followed by the
     oracle's fp32 rotations; strided output straight into a (B,Hk,S,D) cache, block-cyclic positions."""
