@@ -112,55 +112,68 @@ class ClockSampler:
 # CPU baseline: the oracle (a restatement of the reference's eager composition) on the host cores
 # --------------------------------------------------------------------------------------------------
 
-def cpu_prefill_sample(S: int, dims: dict, w_0: int, G: int):
-    """Time a bounded sample of the prefill workload on the CPU and extrapolate to tokens/s.
+def cpu_prefill_sample(S: int, dims: dict, w_0: int, G: int, blocks: int = 16):
+    """Time a bounded sample of the prefill workload on the CPU (about 10-20 s at the default size) and
+    extrapolate to tokens/s.
 
-    Attention: the oracle's two-branch bifocal composition for two 128-row query blocks (rows
-    [S/2, S/2+128) and [S-128, S)) of 8 query heads (one per kv head) over the full key range,
-    scaled by (query heads / 8) x (all causal pairs / sampled pairs).  Dense layers: the fp32
-    projections + MLP of one layer on 256 tokens and a slice of the lm_head on 128 tokens, scaled to S tokens
-    and all layers."""
+    Attention: the oracle's two-branch bifocal composition for `blocks` 128-row query blocks spread evenly over
+    the prompt (the last one ends at row S) of 8 query heads (one per kv head) over their full causal key
+    range, scaled by (query heads / 8) x (all causal pairs / sampled pairs).  The RoPE / regroup of the
+    operands is timed apart and scaled by rows, because the workload rotates every row once per layer, not once
+    per query block.  Dense layers: the fp32 projections + MLP of one layer on 1024 tokens and a slice of the
+    lm_head on 256 tokens, scaled to S tokens and all layers."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import jetlong_oracle as orc
     H, Hk, D, L = dims["heads"], dims["kv_heads"], 128, dims["layers"]
     hidden, inter, vocab = dims["hidden"], dims["inter"], dims["vocab"]
     torch.manual_seed(0)
     inv = orc.default_inv_freq()
-    t_attn, pairs = 0.0, 0
-    for q0 in (S // 2, S - 128):
+    blocks = max(1, min(blocks, S // 128))
+    k_all = torch.randn(1, S, Hk, D)
+    v_all = torch.randn(1, S, Hk, D)
+    t_attn, t_rot, pairs, rot_rows = 0.0, 0.0, 0, 0
+    starts = [(i + 1) * S // blocks - 128 for i in range(blocks)]
+    for q0 in starts:
         n_k = q0 + 128
-        k = torch.randn(1, n_k, Hk, D)
-        v = torch.randn(1, n_k, Hk, D)
+        k, v = k_all[:, :n_k], v_all[:, :n_k]
         q = torch.randn(1, 128, Hk, D)
-        t0 = time.perf_counter()
         qp = (torch.arange(128) + q0).view(1, -1)
         kp = torch.arange(n_k).view(1, -1)
+        t0 = time.perf_counter()
         qb, qg, kb, kg = orc.jetlong_operands(q, k, q_positions=qp, k_positions=kp, group_size=G, inv_freq=inv)
+        t1 = time.perf_counter()
         orc.jetlong_prefill(qb, qg, kb, kg, v, seqstart=q0, w0=w_0)
-        t_attn += time.perf_counter() - t0
+        t2 = time.perf_counter()
+        t_rot += t1 - t0
+        t_attn += t2 - t1
         pairs += 128 * q0 + 128 * 129 // 2
+        rot_rows += (n_k + 128) * Hk
     total_pairs = S * (S + 1) // 2
-    attn_layer = t_attn * (H / Hk) * (total_pairs / pairs)
-    x = torch.randn(256, hidden)
+    attn_layer = t_attn * (H / Hk) * (total_pairs / pairs) + t_rot * (S * (H + Hk) / rot_rows)
+    n_tok = 1024
+    x = torch.randn(n_tok, hidden)
     ws = [torch.randn(hidden, H * D), torch.randn(hidden, 2 * Hk * D), torch.randn(H * D, hidden),
           torch.randn(hidden, 2 * inter), torch.randn(inter, hidden)]
     t0 = time.perf_counter()
     a = x @ ws[0]; _ = x @ ws[1]; _ = a @ ws[2]
     u = x @ ws[3]
     _ = (torch.nn.functional.silu(u[:, :inter]) * u[:, inter:]) @ ws[4]
-    dense_layer = (time.perf_counter() - t0) * (S / 256)
-    xh = torch.randn(128, hidden)
+    t_dense = time.perf_counter() - t0
+    dense_layer = t_dense * (S / n_tok)
+    xh = torch.randn(256, hidden)
     vslice = min(vocab, 16384)
     wv = torch.randn(hidden, vslice)
     t0 = time.perf_counter()
     _ = xh @ wv
-    head = (time.perf_counter() - t0) * (S / 128) * (vocab / vslice)
+    t_head = time.perf_counter() - t0
+    head = t_head * (S / 256) * (vocab / vslice)
     total = L * (attn_layer + dense_layer) + head
     return dict(tok_s=S / total, est_total_s=total, attn_s=L * attn_layer, dense_s=L * dense_layer + head,
-                sample_s=t_attn, cores=torch.get_num_threads(),
-                sample=(f"oracle bifocal attention for 2 query blocks of 128 rows (rows {S // 2}.. and {S - 128}..) x {Hk} heads "
-                        f"over the full key range + one layer's fp32 projections/MLP on 256 tokens + a 16384-column slice of the lm_head on 128 tokens; "
-                        f"extrapolated by causal-pair count, head count, token count and {L} layers"))
+                sample_s=t_attn + t_rot + t_dense + t_head, cores=torch.get_num_threads(),
+                sample=(f"oracle bifocal attention for {blocks} query blocks of 128 rows (ending at rows "
+                        f"{starts[0] + 128}, ..., {starts[-1] + 128}) x {Hk} heads over their causal key range, operand RoPE/regroup "
+                        f"timed apart; one layer's fp32 projections/MLP on {n_tok} tokens; a {vslice}-column slice of the lm_head on "
+                        f"256 tokens; extrapolated by causal-pair count, head count, rows, tokens and {L} layers"))
 
 
 def model_dims(cfg):
