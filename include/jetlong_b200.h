@@ -306,18 +306,19 @@ int jl_silu_mul(const jl_silu_mul_args* args, void* cuda_stream);
  * (modeling_qwen3_jetlong_fused.py:145, :342, :406) and cannot be captured; here the per-token facts
  * live in device memory and kernels whose host arguments are fixed read them.  No reference counterpart.
  *
- * state: int64[JL_STEP_STATE_WORDS] = { pos, row, own, n_far, n_near }
+ * state: int64[JL_STEP_STATE_WORDS] = { pos, row, own, n_far, n_near, steps }
  *   pos    absolute position of the token being decoded
  *   row    cache row (of this rank's stripe) the token's key / value go to
  *   own    1 if this rank stores the token (always 1 without sharding)
  *   n_far  rows of this rank's cache in the far class: positions < pos - w_0
  *   n_near rows in the near class, the new token included when owned
- * jl_step_advance: pos <- pos + 1, the other words recomputed for a cache sharded block-cyclically
+ *   steps  number of advances made on this state (never rewound; an epoch source for jl_peer_merge)
+ * jl_step_advance: pos <- pos + 1, steps <- steps + 1, the other words recomputed for a cache sharded block-cyclically
  * (block `block`, this rank `rank` of `world`; world = 1: contiguous).  lens, if not NULL, is an
  * int32[2 * batch] device array that receives n_far (first batch entries) and n_near (next batch
  * entries) for jl_kv_segment.len_dev.  Initialise state[0] to (next position - 1) from the host.
  * ------------------------------------------------------------------------------------------- */
-#define JL_STEP_STATE_WORDS 5
+#define JL_STEP_STATE_WORDS 6
 typedef struct {
   int64_t* state;
   int32_t* lens;            /* may be NULL */
@@ -368,6 +369,41 @@ typedef struct {
 } jl_decode_append_args;
 
 int jl_decode_append(const jl_decode_append_args* args, void* cuda_stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * jl_peer_merge — the exchange step of the KV-sharded decode fused with the N-way merge, over
+ * peer-mapped memory instead of a collective library call: every rank pushes its partial (O, LSE) into
+ * every rank's exchange buffer with plain peer stores (NVLink), publishes a per-source flag, waits (at
+ * most 1 s; then *status = 1 and the result is invalid — the kernel never hangs) for the other ranks'
+ * flags and merges the `world` partials that have landed in its own memory.  No reference counterpart
+ * (the reference is single-GPU; its split-K merge is cute_decode_sm90.py:199-215).
+ *
+ * part_o (batch, heads, 128) bf16 contiguous, part_lse (batch, heads) fp32: this rank's partial.
+ * peer_buf[r]: rank r's exchange buffer as mapped into THIS process (peer_buf[rank] is the local one);
+ * every buffer has jl_peer_merge_buffer_bytes(world, batch, heads, head_dim) bytes, the same size on all
+ * ranks, and starts zeroed.  All ranks call with the same shapes and the same epoch
+ *   e = (*epoch_base_dev) * epoch_stride + epoch_offset >= 1,
+ * which must grow by exactly 1 from one use of the buffers to the next (two parities alternate on it).
+ * out (batch, heads, 128) bf16, lse_out (batch, heads) fp32 or NULL.  One launch per rank, every rank on
+ * its own GPU.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* part_o;
+  const float* part_lse;
+  void* peer_buf[JL_MAX_PARTS];
+  size_t buffer_bytes;
+  int32_t rank, world;
+  int32_t batch, heads, head_dim;
+  int32_t reserved;
+  const int64_t* epoch_base_dev;   /* NULL: base 0 */
+  int64_t epoch_stride, epoch_offset;
+  void* out;
+  float* lse_out;
+  int32_t* status;                 /* device word, raised to 1 when a wait gave up */
+} jl_peer_merge_args;
+
+size_t jl_peer_merge_buffer_bytes(int32_t world, int32_t batch, int32_t heads, int32_t head_dim);
+int jl_peer_merge(const jl_peer_merge_args* args, void* cuda_stream);
 
 #ifdef __cplusplus
 }

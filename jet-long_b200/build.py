@@ -15,7 +15,7 @@ CSRC = os.path.join(HERE, "csrc")
 OUT_DIR = os.path.join(HERE, "jetlm", "kernels")
 LIB = os.path.join(OUT_DIR, "libjetlong_b200.so")
 OBJ_DIR = os.path.join(HERE, "build")
-SOURCES = ["capi.cu", "merge.cu", "rotate.cu", "step.cu", "decode.cu", "prefill_mma.cu", "prefill_tc.cu"]
+SOURCES = ["capi.cu", "merge.cu", "rotate.cu", "step.cu", "peer.cu", "decode.cu", "prefill_mma.cu", "prefill_tc.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 

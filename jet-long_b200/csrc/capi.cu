@@ -11,6 +11,8 @@ int launch_rotate(const jl_rotate_args* a, cudaStream_t stream);
 int launch_norm_rope(const jl_norm_rope_args* a, cudaStream_t stream);
 int launch_rmsnorm(const jl_rmsnorm_args* a, cudaStream_t stream);
 int launch_silu_mul(const jl_silu_mul_args* a, cudaStream_t stream);
+int launch_peer_merge(const jl_peer_merge_args* a, cudaStream_t stream);
+size_t peer_merge_buffer_bytes(int32_t world, int32_t batch, int32_t heads);
 int launch_step_advance(const jl_step_advance_args* a, cudaStream_t stream);
 int launch_decode_append(const jl_decode_append_args* a, cudaStream_t stream);
 int launch_decode(const jl_decode_args* a, cudaStream_t stream);
@@ -132,6 +134,17 @@ int jl_norm_rope(const jl_norm_rope_args* args, void* cuda_stream) {
   int rc = jl::check_device_arch();
   if (rc != JL_OK) return rc;
   return jl::launch_norm_rope(args, static_cast<cudaStream_t>(cuda_stream));
+}
+
+size_t jl_peer_merge_buffer_bytes(int32_t world, int32_t batch, int32_t heads, int32_t head_dim) {
+  return head_dim == 128 ? jl::peer_merge_buffer_bytes(world, batch, heads) : 0;
+}
+
+int jl_peer_merge(const jl_peer_merge_args* args, void* cuda_stream) {
+  if (args == nullptr) return jl::fail(JL_ERR_BAD_ARG, "jl_peer_merge: args is NULL");
+  int rc = jl::check_device_arch();
+  if (rc != JL_OK) return rc;
+  return jl::launch_peer_merge(args, static_cast<cudaStream_t>(cuda_stream));
 }
 
 int jl_silu_mul(const jl_silu_mul_args* args, void* cuda_stream) {

@@ -25,7 +25,7 @@ __global__ void step_advance_kernel(int64_t* state, int32_t* lens, int batch, in
   const int64_t boundary = pos - w_0 > 0 ? pos - w_0 : 0;
   const int64_t n_far = rows_owned(boundary, rank, world, block);
   const int64_t n_near = row + own - n_far;
-  state[0] = pos; state[1] = row; state[2] = own; state[3] = n_far; state[4] = n_near;
+  state[0] = pos; state[1] = row; state[2] = own; state[3] = n_far; state[4] = n_near; state[5] += 1;
   if (lens != nullptr)
     for (int b = 0; b < batch; ++b) {
       lens[b] = static_cast<int32_t>(n_far);

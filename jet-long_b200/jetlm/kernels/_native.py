@@ -103,7 +103,7 @@ class SiluMulArgs(C.Structure):
     _fields_ = [("gate", C.c_void_p), ("up", C.c_void_p), ("out", C.c_void_p), ("count", C.c_int64)]
 
 
-JL_STEP_STATE_WORDS = 5
+JL_STEP_STATE_WORDS = 6
 
 
 class StepAdvanceArgs(C.Structure):
@@ -127,6 +127,14 @@ class DecodeAppendArgs(C.Structure):
     ]
 
 
+class PeerMergeArgs(C.Structure):
+    _fields_ = [("part_o", C.c_void_p), ("part_lse", C.c_void_p), ("peer_buf", C.c_void_p * JL_MAX_PARTS),
+                ("buffer_bytes", C.c_size_t), ("rank", C.c_int32), ("world", C.c_int32),
+                ("batch", C.c_int32), ("heads", C.c_int32), ("head_dim", C.c_int32), ("reserved", C.c_int32),
+                ("epoch_base_dev", C.c_void_p), ("epoch_stride", C.c_int64), ("epoch_offset", C.c_int64),
+                ("out", C.c_void_p), ("lse_out", C.c_void_p), ("status", C.c_void_p)]
+
+
 # Every symbol include/jetlong_b200.h declares: (name, restype, argtypes)
 EXPORTS = [
     ("jl_version", C.c_int, []),
@@ -143,6 +151,8 @@ EXPORTS = [
     ("jl_rotate", C.c_int, [C.POINTER(RotateArgs), C.c_void_p]),
     ("jl_norm_rope", C.c_int, [C.POINTER(NormRopeArgs), C.c_void_p]),
     ("jl_rmsnorm", C.c_int, [C.POINTER(RmsNormArgs), C.c_void_p]),
+    ("jl_peer_merge_buffer_bytes", C.c_size_t, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
+    ("jl_peer_merge", C.c_int, [C.POINTER(PeerMergeArgs), C.c_void_p]),
     ("jl_silu_mul", C.c_int, [C.POINTER(SiluMulArgs), C.c_void_p]),
     ("jl_step_advance", C.c_int, [C.POINTER(StepAdvanceArgs), C.c_void_p]),
     ("jl_decode_append", C.c_int, [C.POINTER(DecodeAppendArgs), C.c_void_p]),

@@ -223,7 +223,7 @@ def fused_jetlong_decode_cache_stripe(query_base, query_group, key_stripe, value
 
 
 def fused_jetlong_decode_step(query_base, query_group, key_rows, value_rows, *, step, inv_freq, group_size: int,
-                              softmax_scale=None, key_group_rows=None):
+                              softmax_scale=None, key_group_rows=None, exchange_slot=None):
     """Decode whose token-dependent facts come from device memory (ops.StepState), so the launch can sit in
     a CUDA graph that is replayed for every new token.  key_rows / value_rows: this rank's WHOLE
     (B, capacity, Hk, D) cache buffers; the far class is rows [0, n_far) (regrouped in-kernel when
@@ -242,6 +242,11 @@ def fused_jetlong_decode_step(query_base, query_group, key_rows, value_rows, *, 
                                                group_size=int(group_size), softmax_scale=softmax_scale, out=out, lse=lse)
     if sh is None:
         return run(None, None)[0]
+    ex = step.peer_exchange(B, H, D) if exchange_slot is not None else None
+    if ex is not None:
+        part_o, part_lse = run(None, None)
+        return ops.peer_merge(part_o, part_lse, ex, epoch_base=step.steps, epoch_stride=int(exchange_slot[1]),
+                              epoch_offset=int(exchange_slot[0]) + 1)
     buf = _partial_buffer(sh, (B, 1, H, D), (B, H, 1), query_base.dtype, query_base.device)
     out, _ = sharded_attention(run, ops.merge_partials, sh, buf)
     return out

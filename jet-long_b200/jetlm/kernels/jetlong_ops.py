@@ -63,7 +63,7 @@ def _st(t: torch.Tensor, i: int) -> int:
 # Instrumentation used by the benchmark: kernel launches issued through this module, and (when a list
 # is installed with set_event_sink) a CUDA event pair around every attention kernel launch.
 KERNELS_PER_CALL = {"jl_prefill": 1, "jl_decode": 2, "jl_merge": 1, "jl_rotate": 1, "jl_norm_rope": 1, "jl_rmsnorm": 1,
-                    "jl_step_advance": 1, "jl_decode_append": 1, "jl_silu_mul": 1}
+                    "jl_step_advance": 1, "jl_decode_append": 1, "jl_silu_mul": 1, "jl_peer_merge": 1}
 LAUNCHES = {name: 0 for name in KERNELS_PER_CALL}
 _EVENT_SINK: Optional[list] = None
 
@@ -535,6 +535,33 @@ class StepState:
         self.state = torch.zeros(N.JL_STEP_STATE_WORDS, dtype=torch.int64, device=device)
         self.lens = torch.zeros(2, batch, dtype=torch.int32, device=device)
 
+    @property
+    def steps(self) -> torch.Tensor:
+        """Number of advances made so far (device scalar, never rewound)."""
+        return self.state[5:6]
+
+    def peer_exchange(self, batch: int, heads: int, head_dim: int):
+        """The peer-memory exchange of this (sharded) state, created on first use; None when the ranks could
+        not all set it up (then the caller exchanges with NCCL)."""
+        if getattr(self, "_peer", None) is None:
+            import os
+            import warnings
+            import torch.distributed as dist
+            from .sequence_parallel import PeerExchange
+            ok, ex = 1, None
+            if os.environ.get("JETLONG_PEER_EXCHANGE", "0") != "1":
+                ok = 0
+            else:
+                try:
+                    ex = PeerExchange(self.shard, batch, heads, head_dim, self.state.device)
+                except Exception as err:            # no symmetric-memory support on this system
+                    warnings.warn(f"peer-memory exchange unavailable ({err}); using NCCL")
+                    ok = 0
+            agree = torch.tensor([ok], dtype=torch.int32, device=self.state.device)
+            dist.all_reduce(agree, op=dist.ReduceOp.MIN, group=self.shard.group)     # all ranks take the same path
+            self._peer = ex if int(agree) == 1 else False
+        return self._peer or None
+
     def set_next_position(self, pos: int) -> None:
         """The next advance() will describe the token at absolute position `pos`."""
         self.state[0] = int(pos) - 1
@@ -609,6 +636,44 @@ def decode_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_weight: t
     with torch.cuda.device(q.device):
         _timed_call("jl_decode_append", lambda: N.lib().jl_decode_append(C.byref(a), _stream()))
     return q_base, (q_group if q_group is not None else q_base)
+
+
+def peer_merge(part_o: torch.Tensor, part_lse: torch.Tensor, exchange, *, epoch_base: Optional[torch.Tensor],
+               epoch_stride: int, epoch_offset: int, return_lse: bool = False):
+    """Push this rank's decode partial (part_o (B,1,H,D) bf16, part_lse (B,H,1) fp32, both contiguous) to all
+    ranks of `exchange` (sequence_parallel.PeerExchange) through peer-mapped memory, wait for theirs and merge
+    (see jl_peer_merge).  The epoch (*epoch_base) * epoch_stride + epoch_offset must be >= 1, equal on all ranks
+    and grow by exactly 1 from one call on this exchange to the next.  Returns out (B,1,H,D) or (out, lse)."""
+    op = "peer_merge"
+    B, one, H, D = part_o.shape
+    if one != 1 or part_o.dtype not in _SUPPORTED_DTYPES or part_lse.dtype != torch.float32 or part_lse.numel() != B * H:
+        raise ValueError(f"{op}: expects part_o (B,1,H,D) bf16 and part_lse (B,H,1) fp32")
+    _require_contiguous(op, "part_o", part_o)
+    _require_contiguous(op, "part_lse", part_lse)
+    if (B, H, D) != (exchange.batch, exchange.heads, exchange.head_dim):
+        raise ValueError(f"{op}: the exchange was built for (batch, heads, head_dim) = "
+                         f"{(exchange.batch, exchange.heads, exchange.head_dim)}, got {(B, H, D)}")
+    _require_arch(op, part_o.device)
+    out = torch.empty_like(part_o)
+    lse = torch.empty(B, H, 1, dtype=torch.float32, device=part_o.device) if return_lse else None
+    a = N.PeerMergeArgs()
+    a.part_o, a.part_lse = part_o.data_ptr(), part_lse.data_ptr()
+    for r, ptr in enumerate(exchange.ptrs):
+        a.peer_buf[r] = ptr
+    a.buffer_bytes = exchange.nbytes
+    a.rank, a.world = exchange.shard.rank, exchange.shard.world
+    a.batch, a.heads, a.head_dim = B, H, D
+    if epoch_base is not None:
+        if epoch_base.numel() != 1 or epoch_base.dtype != torch.int64 or epoch_base.device != part_o.device:
+            raise ValueError(f"{op}: epoch_base must be one int64 on {part_o.device}")
+        a.epoch_base_dev = epoch_base.data_ptr()
+    a.epoch_stride, a.epoch_offset = int(epoch_stride), int(epoch_offset)
+    a.out = out.data_ptr()
+    a.lse_out = lse.data_ptr() if lse is not None else None
+    a.status = exchange.status.data_ptr()
+    with torch.cuda.device(part_o.device):
+        _timed_call("jl_peer_merge", lambda: N.lib().jl_peer_merge(C.byref(a), _stream()))
+    return (out, lse) if return_lse else out
 
 
 def _require_output(op, name, t, shape, dtype, device):

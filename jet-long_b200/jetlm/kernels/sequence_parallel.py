@@ -91,6 +91,35 @@ class PartialBuffer:
         return [self.out_view(r) for r in range(sh.world)], [self.lse_view(r) for r in range(sh.world)]
 
 
+class PeerExchange:
+    """Exchange buffers for `jl_peer_merge`: one symmetric allocation per rank, mapped into every rank of the
+    group (torch symmetric memory: CUDA virtual-memory handles exchanged once at set-up), zeroed, plus the
+    device status word the kernel raises if a bounded wait gives up.  The buffers serve one monotonically
+    growing epoch sequence; create a new object for a new sequence."""
+
+    def __init__(self, shard: SequenceShard, batch: int, heads: int, head_dim: int, device):
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import _native as N
+        self.shard, self.batch, self.heads, self.head_dim = shard, int(batch), int(heads), int(head_dim)
+        self.nbytes = int(N.lib().jl_peer_merge_buffer_bytes(shard.world, batch, heads, head_dim))
+        if self.nbytes == 0:
+            raise ValueError("unsupported shape for the peer exchange")
+        group = shard.group if shard.group is not None else dist.group.WORLD
+        self.buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        if len(self.ptrs) != shard.world or self.ptrs[shard.rank] != self.buf.data_ptr():
+            raise RuntimeError("symmetric memory rendezvous returned an unexpected mapping")
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)             # every rank's zeroes are in place before anyone pushes
+
+    def failed(self) -> bool:
+        """True if a wait inside jl_peer_merge ever gave up (synchronises)."""
+        return bool(self.status.item())
+
+
 def gather_partials(out: torch.Tensor, lse: torch.Tensor, shard: SequenceShard):
     """All-gather one (O, LSE) pair per rank.  out (B,S,H,D), lse (B,H,S) fp32 ->
     (outs (world,B,S,H,D), lses (world,B,H,S)), identical on every rank."""

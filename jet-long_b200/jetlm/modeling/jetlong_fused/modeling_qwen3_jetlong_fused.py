@@ -184,7 +184,8 @@ class Qwen3JetLongFusedAttention(nn.Module):
                                                 group_size=group, k_group_cache=kg)
             attn = backend.fused_jetlong_decode_step(q_base, q_group, slot.keys, slot.values, step=plan.step,
                                                      inv_freq=inv_freq, group_size=group, softmax_scale=self.scaling,
-                                                     key_group_rows=kg)
+                                                     key_group_rows=kg,
+                                                     exchange_slot=(self.layer_idx, self.config.num_hidden_layers))
             return self.o_proj(attn.reshape(*out_shape, -1)), None
 
         if plan.token_shard is not None:

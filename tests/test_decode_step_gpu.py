@@ -25,7 +25,8 @@ def test_step_advance_follows_the_block_cyclic_geometry(world, block, w_0):
         rows = []
         for pos in range(90, 140):
             st.advance()
-            got = st.state.tolist()
+            got, steps = st.state.tolist()[:5], int(st.steps)
+            assert steps == pos - 89                      # advances made on this state, never rewound
             n_owned = (lambda n: sh.n_owned(n)) if sh is not None else (lambda n: n)
             own = 1 if sh is None else int((pos // block) % world == rank)
             n_far = n_owned(max(pos - w_0, 0))
@@ -83,7 +84,7 @@ def test_device_side_segment_geometry_equals_sliced_segments(n_far, n_near):
     mk = lambda *s: torch.randn(*s, device="cuda").bfloat16()
     qb, qg, kc, vc = mk(B, 1, H, D), mk(B, 1, H, D), mk(B, cap, Hk, D), mk(B, cap, Hk, D)
     st = ops.StepState(B, "cuda", 0)
-    st.state.copy_(torch.tensor([0, 0, 1, n_far, n_near]))
+    st.state[:5].copy_(torch.tensor([0, 0, 1, n_far, n_near]))
     st.lens[0] = n_far
     st.lens[1] = n_near
     kw = dict(inv_freq=inv, group_size=G, num_splits=2)

@@ -106,6 +106,31 @@ def _worker(rank, world, port, results):
             toks_n = model.generate_long(ids2[:, : 3 * chunk], max_new_tokens=4, chunk_tokens=chunk)
             toks_g = model.generate_long(ids2[:, : 3 * chunk], max_new_tokens=4, chunk_tokens=chunk, cuda_graph=True)
             assert toks_g.tolist() == toks_n.tolist(), (rank, toks_g.tolist(), toks_n.tolist())
+            os.environ["JETLONG_PEER_EXCHANGE"] = "1"       # the same graph decode with jl_peer_merge instead of NCCL + jl_merge
+            toks_c = model.generate_long(ids2[:, : 3 * chunk], max_new_tokens=4, chunk_tokens=chunk, cuda_graph=True)
+            os.environ.pop("JETLONG_PEER_EXCHANGE")
+            assert toks_c.tolist() == toks_n.tolist(), (rank, toks_c.tolist(), toks_n.tolist())
+            # jl_peer_merge alone: five exchanges of fresh random partials against all-gather + jl_merge
+            from jetlm.kernels import jetlong_ops as jops
+            from jetlm.kernels.sequence_parallel import PeerExchange
+            ex = PeerExchange(shard, 2, 8, 128, torch.device("cuda", rank))
+            epoch = torch.zeros(1, dtype=torch.int64, device="cuda")
+            for it in range(1, 6):
+                gen = torch.Generator(device="cuda").manual_seed(1000 * it + rank)
+                po = torch.randn(2, 1, 8, 128, device="cuda", generator=gen).bfloat16()
+                pl = torch.randn(2, 8, 1, device="cuda", generator=gen) * 3
+                if it == 3 and rank == 0:
+                    pl.fill_(float("-inf"))                 # a rank without keys contributes nothing
+                epoch.fill_(it)
+                got_o, got_l = jops.peer_merge(po, pl, ex, epoch_base=epoch, epoch_stride=1, epoch_offset=0, return_lse=True)
+                all_o = [torch.empty_like(po) for _ in range(world)]
+                all_l = [torch.empty_like(pl) for _ in range(world)]
+                dist.all_gather(all_o, po)
+                dist.all_gather(all_l, pl)
+                want_o, want_l = jops.merge_partials(all_o, all_l)
+                assert torch.equal(got_o, want_o), (rank, it, (got_o.float() - want_o.float()).abs().max())
+                assert torch.allclose(got_l, want_l, atol=1e-5), (rank, it)
+            assert not ex.failed()
             gathered = [torch.empty_like(toks_n) for _ in range(world)]
             dist.all_gather(gathered, toks_n)
             be.configure_sequence_sharding(None)
