@@ -549,7 +549,7 @@ class StepState:
             import torch.distributed as dist
             from .sequence_parallel import PeerExchange
             ok, ex = 1, None
-            if os.environ.get("JETLONG_PEER_EXCHANGE", "0") != "1":
+            if os.environ.get("JETLONG_PEER_EXCHANGE", "1") == "0":
                 ok = 0
             else:
                 try:

@@ -106,7 +106,7 @@ def _worker(rank, world, port, results):
             toks_n = model.generate_long(ids2[:, : 3 * chunk], max_new_tokens=4, chunk_tokens=chunk)
             toks_g = model.generate_long(ids2[:, : 3 * chunk], max_new_tokens=4, chunk_tokens=chunk, cuda_graph=True)
             assert toks_g.tolist() == toks_n.tolist(), (rank, toks_g.tolist(), toks_n.tolist())
-            os.environ["JETLONG_PEER_EXCHANGE"] = "1"       # the same graph decode with jl_peer_merge instead of NCCL + jl_merge
+            os.environ["JETLONG_PEER_EXCHANGE"] = "0"       # the same graph decode with NCCL all-gather + jl_merge instead of jl_peer_merge
             toks_c = model.generate_long(ids2[:, : 3 * chunk], max_new_tokens=4, chunk_tokens=chunk, cuda_graph=True)
             os.environ.pop("JETLONG_PEER_EXCHANGE")
             assert toks_c.tolist() == toks_n.tolist(), (rank, toks_c.tolist(), toks_n.tolist())
