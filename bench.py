@@ -230,6 +230,7 @@ def decode_microbench(peaks, shard, iters=20):
         flush_rd.max()
 
     inv = 1.0 / (1.0e6 ** (torch.arange(0, D, 2, device="cuda").float() / D))
+    exchange_used = {}
     for B in (1, 8):
         torch.manual_seed(0)
         q = torch.randn(B, 1, H, D, device="cuda").bfloat16()
@@ -238,16 +239,34 @@ def decode_microbench(peaks, shard, iters=20):
         vc = torch.randn(B, Hk, ctx, D, device="cuda").bfloat16()
         boundary = ctx - 1 - w0
         kv, vv = kc.transpose(1, 2), vc.transpose(1, 2)
+        call = lambda exchange, **kw: backend.fused_jetlong_decode_cache(
+            q, qg, kc, vc, boundary=boundary, inv_freq=inv, group_size=G, has_any_pad=False, training=False,
+            exchange=exchange, **kw)
+        variants = []
         if shard is None:
             segs = [ops.KvSegment(kv[:, :boundary], vv[:, :boundary], 1), ops.KvSegment(kv[:, boundary:], vv[:, boundary:], 0)]
-            fn_pre = lambda: ops.decode_segments([q, qg], segs, return_lse=False)
-        else:       # sharded: every rank streams its contiguous range; kc doubles as the regrouped cache (same bytes moved)
-            fn_pre = lambda: backend.fused_jetlong_decode_cache(q, qg, kc, vc, boundary=boundary, inv_freq=inv, group_size=G,
-                                                                has_any_pad=False, training=False, key_cache_group=kc)
-        fn_inplace = lambda: backend.fused_jetlong_decode_cache(q, qg, kc, vc, boundary=boundary, inv_freq=inv, group_size=G,
-                                                                has_any_pad=False, training=False)
+            variants.append(("pregrouped", lambda: ops.decode_segments([q, qg], segs, return_lse=False)))
+            variants.append(("inplace_regroup", lambda: call(None)))
+        else:
+            # sharded: every rank streams its contiguous range (kc doubles as the regrouped cache: same bytes moved);
+            # the partials cross NVLink through jl_peer_merge if every rank can set it up AND it reproduces the
+            # NCCL all-gather + jl_merge result here, else through NCCL
+            exch = "nccl"
+            try:
+                ok = int(torch.equal(call("peer"), call("nccl")))
+            except Exception:
+                ok = 0
+            agree = torch.tensor([ok], device="cuda")
+            torch.distributed.all_reduce(agree, op=torch.distributed.ReduceOp.MIN)
+            if int(agree) == 1:
+                exch = "peer"
+            exchange_used[f"batch{B}"] = exch
+            variants.append(("pregrouped", lambda: call(exch, key_cache_group=kc)))
+            variants.append(("inplace_regroup", lambda: call(exch)))
+            if exch == "peer":
+                variants.append(("pregrouped_nccl_exchange", lambda: call("nccl", key_cache_group=kc)))
         res = {}
-        for tag, fn in (("pregrouped", fn_pre), ("inplace_regroup", fn_inplace)):
+        for tag, fn in variants:
             if fn is None:
                 continue
             for _ in range(3):
@@ -287,7 +306,10 @@ def decode_microbench(peaks, shard, iters=20):
         out[f"batch{B}"] = res
         del kc, vc, kv, vv
     out["config"] = dict(heads=H, kv_heads=Hk, head_dim=D, ctx=ctx, w_0=w0, group_size=G,
-                         timing="CUDA graph replay" if shard is None else "CUDA graph replay incl. NCCL all-gather (eager if capture fails), max over ranks",
+                         timing="CUDA graph replay" if shard is None else
+                         "CUDA graph replay incl. the exchange of the partials (eager if capture fails), max over ranks",
+                         exchange={k: ("jl_peer_merge over peer-mapped memory" if v == "peer" else "NCCL all-gather + jl_merge")
+                                   for k, v in exchange_used.items()} or None,
                          l2="256 MB write + 256 MB read before every iteration (cold, clean L2)")
     return out
 

@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from . import jetlong_ops as ops
-from .sequence_parallel import PartialBuffer, SequenceShard, sharded_attention
+from .sequence_parallel import PartialBuffer, SequenceShard, make_peer_exchange, sharded_attention
 
 _SHARD: SequenceShard | None = None
 _BUFFERS: dict[tuple, PartialBuffer] = {}
@@ -24,6 +24,32 @@ def _partial_buffer(shard, out_shape, lse_shape, dtype, device) -> PartialBuffer
     if buf is None:
         buf = _BUFFERS[key] = PartialBuffer(shard, out_shape, lse_shape, dtype, device)
     return buf
+
+
+_PEERS: dict[tuple, object] = {}
+
+
+def _sharded_decode(part, sh, query_base, return_lse: bool, exchange):
+    """Exchange and merge the ranks' decode partials.  part(out, lse) runs this rank's kernel (into the given
+    tensors, or fresh ones when they are None).  exchange: "peer" = jl_peer_merge over peer-mapped memory,
+    "nccl" = all-gather + jl_merge, None = peer when the ranks can set it up, else NCCL."""
+    B, _, H, D = query_base.shape
+    ex = None
+    if exchange != "nccl":
+        key = (sh.rank, sh.world, B, H, D, query_base.device)
+        if key not in _PEERS:
+            _PEERS[key] = make_peer_exchange(sh, B, H, D, query_base.device)
+        ex = _PEERS[key]
+        if ex is None and exchange == "peer":
+            raise RuntimeError("the peer-memory exchange could not be set up on every rank")
+    if ex is not None:
+        part_o, part_lse = part(None, None)
+        ex.epoch.add_(1)                    # in-stream, so a captured graph advances it on every replay
+        return ops.peer_merge(part_o, part_lse, ex, epoch_base=ex.epoch, epoch_stride=1, epoch_offset=0,
+                              return_lse=return_lse)
+    buf = _partial_buffer(sh, (B, 1, H, D), (B, H, 1), query_base.dtype, query_base.device)
+    out, lse = sharded_attention(part, ops.merge_partials, sh, buf)
+    return (out, lse) if return_lse else out
 
 
 def configure_sequence_sharding(shard: SequenceShard | None) -> None:
@@ -162,7 +188,7 @@ def fused_jetlong_decode(query_base, query_group, key_near, value_near, key_dist
 
 def fused_jetlong_decode_cache(query_base, query_group, key_cache, value_cache, *, boundary: int, inv_freq,
                                group_size: int, softmax_scale=None, has_any_pad: bool, training: bool,
-                               cache_pos0: int = 0, return_lse: bool = False, key_cache_group=None):
+                               cache_pos0: int = 0, return_lse: bool = False, key_cache_group=None, exchange=None):
     """Decode straight off a base-rotated (B,Hk,S,D) cache: keys [0, boundary) are the far class and are
     regrouped inside the kernel while they stream, keys [boundary, S) are the near class.  Replaces the
     reference's per-token host-side regroup of the whole distant cache plus its slice / pad copies
@@ -182,15 +208,13 @@ def fused_jetlong_decode_cache(query_base, query_group, key_cache, value_cache, 
         part = lambda out, lse: _decode_range(query_base, query_group, kc[:, lo:hi], vc[:, lo:hi], int(boundary) - lo, lo,
                                               inv_freq, group_size, softmax_scale, True, out=out, lse=lse,
                                               kg=kg[:, lo:hi] if kg is not None else None)
-        buf = _partial_buffer(sh, (B, 1, H, D), (B, H, 1), query_base.dtype, query_base.device)
-        out, lse = sharded_attention(part, ops.merge_partials, sh, buf)
-        return (out, lse) if return_lse else out
+        return _sharded_decode(part, sh, query_base, return_lse, exchange)
     return _decode_range(query_base, query_group, kc, vc, int(boundary) - int(cache_pos0), int(cache_pos0),
                          inv_freq, group_size, softmax_scale, return_lse, kg=kg)
 
 
 def fused_jetlong_decode_cache_stripe(query_base, query_group, key_stripe, value_stripe, *, boundary: int, inv_freq,
-                                      group_size: int, softmax_scale=None, return_lse: bool = False):
+                                      group_size: int, softmax_scale=None, return_lse: bool = False, exchange=None):
     """Decode when every rank holds only its block-cyclic stripe of the base-rotated cache, as the
     token-sharded prefill leaves it: key_stripe / value_stripe (B,Hk,S_loc,D), local row i at position
     rank*blk + (i // blk) * world*blk + i % blk.  Local rows below `boundary` are the far class
@@ -211,15 +235,14 @@ def fused_jetlong_decode_cache_stripe(query_base, query_group, key_stripe, value
         if n_far < kc.shape[1]:
             segs.append(ops.KvSegment(kc[:, n_far:], vc[:, n_far:], q_class=0))
         if not segs:                       # this rank owns no key yet: an empty partial
-            out.zero_()
-            lse.fill_(float("-inf"))
+            out = torch.zeros_like(query_base) if out is None else out.zero_()
+            lse = (torch.full((B, H, 1), float("-inf"), device=query_base.device) if lse is None
+                   else lse.fill_(float("-inf")))
             return out, lse
         return ops.decode_segments([query_base, query_group], segs, inv_freq=inv_freq, group_size=int(group_size),
                                    softmax_scale=softmax_scale, out=out, lse=lse)
 
-    buf = _partial_buffer(sh, (B, 1, H, D), (B, H, 1), query_base.dtype, query_base.device)
-    out, lse = sharded_attention(part, ops.merge_partials, sh, buf)
-    return (out, lse) if return_lse else out
+    return _sharded_decode(part, sh, query_base, return_lse, exchange)
 
 
 def fused_jetlong_decode_step(query_base, query_group, key_rows, value_rows, *, step, inv_freq, group_size: int,

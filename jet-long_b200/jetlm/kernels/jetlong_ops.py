@@ -544,22 +544,8 @@ class StepState:
         """The peer-memory exchange of this (sharded) state, created on first use; None when the ranks could
         not all set it up (then the caller exchanges with NCCL)."""
         if getattr(self, "_peer", None) is None:
-            import os
-            import warnings
-            import torch.distributed as dist
-            from .sequence_parallel import PeerExchange
-            ok, ex = 1, None
-            if os.environ.get("JETLONG_PEER_EXCHANGE", "1") == "0":
-                ok = 0
-            else:
-                try:
-                    ex = PeerExchange(self.shard, batch, heads, head_dim, self.state.device)
-                except Exception as err:            # no symmetric-memory support on this system
-                    warnings.warn(f"peer-memory exchange unavailable ({err}); using NCCL")
-                    ok = 0
-            agree = torch.tensor([ok], dtype=torch.int32, device=self.state.device)
-            dist.all_reduce(agree, op=dist.ReduceOp.MIN, group=self.shard.group)     # all ranks take the same path
-            self._peer = ex if int(agree) == 1 else False
+            from .sequence_parallel import make_peer_exchange
+            self._peer = make_peer_exchange(self.shard, batch, heads, head_dim, self.state.device) or False
         return self._peer or None
 
     def set_next_position(self, pos: int) -> None:

@@ -112,12 +112,32 @@ class PeerExchange:
         if len(self.ptrs) != shard.world or self.ptrs[shard.rank] != self.buf.data_ptr():
             raise RuntimeError("symmetric memory rendezvous returned an unexpected mapping")
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.epoch = torch.zeros(1, dtype=torch.int64, device=device)     # for callers without an epoch source of their own
         torch.cuda.synchronize(device)
         dist.barrier(group=group)             # every rank's zeroes are in place before anyone pushes
 
     def failed(self) -> bool:
         """True if a wait inside jl_peer_merge ever gave up (synchronises)."""
         return bool(self.status.item())
+
+
+def make_peer_exchange(shard: SequenceShard, batch: int, heads: int, head_dim: int, device) -> Optional[PeerExchange]:
+    """A PeerExchange if EVERY rank of the shard could set one up (the ranks agree through an all-reduce, so they
+    all take the same path), else None.  JETLONG_PEER_EXCHANGE=0 disables it."""
+    import os
+    import warnings
+    ok, ex = 1, None
+    if os.environ.get("JETLONG_PEER_EXCHANGE", "1") == "0":
+        ok = 0
+    else:
+        try:
+            ex = PeerExchange(shard, batch, heads, head_dim, device)
+        except Exception as err:                # no symmetric-memory support on this system
+            warnings.warn(f"peer-memory exchange unavailable ({err}); using NCCL")
+            ok = 0
+    agree = torch.tensor([ok], dtype=torch.int32, device=device)
+    dist.all_reduce(agree, op=dist.ReduceOp.MIN, group=shard.group)
+    return ex if int(agree) == 1 else None
 
 
 def gather_partials(out: torch.Tensor, lse: torch.Tensor, shard: SequenceShard):
