@@ -256,7 +256,7 @@ def gen_model(reference_root, ref_tests, name, *, seed, S_prefill, n_decode, w, 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a Jet-Long checkout (its code is imported, never copied)")
     args = ap.parse_args()
     root = os.path.abspath(args.reference)
     sys.path.insert(0, root)
