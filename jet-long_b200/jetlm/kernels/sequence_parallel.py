@@ -91,6 +91,9 @@ class PartialBuffer:
         return [self.out_view(r) for r in range(sh.world)], [self.lse_view(r) for r in range(sh.world)]
 
 
+PEER_EXCHANGE_VALIDATED_WORLDS = (2,)      # rank counts on which jl_peer_merge has been run against the NCCL path
+
+
 class PeerExchange:
     """Exchange buffers for `jl_peer_merge`: one symmetric allocation per rank, mapped into every rank of the
     group (torch symmetric memory: CUDA virtual-memory handles exchanged once at set-up), zeroed, plus the
@@ -123,11 +126,13 @@ class PeerExchange:
 
 def make_peer_exchange(shard: SequenceShard, batch: int, heads: int, head_dim: int, device) -> Optional[PeerExchange]:
     """A PeerExchange if EVERY rank of the shard could set one up (the ranks agree through an all-reduce, so they
-    all take the same path), else None.  JETLONG_PEER_EXCHANGE=0 disables it."""
+    all take the same path), else None.  JETLONG_PEER_EXCHANGE=0 disables it, =1 enables it for any rank count;
+    unset, it is used for the rank counts it has been validated on (PEER_EXCHANGE_VALIDATED_WORLDS)."""
     import os
     import warnings
     ok, ex = 1, None
-    if os.environ.get("JETLONG_PEER_EXCHANGE", "1") == "0":
+    mode = os.environ.get("JETLONG_PEER_EXCHANGE", "")
+    if mode == "0" or (mode != "1" and shard.world not in PEER_EXCHANGE_VALIDATED_WORLDS):
         ok = 0
     else:
         try:
