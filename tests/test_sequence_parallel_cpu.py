@@ -74,6 +74,16 @@ def _worker(rank, world, port, block, results):
         eod, eld = orc.jetlong_decode(q1, q1g, kb[:, boundary:], v[:, boundary:], kg[:, :boundary], v[:, :boundary])
         dd, _ = orc.compare(od, eod)
         dld, _ = orc.compare(ld, eld)
+        # the peer-memory exchange cannot be set up on CPU ranks: every rank must learn that (one all-reduce)
+        # and take the collective path together, whatever the environment asks for
+        import warnings
+        from jetlm.kernels.sequence_parallel import make_peer_exchange
+        for mode in ("", "0", "1"):
+            os.environ["JETLONG_PEER_EXCHANGE"] = mode
+            with warnings.catch_warnings():
+                warnings.simplefilter("ignore")
+                assert make_peer_exchange(shard, 1, H, D, torch.device("cpu")) is None
+        os.environ.pop("JETLONG_PEER_EXCHANGE")
         results[rank] = (d, cos, dl, dd, dld)
     finally:
         dist.destroy_process_group()
