@@ -196,14 +196,9 @@ __device__ __forceinline__ uint64_t exp2_pair_fma(uint64_t x) {
   const uint64_t magic = pack2(12582912.f, 12582912.f);
   const uint64_t t = add2_round_down(x, magic);
   const uint64_t f = sub2(x, sub2(t, magic));
-#ifdef JL_POLY_DEG2
-  uint64_t q = fma2(pack2(0.3371894359588623f, 0.3371894359588623f), f, pack2(0.657636284828186f, 0.657636284828186f));
-  q = fma2(q, f, pack2(1.0017247200012207f, 1.0017247200012207f));
-#else
   uint64_t q = fma2(pack2(0.07802429050207138f, 0.07802429050207138f), f, pack2(0.22606779634952545f, 0.22606779634952545f));
   q = fma2(q, f, pack2(0.695833146572113f, 0.695833146572113f));
   q = fma2(q, f, pack2(0.9999252557754517f, 0.9999252557754517f));
-#endif
   float t0, t1, q0, q1;
   unpack2(t, t0, t1);
   unpack2(q, q0, q1);
