@@ -112,7 +112,7 @@ class ClockSampler:
 # CPU baseline: the oracle (a restatement of the reference's eager composition) on the host cores
 # --------------------------------------------------------------------------------------------------
 
-def cpu_prefill_sample(S: int, dims: dict, w_0: int, G: int, blocks: int = 16):
+def cpu_prefill_sample(S: int, dims: dict, w_0: int, G: int, blocks: int = 24):
     """Time a bounded sample of the prefill workload on the CPU (about 10-20 s at the default size) and
     extrapolate to tokens/s.
 
