@@ -92,3 +92,24 @@ def test_stock_attention_runs_on_the_static_cache():
         outs.append(torch.cat(logits, dim=1))
         assert cache.get_seq_length() == 40
     assert torch.allclose(outs[0], outs[1], atol=1e-5, rtol=1e-5)
+
+
+@torch.inference_mode()
+def test_hf_generate_accepts_the_static_cache():
+    """HF `generate` (chunked prefill, greedy) with the preallocated cache passed as past_key_values returns the
+    tokens it returns with its own DynamicCache."""
+    from transformers import GenerationConfig
+    from jetlm.kernels.kv_cache import BifocalKVCache
+    from jetlm.modeling.jetlong_fused import Qwen3JetLongFusedForCausalLM
+    cfg = _cfg()
+    cfg.jetlong["w"], cfg.jetlong["w_0"] = 4096, 16
+    torch.manual_seed(3)
+    model = Qwen3JetLongFusedForCausalLM(cfg).eval()
+    ids = torch.randint(0, 160, (1, 40))
+    gen = GenerationConfig(max_new_tokens=5, do_sample=False, pad_token_id=0, eos_token_id=None,
+                           prefill_chunk_size=16, disable_compile=True)
+    want = model.generate(ids, generation_config=gen)
+    cache = BifocalKVCache(cfg, 64, batch=1, device="cpu", dtype=torch.float32)
+    got = model.generate(ids, generation_config=gen, past_key_values=cache)
+    assert got.tolist() == want.tolist()
+    assert cache.get_seq_length() == 44
