@@ -182,44 +182,56 @@ def model_dims(cfg):
 
 
 def run_reference(args):
+    """The reference's CPU path for the same config on all host cores: rank 0 alone works (the other ranks of a
+    torchrun launch exit at once).  The sample is deterministic, so a few repeats are enough: one small warm-up
+    and best of min(steps, 3) full samples, whatever --steps / --warmup say (they are echoed in the line)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torch.distributed.run exports OMP_NUM_THREADS=1 to its workers; the CPU baseline is meant to use the box
+    torch.set_num_threads(os.cpu_count() or 1)
     cfg = model_config(args.model, args.w, args.w0, args.layers)
     G = max(1, math.ceil(args.seq / args.w))
-    for _ in range(max(args.warmup, 0)):
-        cpu_prefill_sample(min(args.seq, 8192), model_dims(cfg), min(args.w0, 2048), G)
-    res = [cpu_prefill_sample(args.seq, model_dims(cfg), args.w0, G) for _ in range(max(args.steps, 1))]
+    if args.warmup > 0:
+        cpu_prefill_sample(min(args.seq, 8192), model_dims(cfg), min(args.w0, 2048), G, blocks=8)
+    res = [cpu_prefill_sample(args.seq, model_dims(cfg), args.w0, G) for _ in range(max(1, min(args.steps, 3)))]
     best = max(res, key=lambda r: r["tok_s"])
-    line = dict(metric="prefill_tok_per_s", value=best["tok_s"], unit="tok/s", n_gpus=args.gpus, steps=args.steps,
+    value = float(f"{best['tok_s']:.3g}")
+    line = dict(metric="prefill_tok_per_s", value=value, unit="tok/s", n_gpus=args.gpus, steps=args.steps,
                 warmup=args.warmup, ms_per_step=best["est_total_s"] * 1e3, higher_is_better=True, scaling="strong",
                 vs_baseline=None, dtype="f32", data="synthetic", impl="reference",
                 config=workload_config(args, cfg, G),
-                cpu_baseline=dict(value=best["tok_s"], unit="tok/s", cores=best["cores"], kind="port", sample=best["sample"]),
-                e2e=dict(value=best["tok_s"], unit="tok/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+                cpu_baseline=dict(value=value, unit="tok/s", cores=best["cores"], kind="port", sample=best["sample"],
+                                  samples_timed=len(res), spread=[float(f"{r['tok_s']:.3g}") for r in res]),
+                e2e=dict(value=value, unit="tok/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
                 note="reference fused kernels are gated to sm_90 and need flash_attn.cute (not installed): the reference's "
-                     "eager composition (restated in oracle/) is timed on the host cores on a bounded sample and extrapolated")
+                     "eager composition (restated in oracle/) is timed on the host cores on a bounded sample and extrapolated; "
+                     "run-to-run spread of the sample is 5-20 %, so the value carries two to three significant digits")
     print(json.dumps(line), flush=True)
 
 
-def workload_config(args, cfg, G):
+def workload_config(args, cfg, G, sp_mode="kv_gather"):
     return dict(workload=f"{args.model} jetlong_fused full-model prefill, batch 1, {args.seq} tokens",
                 layers=cfg.num_hidden_layers, heads=cfg.num_attention_heads, kv_heads=cfg.num_key_value_heads,
                 head_dim=128, hidden=cfg.hidden_size, w=args.w, w_0=args.w0, group_size=G,
                 logits="all positions (reference bench protocol)" if args.logits_to_keep == 0 else f"last {args.logits_to_keep}",
                 l2="inputs and weights far exceed the 126 MB L2; decode microbench flushes L2 (256 MB write + 256 MB read) between iterations",
-                parallelism=(f"sequence-parallel x{args.gpus}: tokens and KV cache block-cyclic over ranks, Q all-gather, "
-                             f"partial (O,LSE) all-to-all + N-way merge") if args.gpus > 1 else "single GPU")
+                parallelism=(f"sequence-parallel x{args.gpus}: tokens and KV cache block-cyclic over ranks (block {SP_BLOCK}); "
+                             "per layer all-gather of K_base and V, local regroup, one launch of this rank's query stripe "
+                             "against all keys" if sp_mode == "kv_gather" else
+                             f"sequence-parallel x{args.gpus}: tokens and KV cache block-cyclic over ranks (block {SP_BLOCK}), "
+                             "Q all-gather, partial (O,LSE) all-to-all + N-way merge") if args.gpus > 1 else "single GPU")
 
 
 # --------------------------------------------------------------------------------------------------
 # decode-attention microbench (the reference's protocol: CUDA graph, 256 MB L2 flush, median)
 # --------------------------------------------------------------------------------------------------
 
-def decode_microbench(peaks, shard, iters=20):
+def decode_microbench(peaks, shard, iters=20, ctx=131072, w0=32768, batches=(1, 8), variants_wanted=None):
     from jetlm.kernels import cute_jetlong_backend as backend, jetlong_ops as ops
     out = {}
-    H, Hk, D, ctx, w0, G = 32, 8, 128, 131072, 32768, 4
+    H, Hk, D, G = 32, 8, 128, 4
+    world = shard.world if shard is not None else 1
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     flush_rd = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda")
 
@@ -231,7 +243,7 @@ def decode_microbench(peaks, shard, iters=20):
 
     inv = 1.0 / (1.0e6 ** (torch.arange(0, D, 2, device="cuda").float() / D))
     exchange_used = {}
-    for B in (1, 8):
+    for B in batches:
         torch.manual_seed(0)
         q = torch.randn(B, 1, H, D, device="cuda").bfloat16()
         qg = torch.randn(B, 1, H, D, device="cuda").bfloat16()
@@ -267,7 +279,7 @@ def decode_microbench(peaks, shard, iters=20):
                 variants.append(("pregrouped_nccl_exchange", lambda: call("nccl", key_cache_group=kc)))
         res = {}
         for tag, fn in variants:
-            if fn is None:
+            if fn is None or (variants_wanted is not None and tag not in variants_wanted):
                 continue
             for _ in range(3):
                 fn()
@@ -300,17 +312,228 @@ def decode_microbench(peaks, shard, iters=20):
                 t = torch.tensor([us], device="cuda")
                 torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
                 us = float(t)
-            nbytes = B * ctx * Hk * D * 2 * 2
-            res[tag] = dict(us=round(us, 2), gbs=round(nbytes / us / 1e3, 1),
-                            frac_of_measured_hbm=round(nbytes / us / 1e3 / peaks["hbm_gbs"], 4))
+            nbytes = B * ctx * Hk * D * 2 * 2 / world            # K and V bytes ONE rank streams, against one GPU's peak
+            res[tag] = dict(us=round(us, 2), gbs_per_gpu=round(nbytes / us / 1e3, 1),
+                            frac_of_measured_hbm=round(nbytes / us / 1e3 / peaks["hbm_gbs"], 4),
+                            frac_of_nominal_8tbs=round(nbytes / us / 1e3 / 8000.0, 4))
         out[f"batch{B}"] = res
         del kc, vc, kv, vv
     out["config"] = dict(heads=H, kv_heads=Hk, head_dim=D, ctx=ctx, w_0=w0, group_size=G,
+                         bytes="K and V bytes one rank streams per call (batch * ctx * kv_heads * head_dim * 2 * 2 / ranks); the "
+                               "denominator is a copy bandwidth, which a read-only stream can exceed by a few percent",
                          timing="CUDA graph replay" if shard is None else
                          "CUDA graph replay incl. the exchange of the partials (eager if capture fails), max over ranks",
                          exchange={k: ("jl_peer_merge over peer-mapped memory" if v == "peer" else "NCCL all-gather + jl_merge")
                                    for k, v in exchange_used.items()} or None,
                          l2="256 MB write + 256 MB read before every iteration (cold, clean L2)")
+    return out
+
+
+# --------------------------------------------------------------------------------------------------
+# instrumentation: launches that go through the C ABI are counted here, not in the product modules
+# --------------------------------------------------------------------------------------------------
+
+class LaunchCounter:
+    """Wraps the kernel-launching entry points of the loaded library object: counts the kernels each call
+    launches and, while `sink` is a list, brackets every jl_prefill call with a CUDA event pair on the stream
+    the kernel is launched on."""
+    KERNELS_PER_CALL = {"jl_prefill": 1, "jl_decode": 1, "jl_decode_static": 1, "jl_merge": 1, "jl_rotate": 1,
+                        "jl_norm_rope": 1, "jl_rmsnorm": 1, "jl_step_advance": 1, "jl_decode_append": 1,
+                        "jl_silu_mul": 1, "jl_peer_merge": 1}
+
+    def __init__(self, lib):
+        self.count, self.sink = 0, None
+        for name, n in self.KERNELS_PER_CALL.items():
+            setattr(lib, name, self._wrap(getattr(lib, name), name, n))
+
+    def _wrap(self, fn, name, n):
+        def call(*a):
+            self.count += n
+            if self.sink is None or name != "jl_prefill":
+                return fn(*a)
+            stream = torch.cuda.current_stream()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record(stream)
+            rc = fn(*a)
+            e.record(stream)
+            self.sink.append((s, e))
+            return rc
+        return call
+
+
+def profiled_traffic_bytes(seq: int):
+    """DRAM read + write bytes of one jl_prefill launch, from the committed ncu summary of the 32768-token case
+    (profiles/), scaled by tokens: every operand crosses HBM once and K/V re-reads are L2 hits, so traffic grows
+    in proportion to the sequence length.  None if the summary is missing."""
+    import re
+    path = os.path.join(ROOT, "profiles", "prefill_tc_kernel__qwen3-8b_1layer_32k.md")
+    try:
+        text = open(path).read()
+        rd = re.search(r"dram__bytes_read\.sum`?\s*\|\s*([0-9.]+)\s*MB", text)
+        wr = re.search(r"dram__bytes_write\.sum`?\s*\|\s*([0-9.]+)\s*MB", text)
+        return round((float(rd.group(1)) + float(wr.group(1))) * 1e6 * seq / 32768)
+    except (OSError, AttributeError, ValueError):
+        return None
+
+
+SP_BLOCK = 256       # tokens per placement block of the sequence-parallel runs (a multiple of the 256 query rows of a CTA)
+
+
+@torch.inference_mode()
+def sharded_parity(shard):
+    """One layer's token-sharded attention, both exchanges, on a 4 x world x 1024-token case against the same
+    rank's UNSHARDED kernel on the whole problem: max-abs and cosine over this rank's rows, worst rank reported."""
+    import torch.distributed as dist
+    from jetlm.kernels import cute_jetlong_backend as backend, jetlong_ops as ops
+    world, blk = shard.world, shard.block
+    S, H, Hk, D, G = 4 * world * 1024, 32, 8, 128, 4
+    w0 = S // 4
+    torch.manual_seed(1234)                                   # the same tensors on every rank
+    inv = (1.0 / (1.0e6 ** (torch.arange(0, D, 2, device="cuda").float() / D)))
+    q = torch.randn(1, S, H, D, device="cuda").bfloat16()
+    k = torch.randn(1, S, Hk, D, device="cuda").bfloat16()
+    v = torch.randn(1, S, Hk, D, device="cuda").bfloat16()
+    ref = ops.posmap_prefill([q, ops.rope_regroup(q, inv, group_size=G)], [k, ops.rope_regroup(k, inv, group_size=G)], v,
+                             pmap=ops.PositionMap.jetlong(w0), q_pos0=0, return_lse=False)
+    rows = shard.owned_rows(S).cuda()
+    ql, kl, vl = q[:, rows].contiguous(), k[:, rows].contiguous(), v[:, rows].contiguous()
+    res = {}
+    for mode in ("kv_gather", "q_exchange"):
+        got = backend.fused_jetlong_prefill_token_sharded(ql, kl, None, vl, q_start=0, inv_freq=inv, group_size=G,
+                                                          window_size_left=w0, softmax_scale=D ** -0.5, mode=mode)
+        a, e = got.float().flatten().double(), ref[:, rows].float().flatten().double()
+        stats = torch.tensor([float((a - e).abs().max()), -float((a @ e) / (a.norm() * e.norm()))], device="cuda")
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        res[mode] = dict(max_abs=round(float(stats[0]), 5), cos=round(-float(stats[1]), 7))
+    res["case"] = f"{S} tokens, 32/8 heads, w_0 {w0}, G {G}, block {blk}; tolerance 2e-2 / 0.9999"
+    res["ok"] = all(res[m]["max_abs"] <= 2e-2 and res[m]["cos"] >= 0.9999 for m in ("kv_gather", "q_exchange"))
+    return res
+
+
+# --------------------------------------------------------------------------------------------------
+# the other BASELINE configurations, as numbers (N = 1 only; the default line stays the metric config)
+# --------------------------------------------------------------------------------------------------
+
+def _time_ms(fn, iters=3, warm=2):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    return statistics.median(ts)
+
+
+@torch.inference_mode()
+def prefill_length_sweep(model, cfg, lengths, w):
+    """Full-model prefill tok/s of the resident model at shorter prompts (the reference's sweep protocol:
+    scripts/throughput/bench_prefill_throughput.py:59-60), same w; w_0 = w."""
+    out = {}
+    gen = torch.Generator().manual_seed(2)
+    for n in lengths:
+        ids = torch.randint(0, cfg.vocab_size, (1, n), generator=gen).cuda()
+        ms = _time_ms(lambda: model(input_ids=ids, use_cache=True, logits_to_keep=0).logits[0, -1], iters=2, warm=2)
+        out[str(n)] = dict(tok_per_s=round(n / ms * 1e3, 1), ms=round(ms, 1), group_size=max(1, math.ceil(n / w)))
+    return out
+
+
+@torch.inference_mode()
+def extra_configs(peaks, args):
+    """BASELINE configs 2 and 3, the reference decode bench's other protocol points, and a same-box library anchor."""
+    from jetlm.kernels import jetlong_ops as ops
+    from jetlm.modeling.jetlong_fused import Qwen3JetLongFusedForCausalLM
+    out = {}
+    D = 128
+    # config 2: Qwen3-1.7B full-model prefill, 65536 tokens, w_0 = 32768
+    cfg2 = model_config("qwen3-1.7b", 32768, 32768, None)
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    torch.manual_seed(0)
+    with torch.device("cuda"):
+        m2 = Qwen3JetLongFusedForCausalLM(cfg2).eval()
+    torch.set_default_dtype(prev)
+    ids = torch.randint(0, cfg2.vocab_size, (1, 65536), generator=torch.Generator().manual_seed(3)).cuda()
+    lib = sys.modules["jetlm.kernels._native"].lib()
+    counter = getattr(lib, "_bench_counter", None)
+    if counter is not None:
+        counter.sink = []
+    ms = _time_ms(lambda: m2(input_ids=ids, use_cache=True, logits_to_keep=0).logits[0, -1], iters=3, warm=2)
+    H2 = cfg2.num_attention_heads
+    flops2 = 4.0 * D * H2 * 65536 * 65537 / 2
+    attn_ms = None
+    if counter is not None and counter.sink:
+        torch.cuda.synchronize()
+        attn_ms = statistics.mean(s.elapsed_time(e) for s, e in counter.sink)
+        counter.sink = None
+    out["config2_qwen3_1.7b_65536"] = dict(
+        tok_per_s=round(65536 / ms * 1e3, 1), ms_per_step=round(ms, 1), layers=cfg2.num_hidden_layers, heads=H2,
+        jl_prefill_mean_ms=round(attn_ms, 3) if attn_ms else None,
+        jl_prefill_tflops=round(flops2 / (attn_ms * 1e-3) / 1e12, 1) if attn_ms else None,
+        frac_of_sustained_bf16=round(flops2 / (attn_ms * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"], 4) if attn_ms else None)
+    del m2, ids
+    torch.cuda.empty_cache()
+
+    # config 3: Qwen3-4B head geometry (32 / 8 heads), 131072 tokens, three position maps through one kernel family
+    S, H, Hk = 131072, 32, 8
+    inv = 1.0 / (1.0e6 ** (torch.arange(0, D, 2, device="cuda").float() / D))
+    torch.manual_seed(4)
+    q = torch.randn(1, S, H, D, device="cuda").bfloat16()
+    k = torch.randn(1, S, Hk, D, device="cuda").bfloat16()
+    v = torch.randn(1, S, Hk, D, device="cuda").bfloat16()
+    flops3 = 4.0 * D * H * S * (S + 1) / 2
+    maps = {}
+    qb, kb = ops.rope_base(q, inv), ops.rope_base(k, inv)
+    cases = {
+        "jetlong_w0_32768": (ops.PositionMap.jetlong(32768), [qb, ops.rope_regroup(qb, inv, group_size=4)],
+                             [kb, ops.rope_regroup(kb, inv, group_size=4)]),
+        "selfext_g8_w2048": (ops.PositionMap.selfext(2048), [qb, ops.rope_rotate(q, inv, div=8, add=2048 - 2048 // 8)],
+                             [kb, ops.rope_rotate(k, inv, div=8)]),
+    }
+    s_, w_ = 32768, 4096
+    kr = ops.rope_rotate(k, inv, div_mul=0, mod=s_, mod_mul=1)
+    cases["dca_chunk_32768"] = (ops.PositionMap.dca(s_),
+                                [ops.rope_rotate(q, inv, div_mul=0, mod=s_, mod_mul=1),
+                                 ops.rope_rotate(q, inv, div_mul=0, mod=s_, mod_mul=1, add=s_, t_max=s_ + w_),
+                                 ops.rope_rotate(q, inv, div_mul=0, add=s_ + w_)], [kr, kr, kr])
+    o = torch.empty_like(q)
+    for name, (pm, qo, ko) in cases.items():
+        ms = _time_ms(lambda: ops.posmap_prefill(qo, ko, v, pmap=pm, q_pos0=0, out=o, return_lse=False), iters=3, warm=1)
+        maps[name] = dict(ms=round(ms, 2), tflops=round(flops3 / (ms * 1e-3) / 1e12, 1),
+                          frac_of_burst_bf16=round(flops3 / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"], 4))
+    out["config3_attention_131072_32x8_heads"] = dict(maps, note="one attention launch per map, kernel timed alone (burst peak); "
+                                                      "operands from jl_rotate; parity of these maps at this size: tests/test_full_size_gpu.py")
+    del cases, qb, kb, kr
+    # same-shape library anchor: torch SDPA causal attention (flash / cuDNN backend), kv heads expanded to 32
+    try:
+        from torch.nn.attention import SDPBackend, sdpa_kernel
+        qh = q.transpose(1, 2)
+        kh = k.transpose(1, 2).repeat_interleave(H // Hk, dim=1)
+        vh = v.transpose(1, 2).repeat_interleave(H // Hk, dim=1)
+        with sdpa_kernel([SDPBackend.FLASH_ATTENTION, SDPBackend.CUDNN_ATTENTION, SDPBackend.EFFICIENT_ATTENTION]):
+            ms = _time_ms(lambda: torch.nn.functional.scaled_dot_product_attention(qh, kh, vh, is_causal=True), iters=3, warm=1)
+        out["sdpa_causal_anchor_131072_32_heads"] = dict(ms=round(ms, 2), tflops=round(flops3 / (ms * 1e-3) / 1e12, 1),
+                                                         note="torch.nn.functional.scaled_dot_product_attention, plain causal mask "
+                                                              "(no bifocal map): a same-box library anchor, not a component")
+        del qh, kh, vh
+    except Exception as err:      # backend not available for this shape on this build
+        out["sdpa_causal_anchor_131072_32_heads"] = dict(error=str(err)[:200])
+    del q, k, v, o
+    torch.cuda.empty_cache()
+
+    # the reference decode bench's other protocol points (scripts/throughput/bench_cute_decode_sm90_jetlong.py:166-172)
+    pts = {}
+    for ctx in (32769, 65537, 131073):
+        for w0 in (4096, 32768):
+            if ctx - 1 - w0 <= 0:
+                continue
+            r = decode_microbench(peaks, None, iters=10, ctx=ctx, w0=w0, batches=(1,))
+            pts[f"ctx{ctx}_w0_{w0}"] = r["batch1"]
+    out["decode_attn_protocol_points_b1"] = pts
     return out
 
 
@@ -425,6 +648,7 @@ def main():
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--only-decode", action="store_true", help="run just the decode-attention microbench (profiling aid)")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the other BASELINE configurations (N = 1 only)")
     ap.add_argument("--long-generate", type=int, default=0, metavar="TOKENS",
                     help="instead of the default workload: chunked prefill of TOKENS tokens into the preallocated "
                          "(sequence-sharded when N > 1) KV cache, then --decode-steps greedy tokens")
@@ -441,7 +665,8 @@ def main():
         return
 
     from jetlm.kernels import _native
-    _native.lib()                                     # fail loudly right away if the extension is missing
+    counter = LaunchCounter(_native.lib())            # fails loudly right away if the extension is missing
+    _native.lib()._bench_counter = counter
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device; there is no CPU path")
 
@@ -455,7 +680,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         from jetlm.kernels import cute_jetlong_backend as backend
         from jetlm.kernels.sequence_parallel import SequenceShard
-        shard = SequenceShard(rank, world, block=1024)
+        shard = SequenceShard(rank, world, block=SP_BLOCK)
         backend.configure_sequence_sharding(shard)
 
     from jetlm.kernels import jetlong_ops as ops
@@ -524,50 +749,69 @@ def main():
             torch.distributed.all_reduce(ms, op=torch.distributed.ReduceOp.MAX)
         return float(ms)
 
+    parity = sharded_parity(shard) if shard is not None else None
+    if parity is not None and not parity["ok"]:
+        raise RuntimeError(f"sharded attention does not reproduce the unsharded kernel: {parity}")
+
     for _ in range(args.warmup):
         step(ids_dev)
-    sink: list = []
-    launches0 = ops.kernel_launch_count()
+    launches0 = counter.count
     sampler = ClockSampler(local)
     sampler.start()
-    ops.set_event_sink(sink)
+    counter.sink = sink = []
     total_ms = timed(lambda: step(ids_dev), args.steps)
-    ops.set_event_sink(None)
-    launches = ops.kernel_launch_count() - launches0
+    counter.sink = None
+    launches = counter.count - launches0
     e2e_ms = timed(step_e2e, args.steps)
     clocks = sampler.stop()
+    status = ops.kernel_status()                      # the bounded waits of the kernels: a timeout invalidates the numbers
+    if status["prefill_wait_timeouts"] or status["peer_exchange_failed"]:
+        raise RuntimeError(f"a bounded wait inside the kernels gave up during the timed region: {status}")
+    sp_mode = None
+    if shard is not None:
+        from jetlm.kernels import cute_jetlong_backend as backend
+        sp_mode = backend.LAST_TOKEN_SHARDED_MODE
 
     # roofline of the dominant kernel: algorithmic FLOPs of one launch / its mean device time
     torch.cuda.synchronize()
-    pre = [(s.elapsed_time(e), info) for name, s, e, info in sink if name == "jl_prefill"]
+    pre = [s_.elapsed_time(e_) for s_, e_ in sink]
     H, D = cfg.num_attention_heads, 128
-    flops_launch = 4.0 * D * H * args.seq * (args.seq + 1) / 2 / world ** 2      # N launches per layer and rank, one per query stripe
-    mean_ms = statistics.mean(t for t, _ in pre) if pre else float("nan")
+    # per layer and rank: one launch over the rank's query stripe and all keys (K/V gather), or N launches, one per
+    # query stripe against the local key stripe (Q exchange)
+    flops_launch = 4.0 * D * H * args.seq * (args.seq + 1) / 2 / (world if sp_mode == "kv_gather" else world ** 2)
+    mean_ms = statistics.mean(pre) if pre else float("nan")
     achieved = flops_launch / (mean_ms * 1e-3) / 1e12
     roofline = dict(bound="tensor", kernel="jl_prefill (bifocal attention)", achieved=round(achieved, 1),
                     peak=peaks["bf16_tflops_sustained"], unit="TFLOP/s",
                     frac=round(achieved / peaks["bf16_tflops_sustained"], 4), peak_source=peaks["source"] + " (sustained)",
                     frac_of_burst=round(achieved / peaks["bf16_tflops"], 4), frac_of_nominal_2250=round(achieved / 2250.0, 4),
                     launches_timed=len(pre), mean_launch_ms=round(mean_ms, 3),
-                    attention_share_of_step=round(sum(t for t, _ in pre) / total_ms, 4) if pre else None,
+                    attention_share_of_step=round(sum(pre) / total_ms, 4) if pre else None,
                     algorithmic_flops_per_launch=flops_launch,
-                    # dram read+write bytes of one launch: ncu capture at 32768 tokens (0.958 GB, profiles/), scaled by
-                    # tokens — every operand crosses HBM once and K/V re-reads are L2 hits, so traffic grows with S
-                    traffic=round(0.958e9 * args.seq / 32768 / world ** 2), traffic_source="ncu at 32768 tokens, scaled by tokens")
+                    traffic=profiled_traffic_bytes(args.seq) if world == 1 else None,
+                    traffic_source="profiles/prefill_tc_kernel__qwen3-8b_1layer_32k.md (ncu, 32768 tokens), scaled by tokens"
+                    if world == 1 else "not captured for the sharded launches")
 
     line = dict(metric="prefill_tok_per_s", value=round(args.seq * args.steps / (total_ms * 1e-3), 1), unit="tok/s",
                 n_gpus=world, steps=args.steps, warmup=args.warmup, ms_per_step=round(total_ms / args.steps, 2),
                 higher_is_better=True, scaling="strong", vs_baseline=None, dtype="bf16", data="synthetic",
-                config=workload_config(args, cfg, G), clocks=clocks,
+                config=workload_config(args, cfg, G, sp_mode), clocks=clocks,
                 e2e=dict(value=round(args.seq * args.steps / (e2e_ms * 1e-3), 1), unit="tok/s",
                          h2d_bytes_per_step=ids_host.numel() * ids_host.element_size(),
                          d2h_bytes_per_step=result_host.numel() * result_host.element_size()),
-                gpu_launches=launches, roofline=roofline)
+                gpu_launches=launches, roofline=roofline, kernel_status=status)
+    if parity is not None:
+        line["sharded_parity"] = parity
+    if world == 1 and not args.no_extras and args.seq == 131072 and args.model == "qwen3-8b" and not args.layers:
+        line["prefill_length_sweep"] = prefill_length_sweep(model, cfg, (32768, 65536), args.w)
 
     del model
     torch.cuda.empty_cache()
     if not args.no_decode:
         line["decode_attn"] = decode_microbench(peaks, shard)
+        ops.check_status()
+    if world == 1 and not args.no_extras:
+        line["other_configs"] = extra_configs(peaks, args)
     if rank == 0 and world == 1 and not args.no_cpu:
         c = cpu_prefill_sample(args.seq, model_dims(cfg), args.w0, G)
         line["cpu_baseline"] = dict(value=round(c["tok_s"], 3), unit="tok/s", cores=c["cores"], kind="port", sample=c["sample"],

@@ -102,7 +102,9 @@ typedef struct {
   int64_t k_block_stride;
   float softmax_scale;
   jl_posmap map;
-  int32_t impl;             /* 0 = default kernel; 1 = legacy mma.sync kernel kept as GPU cross-check */
+  int32_t impl;             /* 0 = the tcgen05 kernel; 1 = the mma.sync kernel kept as an on-GPU cross-check.  impl 0 refuses
+                               (JL_ERR_UNSUPPORTED, never a silent change of kernel) a k_block that is not a multiple of
+                               128, a q_block that is not a multiple of 256, and more than two distinct key tensors */
   int64_t q_block;          /* <= 0 means contiguous */
   int64_t q_block_stride;
 } jl_prefill_args;
@@ -125,8 +127,12 @@ int jl_prefill_status(void);
  * q[c]: (B, 1, H, D)   seg[s].k / .v: (B, len, Hk, D)   out: (B, 1, H, D)   lse: (B, H) fp32.
  * seg[s].len_dev, if not NULL, is an int32 device array (B,) of per-sequence valid lengths
  * (<= len).  With len_dev and row0_dev a launch whose host arguments never change (a CUDA-graph node)
- * follows a growing cache: see jl_step_advance.  workspace holds the fp32 split partials; size it with
- * jl_decode_workspace_bytes.
+ * follows a growing cache: see jl_step_advance.  workspace holds 16 KB of arrival counters followed by the
+ * fp32 split partials; size it with jl_decode_workspace_bytes.  The splits of a (batch, kv head) are merged
+ * by the last of their CTAs to finish (reference idea: the in-kernel split combine,
+ * cute_decode_sm90.py:1769-1785), which it learns from those counters: the first 16 KB of a workspace must be
+ * ZERO the first time it is used (cudaMemset once after allocating it); every launch leaves them zero, so
+ * the same workspace can serve any later call, of any shape, on the same stream.  batch * kv_heads <= 4096.
  * ------------------------------------------------------------------------------------------- */
 typedef struct {
   const void* k;
@@ -181,15 +187,16 @@ int jl_decode(const jl_decode_args* args, void* cuda_stream);
  *
  * Same arguments and results as jl_decode; args->workspace and args->workspace_bytes are ignored.
  * The library makes no allocation on this path.
- *   - Limit: the partials, batch * heads * splits * (head_dim + 1) * 4 bytes, must fit in
- *     jl_decode_static_scratch_bytes() (4 MiB; batch * heads * splits <= 8128).  Larger requests are
+ *   - Limit: 16 KB of counters plus the partials, batch * heads * splits * (head_dim + 1) * 4 bytes, must fit in
+ *     jl_decode_static_scratch_bytes() (4 MiB; batch * heads * splits <= 8096).  Larger requests are
  *     refused with JL_ERR_WORKSPACE and a message naming both sizes; nothing is launched.
  *   - Cost: every GPU on which the library is loaded carries those 4 MiB until the process exits.
  *   - The first call on each device looks up the array's device address (one cheap runtime query, made
  *     with that device current).  Make that first call during start-up, before any stream capture
  *     begins.
  *   - All calls on a device share the one array, and it keeps whatever the previous call left in it.
- *     Nothing in it has to start at zero: each launch writes every slot it later reads.  Two calls
+ *     The counters at its head start at zero (the array is zero when the library is loaded) and every
+ *     launch puts them back; each launch writes every partial slot it later reads.  Two calls
  *     whose kernels may overlap on the GPU (different streams, no dependency between them) race on
  *     it; order them on one stream or with events, or give the overlapping ones jl_decode with
  *     workspaces of their own. */
@@ -374,8 +381,10 @@ int jl_decode_append(const jl_decode_append_args* args, void* cuda_stream);
  * jl_peer_merge — the exchange step of the KV-sharded decode fused with the N-way merge, over
  * peer-mapped memory instead of a collective library call: every rank pushes its partial (O, LSE) into
  * every rank's exchange buffer with plain peer stores (NVLink), publishes a per-source flag, waits (at
- * most 1 s; then *status = 1 and the result is invalid — the kernel never hangs) for the other ranks'
- * flags and merges the `world` partials that have landed in its own memory.  No reference counterpart
+ * most wait_limit_ms, 1 s by default; then *status = 1 and the result is invalid — the kernel never hangs)
+ * for the other ranks' flags and merges the `world` partials that have landed in its own memory.  A caller
+ * must read *status at its next synchronisation point and discard the step (or redo the exchange with a
+ * collective) when it is set; ranks must not drift apart by more than the limit between calls.  No reference counterpart
  * (the reference is single-GPU; its split-K merge is cute_decode_sm90.py:199-215).
  *
  * part_o (batch, heads, 128) bf16 contiguous, part_lse (batch, heads) fp32: this rank's partial.
@@ -394,7 +403,7 @@ typedef struct {
   size_t buffer_bytes;
   int32_t rank, world;
   int32_t batch, heads, head_dim;
-  int32_t reserved;
+  int32_t wait_limit_ms;           /* longest wait for the other ranks' flags; <= 0: 1000 */
   const int64_t* epoch_base_dev;   /* NULL: base 0 */
   int64_t epoch_stride, epoch_offset;
   void* out;

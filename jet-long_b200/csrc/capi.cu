@@ -20,7 +20,7 @@ int launch_decode_static(const jl_decode_args* a, cudaStream_t stream);
 size_t decode_static_scratch_bytes();
 int launch_prefill_mma(const jl_prefill_args* a, cudaStream_t stream);
 int launch_prefill_tc(const jl_prefill_args* a, cudaStream_t stream);
-bool prefill_tc_supports(const jl_prefill_args* a);
+const char* prefill_tc_unsupported_reason(const jl_prefill_args* a);
 int prefill_tc_status();
 int32_t decode_auto_splits(int32_t batch, int32_t kv_heads, int64_t total_keys);
 size_t decode_workspace_bytes(int32_t batch, int32_t heads, int32_t head_dim, int32_t max_splits);
@@ -74,10 +74,11 @@ static int validate_prefill(const jl_prefill_args* a) {
   if (a->map.n_classes != want) return fail(JL_ERR_BAD_ARG, "jl_prefill: map kind %d needs n_classes == %d", a->map.kind, want);
   if (a->map.kind == JL_MAP_BAND && a->map.near_span < 0) return fail(JL_ERR_BAD_ARG, "jl_prefill: near_span must be >= 0");
   if (a->map.kind == JL_MAP_CHUNK && a->map.chunk < 1) return fail(JL_ERR_BAD_ARG, "jl_prefill: chunk must be >= 1");
-  if (a->v == nullptr || a->out == nullptr) return fail(JL_ERR_BAD_ARG, "jl_prefill: v/out is NULL");
+  const bool keys = a->seqlen_k > 0;          // an empty key range may come with NULL key / value pointers
+  if ((keys && a->v == nullptr) || a->out == nullptr) return fail(JL_ERR_BAD_ARG, "jl_prefill: v/out is NULL");
   uintptr_t bits = reinterpret_cast<uintptr_t>(a->v) | reinterpret_cast<uintptr_t>(a->out);
   for (int c = 0; c < a->map.n_classes; ++c) {
-    if (a->q[c] == nullptr || a->k[c] == nullptr) return fail(JL_ERR_BAD_ARG, "jl_prefill: operand of class %d is NULL", c);
+    if (a->q[c] == nullptr || (keys && a->k[c] == nullptr)) return fail(JL_ERR_BAD_ARG, "jl_prefill: operand of class %d is NULL", c);
     bits |= reinterpret_cast<uintptr_t>(a->q[c]) | reinterpret_cast<uintptr_t>(a->k[c]);
   }
   if (bits & 15) return fail(JL_ERR_BAD_ARG, "jl_prefill: pointers must be 16-byte aligned");
@@ -201,8 +202,10 @@ int jl_prefill(const jl_prefill_args* args, void* cuda_stream) {
   if (rc != JL_OK) return rc;
   if (args->seqlen_q == 0) return JL_OK;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-  if (args->impl == 1) return jl::launch_prefill_mma(args, stream);
-  if (!jl::prefill_tc_supports(args)) return jl::launch_prefill_mma(args, stream);
+  if (args->impl == 1) return jl::launch_prefill_mma(args, stream);      // explicit cross-check kernel only
+  if (args->impl != 0) return jl::fail(JL_ERR_BAD_ARG, "jl_prefill: impl must be 0 or 1, got %d", args->impl);
+  if (const char* why = jl::prefill_tc_unsupported_reason(args))
+    return jl::fail(JL_ERR_UNSUPPORTED, "jl_prefill: %s", why);
   return jl::launch_prefill_tc(args, stream);
 }
 

@@ -8,8 +8,10 @@
 // m16n8k16 tensor-core MMAs (rows past H/Hk are zero), scores go through a base-2 online softmax,
 // and P.V accumulates in registers.  Far-class keys of a base-rotated cache can be regrouped on the
 // fly (rotation by (floor(p/G) - p) * inv_freq in registers) so the cache is read exactly once.
-// Each CTA writes one normalised fp32 partial (O, LSE) per query head; a small second kernel
-// merges the splits.
+// Each CTA writes one normalised fp32 partial (O, LSE) per query head.  The splits of a (batch, kv head)
+// are merged by whichever of its CTAs finishes last: every CTA bumps an arrival counter after its
+// partials are visible, and the one that sees splits - 1 merges (the partials are still in L2) and
+// puts the counter back to zero.  Nothing spins, and there is no second launch.
 #include "jl_common.cuh"
 
 namespace jl {
@@ -19,6 +21,8 @@ constexpr int kDecTile = 64;                 // keys per tile (16 per warp)
 constexpr int kDecStages = 3;
 constexpr int kDecMaxSplits = 296;           // 2 resident CTAs on each of 148 SMs
 constexpr int kStageBytes = kDecTile * 256;  // one K or V tile
+constexpr int kDecMaxCounters = 4096;        // arrival counters at the head of the workspace: batch * kv_heads <= 4096
+constexpr size_t kDecCounterBytes = kDecMaxCounters * sizeof(int);
 
 struct DecSeg {
   const __nv_bfloat16* k;
@@ -39,6 +43,10 @@ struct DecParams {
   const float* inv_freq;
   float* part_o;     // (B, H, splits, 128)
   float* part_lse;   // (B, H, splits)
+  int* arrivals;     // (B, Hk) arrival counters, zero between launches
+  __nv_bfloat16* out;
+  int64_t os_b, os_h;
+  float* lse_out;    // (B, H) or NULL
 };
 
 struct DecSmem {
@@ -57,6 +65,33 @@ __device__ __forceinline__ void sincos_reduced(float theta, float* s, float* c) 
   r = fmaf(k, 1.7484555314695172e-7f, r);
   *s = __sinf(r);
   *c = __cosf(r);
+}
+
+// Merge the split partials of one (batch, head) for output dim d (the 128 threads of a CTA cover the row).
+// The partials were written by other SMs, so they are read through L2 (ld.cg), never from this SM's L1.
+__device__ __forceinline__ void combine_head(const float* part_o, const float* part_lse, int64_t base, int num_splits,
+                                             int d, __nv_bfloat16* out_row, float* lse_out) {
+  float m = -INFINITY;
+  for (int s = 0; s < num_splits; ++s) m = fmaxf(m, __ldcg(part_lse + base + s));
+  const float ms = m == -INFINITY ? 0.f : m;
+  float wsum = 0.f, acc = 0.f;
+  for (int s0 = 0; s0 < num_splits; s0 += 8) {
+    float x[8], l[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {          // 8 independent loads in flight per thread
+      const bool ok = s0 + k < num_splits;
+      x[k] = ok ? __ldcg(part_o + (base + s0 + k) * 128 + d) : 0.f;
+      l[k] = ok ? __ldcg(part_lse + base + s0 + k) : -INFINITY;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float w = exp2f((l[k] - ms) * kLog2e);
+      wsum += w;
+      acc = fmaf(w, x[k], acc);
+    }
+  }
+  out_row[d] = __float2bfloat16(wsum > 0.f ? acc / wsum : 0.f);
+  if (lse_out != nullptr && d == 0) *lse_out = wsum > 0.f ? ms + logf(wsum) : -INFINITY;
 }
 
 __global__ void __launch_bounds__(kDecWarps * 32, 2) decode_kernel(const DecParams p) {
@@ -323,36 +358,26 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) decode_kernel(const DecPara
     p.part_o[pidx * 128 + d] = L > 0.f ? acc / L : 0.f;
     if (d == 0) p.part_lse[pidx] = L > 0.f ? (Ms + log2f(L)) * kLn2 : -INFINITY;
   }
-}
 
-// Merge the split partials of one (batch, head): 128 threads, one per output dim.
-__global__ void __launch_bounds__(128) decode_combine_kernel(const float* __restrict__ part_o,
-                                                             const float* __restrict__ part_lse, int num_splits,
-                                                             int heads, __nv_bfloat16* out, int64_t os_b, int64_t os_h,
-                                                             float* lse_out) {
-  const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
-  const int64_t base = (static_cast<int64_t>(b) * heads + h) * num_splits;
-  float m = -INFINITY;
-  for (int s = 0; s < num_splits; ++s) m = fmaxf(m, part_lse[base + s]);
-  const float ms = m == -INFINITY ? 0.f : m;
-  float wsum = 0.f, acc = 0.f;
-  for (int s0 = 0; s0 < num_splits; s0 += 8) {
-    float x[8], l[8];
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {          // 8 independent loads in flight per thread
-      const bool ok = s0 + k < num_splits;
-      x[k] = ok ? part_o[(base + s0 + k) * 128 + d] : 0.f;
-      l[k] = ok ? part_lse[base + s0 + k] : -INFINITY;
-    }
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const float w = exp2f((l[k] - ms) * kLog2e);
-      wsum += w;
-      acc = fmaf(w, x[k], acc);
-    }
+  // ---- the last CTA of this (batch, kv head) to get here merges the splits ----
+  __shared__ int s_last;
+  __threadfence();                       // this thread's partial writes are visible device-wide ...
+  __syncthreads();                       // ... for every thread of the CTA, before the arrival is counted
+  if (threadIdx.x == 0) {
+    int* counter = p.arrivals + b * p.kv_heads + kvh;
+    const int seen = atomicAdd(counter, 1);
+    s_last = seen == p.num_splits - 1;
+    if (s_last) *counter = 0;            // nobody else touches it until the next launch
   }
-  out[b * os_b + h * os_h + d] = __float2bfloat16(wsum > 0.f ? acc / wsum : 0.f);
-  if (lse_out != nullptr && d == 0) lse_out[static_cast<int64_t>(b) * heads + h] = wsum > 0.f ? ms + logf(wsum) : -INFINITY;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int row = 0; row < rep; ++row) {
+    const int head = kvh * rep + row;
+    const int64_t bh = static_cast<int64_t>(b) * p.heads + head;
+    combine_head(p.part_o, p.part_lse, bh * p.num_splits, p.num_splits, threadIdx.x, p.out + b * p.os_b + head * p.os_h,
+                 p.lse_out != nullptr ? p.lse_out + bh : nullptr);
+  }
 }
 
 int32_t decode_auto_splits(int32_t batch, int32_t kv_heads, int64_t total_keys) {
@@ -367,7 +392,7 @@ int32_t decode_auto_splits(int32_t batch, int32_t kv_heads, int64_t total_keys) 
 size_t decode_workspace_bytes(int32_t batch, int32_t heads, int32_t head_dim, int32_t max_splits) {
   if (batch <= 0 || heads <= 0 || head_dim <= 0) return 0;
   const size_t splits = max_splits > 0 ? static_cast<size_t>(max_splits) : static_cast<size_t>(kDecMaxSplits);
-  return static_cast<size_t>(batch) * heads * splits * (static_cast<size_t>(head_dim) + 1) * sizeof(float);
+  return kDecCounterBytes + static_cast<size_t>(batch) * heads * splits * (static_cast<size_t>(head_dim) + 1) * sizeof(float);
 }
 
 int launch_decode(const jl_decode_args* a, cudaStream_t stream) {
@@ -375,6 +400,8 @@ int launch_decode(const jl_decode_args* a, cudaStream_t stream) {
   if (a->batch <= 0 || a->heads <= 0 || a->kv_heads <= 0) return fail(JL_ERR_BAD_ARG, "jl_decode: batch/heads/kv_heads must be positive");
   if (a->heads % a->kv_heads != 0) return fail(JL_ERR_BAD_ARG, "jl_decode: heads must be divisible by kv_heads");
   if (a->heads / a->kv_heads > 16) return fail(JL_ERR_UNSUPPORTED, "jl_decode: at most 16 query heads per kv head");
+  if (static_cast<int64_t>(a->batch) * a->kv_heads > kDecMaxCounters)
+    return fail(JL_ERR_UNSUPPORTED, "jl_decode: batch * kv_heads must be at most %d", kDecMaxCounters);
   if (a->n_segments < 1 || a->n_segments > JL_MAX_SEGMENTS) return fail(JL_ERR_BAD_ARG, "jl_decode: n_segments must be in [1, %d]", JL_MAX_SEGMENTS);
   if (a->out == nullptr) return fail(JL_ERR_BAD_ARG, "jl_decode: out is NULL");
   if (a->q_stride_b % 8 || a->q_stride_h % 8) return fail(JL_ERR_BAD_ARG, "jl_decode: q strides must be multiples of 8 elements");
@@ -428,25 +455,26 @@ int launch_decode(const jl_decode_args* a, cudaStream_t stream) {
   p.group_size = a->group_size > 0 ? a->group_size : 1;
   p.scale_log2 = a->softmax_scale * kLog2e;
   p.inv_freq = a->inv_freq;
-  p.part_o = static_cast<float*>(a->workspace);
+  p.arrivals = static_cast<int*>(a->workspace);
+  p.part_o = reinterpret_cast<float*>(static_cast<uint8_t*>(a->workspace) + kDecCounterBytes);
   p.part_lse = p.part_o + static_cast<size_t>(a->batch) * a->heads * splits * kHeadDim;
+  p.out = static_cast<__nv_bfloat16*>(a->out);
+  p.os_b = a->o_stride_b; p.os_h = a->o_stride_h;
+  p.lse_out = a->lse;
 
-  static bool attr_set = false;
+  // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute
+  static bool attr_set[64] = {false};
   const int smem = static_cast<int>(sizeof(DecSmem));
-  if (!attr_set) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(JL_ERR_LAUNCH, "jl_decode: no current CUDA device");
+  if (!attr_set[dev]) {
     if (cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
       return check_launch("jl_decode (shared memory opt-in)");
-    attr_set = true;
+    attr_set[dev] = true;
   }
   dim3 grid(splits, a->kv_heads, a->batch);
   decode_kernel<<<grid, kDecWarps * 32, smem, stream>>>(p);
-  int rc = check_launch("jl_decode");
-  if (rc != JL_OK) return rc;
-  dim3 cgrid(a->heads, a->batch);
-  decode_combine_kernel<<<cgrid, 128, 0, stream>>>(p.part_o, p.part_lse, splits, a->heads,
-                                                   static_cast<__nv_bfloat16*>(a->out), a->o_stride_b, a->o_stride_h,
-                                                   a->lse);
-  return check_launch("jl_decode (combine)");
+  return check_launch("jl_decode");
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -457,10 +485,11 @@ int launch_decode(const jl_decode_args* a, cudaStream_t stream) {
 // any later cudaMalloc (an allocation there can fail, fragment the arena's neighbour, or stall every
 // stream of the device while the driver services it), or a plug-in that only receives raw input and
 // output pointers from its host and owns no allocator at all.  For them the scratch is this fixed
-// array inside the library image.  It costs kStaticScratchBytes on every GPU that loads the library,
+// array inside the library image (zero when the image is loaded, which is what the arrival counters at
+// its head need; the kernel puts them back to zero).  It costs kStaticScratchBytes on every GPU that loads the library,
 // for the life of the process, whether or not this entry point is ever used.
 // ---------------------------------------------------------------------------------------------
-constexpr size_t kStaticScratchBytes = size_t(4) << 20;      // 4 MiB: B * H * splits <= 8128 at head_dim 128
+constexpr size_t kStaticScratchBytes = size_t(4) << 20;      // 4 MiB: 16 KB of arrival counters + partials for B * H * splits <= 8096 at head_dim 128
 static __device__ __align__(256) float g_decode_scratch[kStaticScratchBytes / sizeof(float)];
 
 int launch_decode_static(const jl_decode_args* a, cudaStream_t stream) {

@@ -18,7 +18,6 @@ namespace {
 
 constexpr int kPeerRowsPerCta = 32;
 constexpr int kPeerThreads = 128;
-constexpr uint64_t kPeerWaitLimitNs = 1000ull * 1000 * 1000;      // 1 s
 
 __host__ __device__ inline int64_t peer_align(int64_t x) { return (x + 255) / 256 * 256; }
 
@@ -49,6 +48,7 @@ struct PeerParams {
   uint4* out;
   float* lse_out;
   int* status;
+  uint64_t wait_limit_ns;
 };
 
 __device__ __forceinline__ uint64_t peer_timer_ns() {
@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(kPeerThreads) peer_merge_kernel(const PeerPara
     if (*flag < epoch) {
       const uint64_t t0 = peer_timer_ns();
       while (*flag < epoch) {
-        if (peer_timer_ns() - t0 > kPeerWaitLimitNs) { s_failed = 1; break; }
+        if (peer_timer_ns() - t0 > p.wait_limit_ns) { s_failed = 1; break; }
       }
     }
     __threadfence_system();
@@ -178,6 +178,7 @@ int launch_peer_merge(const jl_peer_merge_args* a, cudaStream_t stream) {
   p.out = static_cast<uint4*>(a->out);
   p.lse_out = a->lse_out;
   p.status = a->status;
+  p.wait_limit_ns = static_cast<uint64_t>(a->wait_limit_ms > 0 ? a->wait_limit_ms : 1000) * 1000000ull;
   const int ctas = static_cast<int>((p.rows + kPeerRowsPerCta - 1) / kPeerRowsPerCta);
   if (ctas > 148) return fail(JL_ERR_UNSUPPORTED, "jl_peer_merge: batch * heads must be at most %d", 148 * kPeerRowsPerCta);
   peer_merge_kernel<<<ctas, kPeerThreads, 0, stream>>>(p);

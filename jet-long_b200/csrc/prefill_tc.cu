@@ -617,21 +617,23 @@ static int make_map(CUtensorMap* m, const void* base, int batch, int seq, int he
   return JL_OK;
 }
 
-bool prefill_tc_supports(const jl_prefill_args* a) {
-  if (a->seqlen_k < 1) return false;
-  if (a->k_block > 0 && a->k_block < a->seqlen_k && (a->k_block % tc::kTileN != 0)) return false;
-  if (a->q_block > 0 && a->q_block < a->seqlen_q && (a->q_block % tc::kRowsPerCta != 0)) return false;
+// NULL if the tcgen05 kernel covers the request, else the reason it does not.
+const char* prefill_tc_unsupported_reason(const jl_prefill_args* a) {
+  if (a->k_block > 0 && a->k_block < a->seqlen_k && (a->k_block % tc::kTileN != 0))
+    return "k_block must be a multiple of 128 (the key tile)";
+  if (a->q_block > 0 && a->q_block < a->seqlen_q && (a->q_block % tc::kRowsPerCta != 0))
+    return "q_block must be a multiple of 256 (the query rows of one CTA)";
   int distinct = 0;
   const void* seen[2] = {nullptr, nullptr};
   for (int c = 0; c < a->map.n_classes; ++c) {
     bool found = false;
     for (int i = 0; i < distinct; ++i) found |= seen[i] == a->k[c];
     if (!found) {
-      if (distinct == 2) return false;
+      if (distinct == 2) return "at most two distinct key tensors";
       seen[distinct++] = a->k[c];
     }
   }
-  return true;
+  return nullptr;
 }
 
 // Status word of the bounded waits: a file-scope device variable (no allocation), one per device image.
@@ -664,6 +666,7 @@ int launch_prefill_tc(const jl_prefill_args* a, cudaStream_t stream) {
   tc::Params p{};
   int n_k = 0;
   const void* kptr[2] = {nullptr, nullptr};
+  const bool no_keys = a->seqlen_k == 0;      // nothing is loaded then: the key / value maps only have to be well formed
   for (int c = 0; c < a->map.n_classes; ++c) {
     int rc = make_map(&maps.q[c], a->q[c], a->batch, a->seqlen_q, a->heads, a->q_stride_b, a->q_stride_s, a->q_stride_h);
     if (rc != JL_OK) return rc;
@@ -673,14 +676,16 @@ int launch_prefill_tc(const jl_prefill_args* a, cudaStream_t stream) {
     if (slot < 0) {
       slot = n_k++;
       kptr[slot] = a->k[c];
-      rc = make_map(&maps.k[slot], a->k[c], a->batch, a->seqlen_k, a->kv_heads, a->k_stride_b, a->k_stride_s, a->k_stride_h);
+      rc = no_keys ? make_map(&maps.k[slot], a->q[0], 1, 1, 1, 0, 0, 0)
+                   : make_map(&maps.k[slot], a->k[c], a->batch, a->seqlen_k, a->kv_heads, a->k_stride_b, a->k_stride_s, a->k_stride_h);
       if (rc != JL_OK) return rc;
     }
     p.k_map[c] = slot;
   }
   for (int c = a->map.n_classes; c < JL_MAX_CLASSES; ++c) maps.q[c] = maps.q[0];
   if (n_k == 1) maps.k[1] = maps.k[0];
-  int rc = make_map(&maps.v, a->v, a->batch, a->seqlen_k, a->kv_heads, a->v_stride_b, a->v_stride_s, a->v_stride_h);
+  int rc = no_keys ? make_map(&maps.v, a->q[0], 1, 1, 1, 0, 0, 0)
+                   : make_map(&maps.v, a->v, a->batch, a->seqlen_k, a->kv_heads, a->v_stride_b, a->v_stride_s, a->v_stride_h);
   if (rc != JL_OK) return rc;
   p.sq = a->seqlen_q; p.sk = a->seqlen_k; p.heads = a->heads; p.kv_heads = a->kv_heads; p.batch = a->batch;
   p.q_pos0 = a->q_pos0; p.k_pos0 = a->k_pos0;
@@ -696,11 +701,14 @@ int launch_prefill_tc(const jl_prefill_args* a, cudaStream_t stream) {
   p.os_b = a->o_stride_b; p.os_s = a->o_stride_s; p.os_h = a->o_stride_h;
   p.status = status_word();
   const int smem = static_cast<int>(sizeof(tc::Smem)) + 1024;
-  static bool attr_done = false;
-  if (!attr_done) {
+  // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute
+  static bool attr_done[64] = {false};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(JL_ERR_LAUNCH, "jl_prefill: no current CUDA device");
+  if (!attr_done[dev]) {
     if (cudaFuncSetAttribute(tc::prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
       return check_launch("jl_prefill (shared memory opt-in)");
-    attr_done = true;
+    attr_done[dev] = true;
   }
   dim3 grid((a->seqlen_q + tc::kRowsPerCta - 1) / tc::kRowsPerCta, a->heads, a->batch);
   tc::prefill_tc_kernel<<<grid, tc::kThreads, smem, stream>>>(maps, p);

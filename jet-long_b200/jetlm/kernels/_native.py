@@ -130,7 +130,7 @@ class DecodeAppendArgs(C.Structure):
 class PeerMergeArgs(C.Structure):
     _fields_ = [("part_o", C.c_void_p), ("part_lse", C.c_void_p), ("peer_buf", C.c_void_p * JL_MAX_PARTS),
                 ("buffer_bytes", C.c_size_t), ("rank", C.c_int32), ("world", C.c_int32),
-                ("batch", C.c_int32), ("heads", C.c_int32), ("head_dim", C.c_int32), ("reserved", C.c_int32),
+                ("batch", C.c_int32), ("heads", C.c_int32), ("head_dim", C.c_int32), ("wait_limit_ms", C.c_int32),
                 ("epoch_base_dev", C.c_void_p), ("epoch_stride", C.c_int64), ("epoch_offset", C.c_int64),
                 ("out", C.c_void_p), ("lse_out", C.c_void_p), ("status", C.c_void_p)]
 

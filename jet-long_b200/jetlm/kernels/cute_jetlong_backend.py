@@ -11,7 +11,8 @@ from __future__ import annotations
 import torch
 
 from . import jetlong_ops as ops
-from .sequence_parallel import PartialBuffer, SequenceShard, make_peer_exchange, sharded_attention
+from .sequence_parallel import (PartialBuffer, SequenceShard, interleave_stripes, make_peer_exchange,
+                                sharded_attention)
 
 _SHARD: SequenceShard | None = None
 _BUFFERS: dict[tuple, PartialBuffer] = {}
@@ -64,18 +65,95 @@ def sequence_shard() -> SequenceShard | None:
     return _SHARD
 
 
+def token_sharded_prefill_mode(world: int, n_keys_total: int, n_queries_total: int, heads: int, kv_heads: int) -> str:
+    """Which exchange the token-sharded prefill uses.  "kv_gather": all-gather K_base and V, every rank attends
+    its own query stripe to ALL keys in one launch (no return trip, no merge); per rank it receives
+    (N-1)/N * n_keys_total * kv_heads * D * 2 * 2 bytes.  "q_exchange": all-gather Q, every rank attends all
+    query stripes to its OWN key stripe, partial (O, LSE) go back by all-to-all and are merged; it receives
+    about (N-1)/N * n_queries_total * heads * D * 2 * 2 bytes, however long the cache already is.  The smaller
+    volume wins: a fresh prompt under grouped-query attention gathers K / V (4x fewer bytes at 32 / 8 heads),
+    a late chunk of a long chunked prefill keeps its keys at home.  JETLONG_SP_PREFILL=kv|q overrides."""
+    import os
+    forced = os.environ.get("JETLONG_SP_PREFILL", "")
+    if forced in ("kv", "q"):
+        return "kv_gather" if forced == "kv" else "q_exchange"
+    return "kv_gather" if n_keys_total * kv_heads <= n_queries_total * heads else "q_exchange"
+
+
+def _prefill_kv_gather(query_base, key_base, value, *, q_start, inv_freq, group_size, window_size_left, softmax_scale):
+    """Token-sharded prefill by gathering the keys: see token_sharded_prefill_mode.  The ranks' stripes arrive
+    rank-major; one strided copy puts them into position order, the far-class keys are regrouped locally from the
+    gathered base keys (one jl_rotate pass), and ONE jl_prefill launch attends this rank's block-cyclic query
+    stripe to the whole key range."""
+    import torch.distributed as dist
+    sh = _SHARD
+    N, blk, me = sh.world, sh.block, sh.rank
+    B, S_loc, H, D = query_base.shape
+    R, Hk = key_base.shape[1], key_base.shape[2]
+    if R % blk != 0:
+        raise ValueError(f"token-sharded prefill needs whole blocks per rank: {R} cache rows, block {blk}")
+    dev, dt = query_base.device, query_base.dtype
+    key = ("kvg", me, N, B, S_loc, R, H, Hk, D, dt, dev)
+    bufs = _BUFFERS.get(key)
+    if bufs is None:
+        for old in [k for k in _BUFFERS if k[0] == "kvg"]:      # a chunked prefill changes R every call: keep one set
+            del _BUFFERS[old]
+        bufs = _BUFFERS[key] = dict(
+            stage=torch.empty(N, 2, B, R, Hk, D, dtype=dt, device=dev),        # [rank][K / V] stripes as they arrive
+            full=torch.empty(2, B, R * N, Hk, D, dtype=dt, device=dev),        # K_base / V in position order
+            k_grp=torch.empty(B, R * N, Hk, D, dtype=dt, device=dev),
+            q_grp=torch.empty(B, S_loc, H, D, dtype=dt, device=dev))
+    stage, full, k_grp, q_grp = bufs["stage"], bufs["full"], bufs["k_grp"], bufs["q_grp"]
+    stage[me, 0].copy_(key_base)
+    stage[me, 1].copy_(value)
+    gather = dist.all_gather_into_tensor(stage.view(-1), stage[me].view(-1), group=sh.group, async_op=True)
+    stride = N * blk
+    regroup = int(group_size) > 1
+    if regroup:     # the regrouped queries need no remote data: formed while the gather is in flight
+        ops.rope_regroup(query_base, inv_freq, group_size=int(group_size), pos0=int(q_start) + me * blk, pos_block=blk,
+                         pos_block_stride=stride, out=q_grp)
+    gather.wait()
+    interleave_stripes(stage, blk, full)
+    if regroup:
+        ops.rope_regroup(full[0], inv_freq, group_size=int(group_size), pos0=0, out=k_grp)
+    return ops.posmap_prefill([query_base, q_grp if regroup else query_base], [full[0], k_grp if regroup else full[0]], full[1],
+                              pmap=ops.PositionMap.jetlong(int(window_size_left)), q_pos0=int(q_start) + me * blk,
+                              q_block=blk, q_block_stride=stride, k_pos0=0, softmax_scale=softmax_scale, return_lse=False)
+
+
+LAST_TOKEN_SHARDED_MODE = None      # "kv_gather" / "q_exchange": what the most recent token-sharded prefill call used
+
+
 def fused_jetlong_prefill_token_sharded(query_base, key_base, key_group, value, *, q_start: int, inv_freq,
-                                        group_size: int, window_size_left: int, softmax_scale: float):
+                                        group_size: int, window_size_left: int, softmax_scale: float, mode=None):
     """Bifocal prefill when the TOKENS are sharded block-cyclically over the ranks (every rank ran the
     projections only for its own stripe of the prompt and keeps only its stripe of the KV cache).
 
     query_base (B, S_loc, H, D): this rank's base-rotated queries, row i at position
     q_start + rank*blk + (i // blk) * world*blk + i % blk.  key_base / key_group / value
-    (B, Skv_loc, Hk, D) views: this rank's cache stripe (same geometry from position 0).
-    Steps: all-gather the base-rotated queries (the regrouped ones are re-derived locally), attend
+    (B, Skv_loc, Hk, D) views: this rank's cache stripe (same geometry from position 0); key_group may be
+    None (it is only read by the "q_exchange" form, which regroups on demand).
+    mode None picks the cheaper exchange (token_sharded_prefill_mode).  The "q_exchange" form:
+    all-gather the base-rotated queries (the regrouped ones are re-derived locally), attend
     every rank's query stripe to the local key stripe, send each partial (O, LSE) to the rank that
     owns those query rows (all-to-all), merge the N partials of the local rows.  Returns (B, S_loc, H, D).
-    K and V never cross NVLink; per layer a rank receives one copy of Q and one copy of O."""
+    There K and V never cross NVLink; per layer a rank receives one copy of Q and one copy of O."""
+    global LAST_TOKEN_SHARDED_MODE
+    if _SHARD is None:
+        raise RuntimeError("token-sharded prefill needs configure_sequence_sharding(...) first")
+    if mode is None:
+        mode = token_sharded_prefill_mode(_SHARD.world, key_base.shape[1] * _SHARD.world, query_base.shape[1] * _SHARD.world,
+                                          query_base.shape[2], key_base.shape[2])
+    LAST_TOKEN_SHARDED_MODE = mode
+    if mode == "kv_gather":
+        return _prefill_kv_gather(query_base, key_base, value, q_start=q_start, inv_freq=inv_freq, group_size=group_size,
+                                  window_size_left=window_size_left, softmax_scale=softmax_scale)
+    if key_group is None:
+        key_group = key_base
+        if int(group_size) > 1:
+            key_group = torch.empty_strided(key_base.shape, key_base.stride(), dtype=key_base.dtype, device=key_base.device)
+            ops.rope_regroup(key_base, inv_freq, group_size=int(group_size), pos0=_SHARD.rank * _SHARD.block,
+                             pos_block=_SHARD.block, pos_block_stride=_SHARD.world * _SHARD.block, out=key_group)
     import torch.distributed as dist
     sh = _SHARD
     if sh is None:
@@ -207,7 +285,7 @@ def fused_jetlong_decode_cache(query_base, query_group, key_cache, value_cache, 
         B, _, H, D = query_base.shape
         part = lambda out, lse: _decode_range(query_base, query_group, kc[:, lo:hi], vc[:, lo:hi], int(boundary) - lo, lo,
                                               inv_freq, group_size, softmax_scale, True, out=out, lse=lse,
-                                              kg=kg[:, lo:hi] if kg is not None else None)
+                                              kg=kg[:, lo:hi] if kg is not None else None, allow_empty=True)
         return _sharded_decode(part, sh, query_base, return_lse, exchange)
     return _decode_range(query_base, query_group, kc, vc, int(boundary) - int(cache_pos0), int(cache_pos0),
                          inv_freq, group_size, softmax_scale, return_lse, kg=kg)
@@ -318,7 +396,7 @@ def fused_jetlong_freq_decode(query_base, key_cache, value_cache, *, delta_inv_f
 
 
 def _decode_range(query_base, query_group, kc, vc, b, pos0, inv_freq, group_size, softmax_scale, return_lse,
-                  out=None, lse=None, kg=None):
+                  out=None, lse=None, kg=None, allow_empty=False):
     """Decode over rows of a (B,S,Hk,D) cache view whose row 0 has absolute position pos0; rows < b are far."""
     b = max(0, min(b, kc.shape[1]))
     segs = []
@@ -329,6 +407,12 @@ def _decode_range(query_base, query_group, kc, vc, b, pos0, inv_freq, group_size
     if b < kc.shape[1]:
         segs.append(ops.KvSegment(kc[:, b:], vc[:, b:], q_class=0))
     if not segs:
-        raise RuntimeError("JetLong backend 'fused' got an empty key range")
+        if not allow_empty:
+            raise RuntimeError("JetLong backend 'fused' got an empty key range")
+        # a rank of a sharded call that owns no key still has to reach the exchange: an empty partial (0, -inf)
+        B, _, H, _ = query_base.shape
+        out = torch.zeros_like(query_base) if out is None else out.zero_()
+        lse = (torch.full((B, H, 1), float("-inf"), device=query_base.device) if lse is None else lse.fill_(float("-inf")))
+        return (out, lse) if return_lse else out
     return ops.decode_segments([query_base, query_group], segs, inv_freq=inv_freq, group_size=int(group_size),
                                softmax_scale=softmax_scale, return_lse=return_lse, out=out, lse=lse)

@@ -34,6 +34,9 @@ class GraphedDecodeStep:
         self.token = torch.zeros(self.batch, 1, dtype=torch.long, device=self.device)
         self._graph, self._graph_group = None, None
         self._device_pos = None            # position the device-side state will describe after its next advance
+        # the peer exchange's status word is mirrored into pinned host memory by the graph's last node, so a
+        # wait that gave up is noticed at the next call without a synchronisation
+        self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
 
     def _body(self, group: int) -> None:
         self.step.advance()
@@ -44,6 +47,16 @@ class GraphedDecodeStep:
             src = dist.get_global_rank(self.shard.group, 0) if self.shard.group is not None else 0
             dist.broadcast(nxt, src=src, group=self.shard.group)
         self.token.copy_(nxt)
+        peer = getattr(self.step, "_peer", None)
+        if peer:
+            self._status_host.copy_(peer.status, non_blocking=True)
+
+    def check(self) -> None:
+        """Raise if a bounded wait of the peer exchange gave up in a replay that has completed (no synchronisation:
+        reads the pinned mirror; `ops.check_status()` is the synchronising form)."""
+        if int(self._status_host[0]) != 0:
+            raise RuntimeError("jl_peer_merge gave up waiting for another rank during a decode step; the tokens "
+                               "produced since are invalid")
 
     def _refresh_group_keys(self, group: int, pos: int) -> None:
         """With a regrouped far-key cache: regroup every row that is far for the token at `pos` with this G
@@ -78,11 +91,18 @@ class GraphedDecodeStep:
         with torch.cuda.graph(graph):
             self._body(group)
         self._graph, self._graph_group, self._device_pos = graph, group, pos
+        if self.shard is not None:
+            # capture takes a different time on every rank; line the ranks up again so that the first replay's
+            # bounded waits only have to cover kernel-time skew
+            import torch.distributed as dist
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.shard.group)
 
     @torch.no_grad()
     def __call__(self, token=None) -> torch.Tensor:
         """Feed `token` (B,1) — by default the token this object produced last — and return the next greedy
         token.  The result is the object's static buffer: clone it to keep it past the next call."""
+        self.check()
         pos = self.cache.get_seq_length()
         group = max(1, math.ceil((pos + 1) / self.w))
         if token is not None:

@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import weakref
 from dataclasses import dataclass
 from typing import Optional, Sequence
 
@@ -60,46 +61,65 @@ def _st(t: torch.Tensor, i: int) -> int:
     return t.stride(i) if t.shape[i] > 1 else 0
 
 
-# Instrumentation used by the benchmark: kernel launches issued through this module, and (when a list
-# is installed with set_event_sink) a CUDA event pair around every attention kernel launch.
-KERNELS_PER_CALL = {"jl_prefill": 1, "jl_decode": 2, "jl_merge": 1, "jl_rotate": 1, "jl_norm_rope": 1, "jl_rmsnorm": 1,
-                    "jl_step_advance": 1, "jl_decode_append": 1, "jl_silu_mul": 1, "jl_peer_merge": 1}
-LAUNCHES = {name: 0 for name in KERNELS_PER_CALL}
-_EVENT_SINK: Optional[list] = None
-
-
-def set_event_sink(sink: Optional[list]) -> None:
-    """sink receives (name, start_event, end_event, info) per prefill/decode launch; None disables."""
-    global _EVENT_SINK
-    _EVENT_SINK = sink
-
-
-def kernel_launch_count() -> int:
-    return sum(LAUNCHES[k] * KERNELS_PER_CALL[k] for k in LAUNCHES)
-
-
-def _timed_call(name: str, fn, info=None) -> None:
-    LAUNCHES[name] += 1
-    if _EVENT_SINK is None or name not in ("jl_prefill", "jl_decode"):
-        N.check(name, fn())
-        return
-    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s.record()
+def _call(name: str, fn) -> None:
+    """Run one C-ABI call and raise on a non-zero status."""
     N.check(name, fn())
-    e.record()
-    _EVENT_SINK.append((name, s, e, info))
+
+
+# ----------------------------------------------------------------------------------------------
+# status words of the bounded waits
+# ----------------------------------------------------------------------------------------------
+
+_PEER_EXCHANGES: "weakref.WeakSet" = weakref.WeakSet()      # every live sequence_parallel.PeerExchange
+
+
+def register_peer_exchange(exchange) -> None:
+    _PEER_EXCHANGES.add(exchange)
+
+
+def kernel_status() -> dict:
+    """What the kernels' bounded waits reported since the last call (synchronises the current device; reading a
+    raised prefill status clears it): {"prefill_wait_timeouts": 0 / 1, "peer_exchange_failed": bool}."""
+    failed = any(bool(ex.status.item()) for ex in list(_PEER_EXCHANGES))
+    return dict(prefill_wait_timeouts=int(N.lib().jl_prefill_status()), peer_exchange_failed=failed)
+
+
+def check_status() -> None:
+    """Raise if a bounded wait inside jl_prefill or jl_peer_merge gave up: the results produced since the
+    last check are then invalid.  Call at a point that synchronises anyway (end of a step, before logits leave)."""
+    st = kernel_status()
+    if st["prefill_wait_timeouts"] or st["peer_exchange_failed"]:
+        raise RuntimeError(f"a bounded wait inside the attention kernels gave up ({st}); results since the last "
+                           f"check are invalid")
 
 
 _WORKSPACES: dict[tuple, torch.Tensor] = {}
+_SPARE_WORKSPACES: dict[int, list] = {}
 
 
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    """Split-KV scratch, cached per (device, stream) so concurrent streams never share it."""
+    """Split-KV scratch, cached per (device, stream) so concurrent streams never share it.  Zeroed once:
+    the arrival counters at its head must start at zero, and every launch leaves them zero.
+
+    A CUDA-graph capture runs on a stream of its own and so asks for a workspace of its own; zeroing one there
+    would put a memset node into the graph.  Every eager call therefore leaves one zeroed spare per device
+    behind, and a capturing call takes it."""
     key = (device.index, _stream())
     ws = _WORKSPACES.get(key)
+    capturing = torch.cuda.is_current_stream_capturing()
     if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        spares = _SPARE_WORKSPACES.setdefault(device.index, [])
+        fit = next((t for t in spares if t.numel() >= nbytes), None) if capturing else None
+        if fit is not None:
+            spares.remove(fit)
+            ws = fit
+        else:
+            ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _WORKSPACES[key] = ws
+    if not capturing:
+        spares = _SPARE_WORKSPACES.setdefault(device.index, [])
+        if not any(t.numel() >= nbytes for t in spares):
+            spares[:] = [torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)]
     return ws
 
 
@@ -159,7 +179,7 @@ def rope_rotate(x: torch.Tensor, inv_freq: torch.Tensor, *, pos0: int = 0, div: 
                      B, S, H, D, int(pos0), int(div), int(div_mul), int(mod), int(mod_mul), int(add), int(t_max),
                      inv_freq.data_ptr(), int(pos_block), int(pos_block_stride))
     with torch.cuda.device(x.device):
-        _timed_call("jl_rotate", lambda: N.lib().jl_rotate(C.byref(a), _stream()))
+        _call("jl_rotate", lambda: N.lib().jl_rotate(C.byref(a), _stream()))
     return out
 
 
@@ -193,7 +213,7 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, *, eps: float, residual: Opti
         summed = torch.empty_like(x)
         a.residual, a.sum_out = residual.data_ptr(), summed.data_ptr()
     with torch.cuda.device(x.device):
-        _timed_call("jl_rmsnorm", lambda: N.lib().jl_rmsnorm(C.byref(a), _stream()))
+        _call("jl_rmsnorm", lambda: N.lib().jl_rmsnorm(C.byref(a), _stream()))
     return (summed, out) if residual is not None else out
 
 
@@ -208,7 +228,7 @@ def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     out = torch.empty_like(gate)
     a = N.SiluMulArgs(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel())
     with torch.cuda.device(gate.device):
-        _timed_call("jl_silu_mul", lambda: N.lib().jl_silu_mul(C.byref(a), _stream()))
+        _call("jl_silu_mul", lambda: N.lib().jl_silu_mul(C.byref(a), _stream()))
     return out
 
 
@@ -241,7 +261,7 @@ def norm_rope(x: torch.Tensor, weight: torch.Tensor, inv_freq: torch.Tensor, *, 
                        B, S, H, D, float(eps), int(group_size) if want_group else 1,
                        int(pos0), int(pos_block), int(pos_block_stride), inv_freq.data_ptr())
     with torch.cuda.device(x.device):
-        _timed_call("jl_norm_rope", lambda: N.lib().jl_norm_rope(C.byref(a), _stream()))
+        _call("jl_norm_rope", lambda: N.lib().jl_norm_rope(C.byref(a), _stream()))
     return (out_base, out_group) if want_group else out_base
 
 
@@ -299,7 +319,7 @@ def merge_partials(o_parts: Sequence[torch.Tensor], lse_parts: Sequence[torch.Te
     a.out = out.data_ptr()
     a.lse_out = lse_out.data_ptr() if lse_out is not None else None
     with torch.cuda.device(o0.device):
-        _timed_call("jl_merge", lambda: N.lib().jl_merge(C.byref(a), _stream()))
+        _call("jl_merge", lambda: N.lib().jl_merge(C.byref(a), _stream()))
     return (out, lse_out) if return_lse else out
 
 
@@ -373,8 +393,7 @@ def posmap_prefill(q_ops: Sequence[torch.Tensor], k_ops: Sequence[torch.Tensor],
     a.impl = int(impl)
     a.q_block, a.q_block_stride = int(q_block), int(q_block_stride)
     with torch.cuda.device(q0.device):
-        _timed_call("jl_prefill", lambda: N.lib().jl_prefill(C.byref(a), _stream()),
-                    dict(B=B, Sq=Sq, Skv=Skv, H=H, q_pos0=int(q_pos0)))
+        _call("jl_prefill", lambda: N.lib().jl_prefill(C.byref(a), _stream()))
     return (out, lse) if return_lse else out
 
 
@@ -436,7 +455,8 @@ def decode_segments(q_ops: Sequence[Optional[torch.Tensor]], segments: Sequence[
                     lse: Optional[torch.Tensor] = None, return_lse: bool = True,
                     workspace: Optional[torch.Tensor] = None):
     """Split-KV decode of one query token per sequence over in-place key segments (see jl_decode).
-    q_ops[c]: (B,1,H,D) views sharing strides (None for unused classes).  Returns (out (B,1,H,D), lse (B,H,1))."""
+    q_ops[c]: (B,1,H,D) views sharing strides (None for unused classes).  Returns (out (B,1,H,D), lse (B,H,1)).
+    A caller-provided `workspace` must have had its first 16 KB zeroed once (torch.zeros) before its first use."""
     op = "decode_segments"
     q0 = next(t for t in q_ops if t is not None)
     if q0.dim() != 4:
@@ -521,7 +541,7 @@ def decode_segments(q_ops: Sequence[Optional[torch.Tensor]], segments: Sequence[
     ws = workspace if workspace is not None else _workspace(q0.device, need)
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel() * ws.element_size()
     with torch.cuda.device(q0.device):
-        _timed_call("jl_decode", lambda: lib.jl_decode(C.byref(a), _stream()), dict(B=B, keys=total, Hk=Hk))
+        _call("jl_decode", lambda: lib.jl_decode(C.byref(a), _stream()))
     return (out, lse) if return_lse else out
 
 
@@ -558,7 +578,7 @@ class StepState:
                               sh.rank if sh is not None else 0, sh.world if sh is not None else 1, 0,
                               sh.block if sh is not None else 1, self.w_0)
         with torch.cuda.device(self.state.device):
-            _timed_call("jl_step_advance", lambda: N.lib().jl_step_advance(C.byref(a), _stream()))
+            _call("jl_step_advance", lambda: N.lib().jl_step_advance(C.byref(a), _stream()))
 
     # views the kernels take
     @property
@@ -620,14 +640,15 @@ def decode_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_weight: t
                            sh.rank * sh.block if sh is not None else 0, sh.block if sh is not None else 0,
                            sh.world * sh.block if sh is not None else 0)
     with torch.cuda.device(q.device):
-        _timed_call("jl_decode_append", lambda: N.lib().jl_decode_append(C.byref(a), _stream()))
+        _call("jl_decode_append", lambda: N.lib().jl_decode_append(C.byref(a), _stream()))
     return q_base, (q_group if q_group is not None else q_base)
 
 
 def peer_merge(part_o: torch.Tensor, part_lse: torch.Tensor, exchange, *, epoch_base: Optional[torch.Tensor],
-               epoch_stride: int, epoch_offset: int, return_lse: bool = False):
+               epoch_stride: int, epoch_offset: int, return_lse: bool = False, wait_limit_ms: int = 0):
     """Push this rank's decode partial (part_o (B,1,H,D) bf16, part_lse (B,H,1) fp32, both contiguous) to all
-    ranks of `exchange` (sequence_parallel.PeerExchange) through peer-mapped memory, wait for theirs and merge
+    ranks of `exchange` (sequence_parallel.PeerExchange) through peer-mapped memory, wait for theirs (at most
+    wait_limit_ms, default 1 s; then exchange.status is raised and the result is invalid: check_status()) and merge
     (see jl_peer_merge).  The epoch (*epoch_base) * epoch_stride + epoch_offset must be >= 1, equal on all ranks
     and grow by exactly 1 from one call on this exchange to the next.  Returns out (B,1,H,D) or (out, lse)."""
     op = "peer_merge"
@@ -657,8 +678,9 @@ def peer_merge(part_o: torch.Tensor, part_lse: torch.Tensor, exchange, *, epoch_
     a.out = out.data_ptr()
     a.lse_out = lse.data_ptr() if lse is not None else None
     a.status = exchange.status.data_ptr()
+    a.wait_limit_ms = int(wait_limit_ms)
     with torch.cuda.device(part_o.device):
-        _timed_call("jl_peer_merge", lambda: N.lib().jl_peer_merge(C.byref(a), _stream()))
+        _call("jl_peer_merge", lambda: N.lib().jl_peer_merge(C.byref(a), _stream()))
     return (out, lse) if return_lse else out
 
 

@@ -115,6 +115,8 @@ class PeerExchange:
         if len(self.ptrs) != shard.world or self.ptrs[shard.rank] != self.buf.data_ptr():
             raise RuntimeError("symmetric memory rendezvous returned an unexpected mapping")
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        from . import jetlong_ops
+        jetlong_ops.register_peer_exchange(self)       # so that jetlong_ops.check_status() sees this status word
         self.epoch = torch.zeros(1, dtype=torch.int64, device=device)     # for callers without an epoch source of their own
         torch.cuda.synchronize(device)
         dist.barrier(group=group)             # every rank's zeroes are in place before anyone pushes
@@ -143,6 +145,22 @@ def make_peer_exchange(shard: SequenceShard, batch: int, heads: int, head_dim: i
     agree = torch.tensor([ok], dtype=torch.int32, device=device)
     dist.all_reduce(agree, op=dist.ReduceOp.MIN, group=shard.group)
     return ex if int(agree) == 1 else None
+
+
+def interleave_stripes(stage: torch.Tensor, block: int, out: torch.Tensor) -> torch.Tensor:
+    """Block-cyclic stripes, rank-major as an all-gather delivers them, into position order.
+    stage (N, C, B, R, ...): rank r's R rows are positions r*block + (i // block) * N*block + i % block;
+    out (C, B, R * N, ...): row p is position p.  One strided copy."""
+    N, C, B, R = stage.shape[:4]
+    tail = tuple(stage.shape[4:])
+    if R % block != 0:
+        raise ValueError(f"stripes must hold whole blocks: {R} rows, block {block}")
+    nb = R // block
+    if tuple(out.shape) != (C, B, R * N) + tail:
+        raise ValueError(f"out must have shape {(C, B, R * N) + tail}, got {tuple(out.shape)}")
+    src = stage.view(N, C, B, nb, block, *tail).permute(1, 2, 3, 0, 4, *range(5, 5 + len(tail)))
+    out.view(C, B, nb, N, block, *tail).copy_(src)
+    return out
 
 
 def gather_partials(out: torch.Tensor, lse: torch.Tensor, shard: SequenceShard):

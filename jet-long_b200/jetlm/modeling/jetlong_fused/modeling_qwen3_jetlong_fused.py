@@ -366,15 +366,18 @@ class Qwen3JetLongFusedAttention(nn.Module):
             k_all, v_all = k_all.transpose(1, 2), v_all.transpose(1, 2)
         else:
             k_all, v_all = k_new, v
-        if group > 1:
-            k_group = (past_key_values.group_scratch(k_all.shape[1]) if slot is not None
-                       else torch.empty(bsz, Hk, k_all.shape[1], D, dtype=k_all.dtype, device=k_all.device).transpose(1, 2))
-            ops.rope_regroup(k_all, inv_freq, group_size=group, pos0=sh.rank * sh.block, out=k_group, **geo)
-        else:
-            k_group = k_all
+        mode = backend.token_sharded_prefill_mode(sh.world, k_all.shape[1] * sh.world, seq * sh.world, self.num_heads, Hk)
+        k_group = None                   # the K/V-gather form regroups the gathered keys itself
+        if mode == "q_exchange":
+            if group > 1:
+                k_group = (past_key_values.group_scratch(k_all.shape[1]) if slot is not None
+                           else torch.empty(bsz, Hk, k_all.shape[1], D, dtype=k_all.dtype, device=k_all.device).transpose(1, 2))
+                ops.rope_regroup(k_all, inv_freq, group_size=group, pos0=sh.rank * sh.block, out=k_group, **geo)
+            else:
+                k_group = k_all
         attn = backend.fused_jetlong_prefill_token_sharded(
             q_base, k_all, k_group, v_all, q_start=plan.q_pos0,
-            inv_freq=inv_freq, group_size=group, window_size_left=self.jetlong_w_0, softmax_scale=self.scaling)
+            inv_freq=inv_freq, group_size=group, window_size_left=self.jetlong_w_0, softmax_scale=self.scaling, mode=mode)
         return self.o_proj(attn.reshape(bsz, seq, -1)), None
 
 
@@ -468,9 +471,18 @@ class Qwen3JetLongFusedModel(Qwen3PreTrainedModel):
                            position_embeddings=position_embeddings, position_ids=position_ids,
                            past_key_values=past_key_values, use_cache=use_cache, **kwargs)
         hidden = self.norm(hidden)
+        self._check_kernel_status(extended)
         return BaseModelOutputWithPast(last_hidden_state=hidden,
                                        past_key_values=past_key_values if use_cache else None)
 
+    def _check_kernel_status(self, extended: bool) -> None:
+        """With `model.check_kernel_status = True` (or JETLONG_CHECK_STATUS=1) every extended forward ends by
+        reading the status words of the kernels' bounded waits and raises if one gave up.  Off by default: the
+        read synchronises the device."""
+        import os
+        if extended and (getattr(self, "check_kernel_status", False) or os.environ.get("JETLONG_CHECK_STATUS") == "1"):
+            from jetlm.kernels import jetlong_ops as ops
+            ops.check_status()
 
     def decode_step(self, token, cache, step, group: int):
         """One-token forward with no host-side dependence on the position: `step` (ops.StepState) was advanced
@@ -519,6 +531,7 @@ class Qwen3JetLongFusedModel(Qwen3PreTrainedModel):
             hidden = layer(hidden, attention_mask=None, position_embeddings=position_embeddings,
                            position_ids=position_ids, past_key_values=past_key_values, use_cache=use_cache, **kwargs)
         hidden = self.norm(hidden)
+        self._check_kernel_status(True)
         return BaseModelOutputWithPast(last_hidden_state=hidden, past_key_values=past_key_values if use_cache else None)
 
 

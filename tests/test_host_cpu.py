@@ -32,20 +32,32 @@ def test_library_exports_every_declared_symbol():
 
 
 def test_struct_layout_matches_header(tmp_path):
+    """sizeof of every argument structure of the header == its ctypes mirror (a stub that is one field short
+    makes the library read past the caller's struct)."""
     n = _native()
+    pairs = [("jl_posmap", n.PosMap), ("jl_prefill_args", n.PrefillArgs), ("jl_kv_segment", n.KvSegment),
+             ("jl_decode_args", n.DecodeArgs), ("jl_merge_args", n.MergeArgs), ("jl_rotate_args", n.RotateArgs),
+             ("jl_norm_rope_args", n.NormRopeArgs), ("jl_rmsnorm_args", n.RmsNormArgs), ("jl_silu_mul_args", n.SiluMulArgs),
+             ("jl_step_advance_args", n.StepAdvanceArgs), ("jl_decode_append_args", n.DecodeAppendArgs),
+             ("jl_peer_merge_args", n.PeerMergeArgs)]
+    header = open(os.path.join(ROOT, "include", "jetlong_b200.h")).read()
+    declared = set(re.findall(r"}\s*(jl_[a-z0-9_]+)\s*;", header))
+    assert declared == {name for name, _ in pairs}, declared ^ {name for name, _ in pairs}
     src = tmp_path / "sz.c"
-    src.write_text('#include <stdio.h>\n#include "jetlong_b200.h"\nint main(){printf("%zu %zu %zu %zu %zu %zu %zu %zu\\n",'
-                   "sizeof(jl_posmap),sizeof(jl_prefill_args),sizeof(jl_kv_segment),sizeof(jl_decode_args),"
-                   "sizeof(jl_merge_args),sizeof(jl_rotate_args),sizeof(jl_norm_rope_args),sizeof(jl_rmsnorm_args));return 0;}\n")
+    body = "".join(f'printf("%zu\\n", sizeof({name}));' for name, _ in pairs)
+    src.write_text('#include <stdio.h>\n#include "jetlong_b200.h"\nint main(){' + body + "return 0;}\n")
     exe = tmp_path / "sz"
     subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), "-o", str(exe), str(src)])
     sizes = [int(x) for x in subprocess.check_output([str(exe)]).split()]
-    assert sizes == [C.sizeof(t) for t in (n.PosMap, n.PrefillArgs, n.KvSegment, n.DecodeArgs, n.MergeArgs, n.RotateArgs, n.NormRopeArgs, n.RmsNormArgs)]
+    assert sizes == [C.sizeof(t) for _, t in pairs], list(zip([p[0] for p in pairs], sizes, [C.sizeof(t) for _, t in pairs]))
+    # and the last fields sit where the header puts them (a missing trailing field shows up here)
+    assert n.PrefillArgs.q_block_stride.offset + 8 == C.sizeof(n.PrefillArgs)
+    assert n.PeerMergeArgs.status.offset + 8 == C.sizeof(n.PeerMergeArgs)
 
 
 def test_host_only_entry_points():
     lib = _native().lib()
-    assert lib.jl_decode_workspace_bytes(1, 32, 128, 4) == 1 * 32 * 4 * 129 * 4
+    assert lib.jl_decode_workspace_bytes(1, 32, 128, 4) == 16384 + 1 * 32 * 4 * 129 * 4      # arrival counters + partials
     assert lib.jl_decode_workspace_bytes(0, 32, 128, 4) == 0
     s = lib.jl_decode_auto_splits(1, 8, 131072)
     assert 1 <= s and s * 8 <= 296

@@ -76,11 +76,17 @@ def _worker(rank, world, port, results):
             shard = SequenceShard(rank, world, block=256)
             be.configure_sequence_sharding(shard)
             model.model.token_sharded = True
-            local = model(input_ids=ids).logits.float()
+            rows = shard.owned_rows(ids.shape[1]).cuda()
+            d_tok, cos_tok = 0.0, 1.0
+            for forced in ("kv", "q"):          # both exchanges: gathered K / V, and gathered Q + returned partials
+                os.environ["JETLONG_SP_PREFILL"] = forced
+                local = model(input_ids=ids).logits.float()
+                assert be.LAST_TOKEN_SHARDED_MODE == ("kv_gather" if forced == "kv" else "q_exchange")
+                d, c = orc.compare(local.cpu(), full[:, rows].cpu())
+                d_tok, cos_tok = max(d_tok, d), min(cos_tok, c)
+            os.environ.pop("JETLONG_SP_PREFILL")
             be.configure_sequence_sharding(None)
             model.model.token_sharded = False
-        rows = shard.owned_rows(ids.shape[1]).cuda()
-        d_tok, cos_tok = orc.compare(local.cpu(), full[:, rows].cpu())
         # chunked prefill (first chunk inside the window) + decode steps on a striped static cache vs the
         # same schedule on one GPU; then the greedy driver, which must return the same tokens on every rank
         from jetlm.kernels.kv_cache import BifocalKVCache

@@ -84,6 +84,17 @@ def _worker(rank, world, port, block, results):
                 warnings.simplefilter("ignore")
                 assert make_peer_exchange(shard, 1, H, D, torch.device("cpu")) is None
         os.environ.pop("JETLONG_PEER_EXCHANGE")
+        # the K/V-gather form of the token-sharded prefill: every rank contributes its block-cyclic stripe of the
+        # keys and values, one all-gather, one strided copy -> the whole sequence in position order on every rank
+        from jetlm.kernels.sequence_parallel import interleave_stripes
+        n_full = 2 * world * block                              # two whole blocks per rank
+        seq = torch.randn(2, B, n_full, Hk, 8)                  # [K / V], same on every rank (seeded)
+        mine = shard.owned_rows(n_full)
+        stage = torch.empty(world, 2, B, mine.numel(), Hk, 8)
+        stage[rank] = seq[:, :, mine]
+        dist.all_gather_into_tensor(stage.view(-1), stage[rank].clone().view(-1))
+        full = interleave_stripes(stage, block, torch.empty(2, B, n_full, Hk, 8))
+        assert torch.equal(full, seq)
         results[rank] = (d, cos, dl, dd, dld)
     finally:
         dist.destroy_process_group()

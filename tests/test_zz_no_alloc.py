@@ -47,7 +47,7 @@ def test_static_scratch_decode_matches_workspace_decode_twice_in_a_row():
         v = torch.randn(B, S, Hk, 128, device="cuda").bfloat16()
         out_ws, out_st = (torch.zeros(B, 1, H, 128, device="cuda", dtype=torch.bfloat16) for _ in range(2))
         lse_ws, lse_st = (torch.zeros(B, H, device="cuda") for _ in range(2))
-        ws = torch.empty(lib.jl_decode_workspace_bytes(B, H, 128, 0), dtype=torch.uint8, device="cuda")
+        ws = torch.zeros(lib.jl_decode_workspace_bytes(B, H, 128, 0), dtype=torch.uint8, device="cuda")   # counters start at zero
         a = _args(n, q, k, v, boundary, out_ws, lse_ws, splits)
         a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
         n.check("jl_decode", lib.jl_decode(C.byref(a), stream))
