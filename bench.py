@@ -273,19 +273,17 @@ def decode_microbench(peaks, shard, iters=20, ctx=131072, w0=32768, batches=(1, 
             if int(agree) == 1:
                 exch = "peer"
             exchange_used[f"batch{B}"] = exch
-            variants.append(("pregrouped", lambda: call(exch, key_cache_group=kc)))
-            variants.append(("inplace_regroup", lambda: call(exch)))
+            variants.append(("pregrouped", lambda e: call(e, key_cache_group=kc), exch))
+            variants.append(("inplace_regroup", lambda e: call(e), exch))
             if exch == "peer":
-                variants.append(("pregrouped_nccl_exchange", lambda: call("nccl", key_cache_group=kc)))
-        res = {}
-        for tag, fn in variants:
-            if fn is None or (variants_wanted is not None and tag not in variants_wanted):
-                continue
+                variants.append(("pregrouped_nccl_exchange", lambda e: call(e, key_cache_group=kc), "nccl"))
+
+        def measure(fn):
             for _ in range(3):
                 fn()
             torch.cuda.synchronize()
             graph = None
-            try:                                   # kernels + (for N > 1) the NCCL all-gather in one graph
+            try:                                   # kernels + (for N > 1) the exchange in one graph
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph):
                     fn()
@@ -312,6 +310,28 @@ def decode_microbench(peaks, shard, iters=20, ctx=131072, w0=32768, batches=(1, 
                 t = torch.tensor([us], device="cuda")
                 torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
                 us = float(t)
+            return us
+
+        def peer_wait_gave_up():
+            """True on every rank if a bounded wait of jl_peer_merge ran out on any rank (the status words are cleared)."""
+            st = ops.kernel_status()
+            bad = torch.tensor([int(st["peer_exchange_failed"])], device="cuda")
+            torch.distributed.all_reduce(bad, op=torch.distributed.ReduceOp.MAX)
+            if int(bad):
+                ops.clear_peer_status()
+            return bool(int(bad))
+
+        res = {}
+        for tag, fn, *how in variants:
+            if fn is None or (variants_wanted is not None and tag not in variants_wanted):
+                continue
+            if shard is None:
+                us = measure(fn)
+            else:
+                us = measure(lambda: fn(how[0]))
+                if how[0] == "peer" and peer_wait_gave_up():       # never report a number whose exchange timed out
+                    us = measure(lambda: fn("nccl"))
+                    exchange_used[f"batch{B}"] = "nccl"
             nbytes = B * ctx * Hk * D * 2 * 2 / world            # K and V bytes ONE rank streams, against one GPU's peak
             res[tag] = dict(us=round(us, 2), gbs_per_gpu=round(nbytes / us / 1e3, 1),
                             frac_of_measured_hbm=round(nbytes / us / 1e3 / peaks["hbm_gbs"], 4),

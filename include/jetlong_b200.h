@@ -107,6 +107,17 @@ typedef struct {
                                128, a q_block that is not a multiple of 256, and more than two distinct key tensors */
   int64_t q_block;          /* <= 0 means contiguous */
   int64_t q_block_stride;
+  /* Far-field positions remapped INSIDE the kernel (band map, impl 0 only): with remap_far_in_kernel != 0 the far
+   * class is formed from the class-0 operands, which must be base-rotated (position p): every query tile and
+   * every key tile of the far phase is rotated in shared memory by (floor(p / group_size) - p) * inv_freq before
+   * the tensor cores read it, so q[1] / k[1] are ignored (may be NULL) and no regrouped copy of Q or K exists in
+   * HBM.  Replaces correction_rotate_per_sample on q and on the whole key cache,
+   * modeling_qwen3_jetlong_fused.py:375-379; the reference's own in-kernel form of the idea is
+   * apply_jetlong_k_transform_smem, cute_decode_sm90.py:931-966.  Slower than the pre-rotated operands (the
+   * rotation is repeated by every CTA that visits a key tile), so the Python layer leaves it off by default. */
+  int32_t remap_far_in_kernel;
+  int32_t group_size;
+  const float* inv_freq;    /* (head_dim/2,) fp32 device array; needed only with remap_far_in_kernel */
 } jl_prefill_args;
 
 int jl_prefill(const jl_prefill_args* args, void* cuda_stream);

@@ -78,6 +78,7 @@ static int validate_prefill(const jl_prefill_args* a) {
   if ((keys && a->v == nullptr) || a->out == nullptr) return fail(JL_ERR_BAD_ARG, "jl_prefill: v/out is NULL");
   uintptr_t bits = reinterpret_cast<uintptr_t>(a->v) | reinterpret_cast<uintptr_t>(a->out);
   for (int c = 0; c < a->map.n_classes; ++c) {
+    if (c > 0 && a->remap_far_in_kernel && a->impl == 0) continue;      // formed in-kernel from class 0
     if (a->q[c] == nullptr || (keys && a->k[c] == nullptr)) return fail(JL_ERR_BAD_ARG, "jl_prefill: operand of class %d is NULL", c);
     bits |= reinterpret_cast<uintptr_t>(a->q[c]) | reinterpret_cast<uintptr_t>(a->k[c]);
   }
@@ -202,7 +203,10 @@ int jl_prefill(const jl_prefill_args* args, void* cuda_stream) {
   if (rc != JL_OK) return rc;
   if (args->seqlen_q == 0) return JL_OK;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-  if (args->impl == 1) return jl::launch_prefill_mma(args, stream);      // explicit cross-check kernel only
+  if (args->impl == 1) {                                                  // explicit cross-check kernel only
+    if (args->remap_far_in_kernel) return jl::fail(JL_ERR_UNSUPPORTED, "jl_prefill: remap_far_in_kernel needs impl 0");
+    return jl::launch_prefill_mma(args, stream);
+  }
   if (args->impl != 0) return jl::fail(JL_ERR_BAD_ARG, "jl_prefill: impl must be 0 or 1, got %d", args->impl);
   if (const char* why = jl::prefill_tc_unsupported_reason(args))
     return jl::fail(JL_ERR_UNSUPPORTED, "jl_prefill: %s", why);

@@ -55,18 +55,6 @@ struct DecSmem {
   float inv_freq[64];
 };
 
-// sin/cos of an fp32 angle of any magnitude reached by RoPE positions (|theta| up to ~1e6 rad):
-// two-constant Cody-Waite reduction by 2*pi.  The first FMA subtracts k * fl32(2*pi) with the product
-// kept exact inside the FMA, so the cancellation costs nothing; the second adds back k times the
-// representation error of fl32(2*pi).  The SFU approximations are then used on [-pi, pi] only.
-__device__ __forceinline__ void sincos_reduced(float theta, float* s, float* c) {
-  const float k = rintf(theta * 0.15915494309189535f);
-  float r = fmaf(-k, 6.2831854820251465f, theta);
-  r = fmaf(k, 1.7484555314695172e-7f, r);
-  *s = __sinf(r);
-  *c = __cosf(r);
-}
-
 // Merge the split partials of one (batch, head) for output dim d (the 128 threads of a CTA cover the row).
 // The partials were written by other SMs, so they are read through L2 (ld.cg), never from this SM's L1.
 __device__ __forceinline__ void combine_head(const float* part_o, const float* part_lse, int64_t base, int num_splits,

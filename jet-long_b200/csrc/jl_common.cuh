@@ -88,6 +88,18 @@ __device__ __host__ __forceinline__ int64_t key_position(int64_t j, int64_t pos0
   return pos0 + (j / block) * block_stride + (j % block);
 }
 
+// sin/cos of an fp32 angle of any magnitude reached by RoPE positions (|theta| up to ~1e6 rad):
+// two-constant Cody-Waite reduction by 2*pi.  The first FMA subtracts k * fl32(2*pi) with the product
+// kept exact inside the FMA, so the cancellation costs nothing; the second adds back k times the
+// representation error of fl32(2*pi).  The SFU approximations are then used on [-pi, pi] only.
+__device__ __forceinline__ void sincos_reduced(float theta, float* s, float* c) {
+  const float k = rintf(theta * 0.15915494309189535f);
+  float r = fmaf(-k, 6.2831854820251465f, theta);
+  r = fmaf(k, 1.7484555314695172e-7f, r);
+  *s = __sinf(r);
+  *c = __cosf(r);
+}
+
 // One head row of "per-head Qwen3RMSNorm -> base RoPE", for the lane that holds dims (2l, 2l+1) in lo and
 // (64+2l, 64+2l+1) in hi.  Qwen3RMSNorm rounds the normalised value to bf16 before the (bf16) weight
 // multiply; the rotation is fp32 and the caller rounds once when it stores.  Shared by the prefill-side

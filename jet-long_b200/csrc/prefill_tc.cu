@@ -29,7 +29,22 @@ constexpr int kTileM = 128, kTileN = 128, kRowsPerCta = 256;
 constexpr int kKStages = 3, kVStages = 2;
 constexpr int kTileBytes = 128 * 256;           // 128 rows x 128 bf16
 constexpr int kHalfBytes = 128 * 128;           // one 64-column half (a TMA box)
-constexpr int kThreads = 384;
+#ifndef JL_SPLIT
+#define JL_SPLIT 1
+#endif
+// Softmax threads per query row.  1: one thread owns a row's 128 scores.  2: two threads in two warps of the same
+// TMEM lane quadrant own 64 columns each (they agree on the row maximum through shared memory), which halves
+// the dependent instruction stream between "S ready" and "P published".
+constexpr int kSplit = JL_SPLIT;
+constexpr int kCols = 128 / kSplit;             // score columns per softmax thread
+constexpr int kThreads = 128 + 256 * kSplit;
+#ifndef JL_TWO_PASS
+#define JL_TWO_PASS 0
+#endif
+// 1: the scores are read from tensor memory twice (once for the row maximum, once for the exponentials) instead of
+// being kept in registers in between; for the register budget of two threads per row.
+constexpr bool kTwoPass = JL_TWO_PASS != 0;
+constexpr int kRegsLow = 56, kRegsHigh = kSplit == 1 ? 224 : 104;   // per-role budgets; their weighted sum is the launch total
 #ifndef JL_POLY_MASK
 #define JL_POLY_MASK 0x11
 #endif
@@ -49,6 +64,10 @@ struct Params {
   float* lse;
   int64_t os_b, os_s, os_h;
   int* status;                    // device status word (0 = ok)
+  // In-kernel remap of the far class (BAND map): class 1 reads the class-0 tensors and warps 2-3 rotate every
+  // landed tile in shared memory by (floor(p / group_size) - p) * inv_freq before the tensor pipe reads it.
+  int remap, group_size;
+  const float* inv_freq;
 };
 
 struct Maps {
@@ -63,8 +82,10 @@ struct Smem {
   alignas(1024) uint8_t v[kVStages][kTileBytes];
   uint64_t q_full, q_free, k_full[kKStages], k_empty[kKStages], v_full[kVStages], v_empty[kVStages];
   uint64_t s_full[2], p_half[2][2], all_done;     // p_half[t][h]: probabilities of keys 64h..64h+63 of tile t are in TMEM
+  uint64_t q_ready, k_ready[kKStages];            // in-kernel remap only: the tile has been rotated (or needs no rotation)
   uint32_t tmem_base;
   int failed;
+  uint16_t xmax[kSplit == 2 ? 2 * 2 * 128 : 4];   // [query tile][column half][row]: bf16 row maxima exchanged by the two threads of a row
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -152,6 +173,11 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
   asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17," \
                "%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"                                              \
                ::"r"(taddr), JL_W32(r, o) : "memory")
+#define JL_TMEM_ST16(taddr, r, o)                                                                                          \
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"     \
+               ::"r"(taddr), "r"(r[o + 0]), "r"(r[o + 1]), "r"(r[o + 2]), "r"(r[o + 3]), "r"(r[o + 4]), "r"(r[o + 5]),       \
+                 "r"(r[o + 6]), "r"(r[o + 7]), "r"(r[o + 8]), "r"(r[o + 9]), "r"(r[o + 10]), "r"(r[o + 11]), "r"(r[o + 12]), \
+                 "r"(r[o + 13]), "r"(r[o + 14]), "r"(r[o + 15]) : "memory")
 // ---- packed fp32 pairs (one instruction per two lanes of work) and the FMA-pipe exp2 ----
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
@@ -297,6 +323,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
     for (int i = 0; i < kVStages; ++i) { mbar_init(&sm.v_full[i], 1); mbar_init(&sm.v_empty[i], 1); }
     for (int t = 0; t < 2; ++t) { mbar_init(&sm.s_full[t], 1); mbar_init(&sm.p_half[t][0], 128); mbar_init(&sm.p_half[t][1], 128); }
     mbar_init(&sm.all_done, 1);
+    mbar_init(&sm.q_ready, 64);
+    for (int i = 0; i < kKStages; ++i) mbar_init(&sm.k_ready[i], 64);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
@@ -311,7 +339,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
   // Register budget per role: the data-movement warpgroup gives registers back, the two softmax
   // warpgroups (one thread per row, 128 scores live) take them.
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;" ::);
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsLow));
   if (warp == 0) {
     // ===================================== TMA producer =====================================
     if (lane == 0) {
@@ -364,9 +392,11 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
       };
       int g = 0;           // global tile counter (K/V ring index, barrier parities)
       for (int ph = 0; ph < sched.n_phases; ++ph) {
-        mbar_wait(&sm.q_full, ph & 1, sm);
+        uint64_t* const q_bar = p.remap ? &sm.q_ready : &sm.q_full;           // with the in-kernel remap the tiles pass
+        uint64_t* const k_bar = p.remap ? sm.k_ready : sm.k_full;             // through warps 2-3 first
+        mbar_wait(q_bar, ph & 1, sm);
         const int n = sched.n_tiles[ph];
-        mbar_wait(&sm.k_full[g % kKStages], (g / kKStages) & 1, sm);
+        mbar_wait(&k_bar[g % kKStages], (g / kKStages) & 1, sm);
         tc_fence_after();
         issue_qk(0, g);
         issue_qk(1, g);
@@ -390,14 +420,14 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
               if (leader) {
 #pragma unroll
                 for (int kk = 4 * h; kk < 4 * h + 4; ++kk)
-                  mma_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8, vd + static_cast<uint64_t>((kk * 2048) >> 4), idesc_pv,
+                  mma_ts(tmem + 256 + t * 128, tmem + t * 128 + (kSplit == 1 ? kk * 8 : (kk >> 2) * 64 + (kk & 3) * 8), vd + static_cast<uint64_t>((kk * 2048) >> 4), idesc_pv,
                          (g > 0 || kk > 0) ? 1u : 0u);
                 if (t == 1 && h == 1) mma_commit(&sm.v_empty[vs]);
               }
             }
             if (more) {
               const int gn = g + 1;
-              if (t == 0) { mbar_wait(&sm.k_full[gn % kKStages], (gn / kKStages) & 1, sm); tc_fence_after(); }
+              if (t == 0) { mbar_wait(&k_bar[gn % kKStages], (gn / kKStages) & 1, sm); tc_fence_after(); }
               issue_qk(t, gn);
               if (t == 1 && leader) {
                 if (jj + 2 == n) mma_commit(&sm.q_free);       // last QK^T of this phase issued
@@ -410,11 +440,68 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
       if (leader) mma_commit(&sm.all_done);
       __syncwarp();
     }
+  } else if (p.remap) {
+    // =========================== in-kernel remap of the far class ===========================
+    // Warps 2-3 (64 threads).  Far phase: the query tiles and every key tile arrive base-rotated (the class-0
+    // tensors) and are rotated here, in shared memory, to the remapped position floor(p / G): each thread takes
+    // a 16-byte chunk (8 dims) of a row in the low half and the matching chunk of the high half (rotate-half
+    // pairs d <-> d + 64), with the angle fp32(floor(p / G) - p) * inv_freq[d] formed exactly as jl_rotate does.
+    // Other phases: the tiles are passed on untouched.  Generic-proxy writes are fenced for the tensor pipe.
+    const int tid = threadIdx.x - 64;
+    auto rotate_tile = [&](uint8_t* tile, int64_t row_pos0, int64_t block, int64_t block_stride, int64_t row0, int rows) {
+      for (int idx = tid; idx < 128 * 8; idx += 64) {
+        const int r = idx >> 3, ch = idx & 7;
+        if (r >= rows) continue;
+        const int64_t pos = key_position(row0 + r, row_pos0, block, block_stride);
+        const float tf = static_cast<float>(pos / p.group_size - pos);
+        uint8_t* lo_ptr = tile + r * 128 + ((ch ^ (r & 7)) << 4);
+        uint4 lo = *reinterpret_cast<uint4*>(lo_ptr), hi = *reinterpret_cast<uint4*>(lo_ptr + kHalfBytes);
+        uint32_t* lw = reinterpret_cast<uint32_t*>(&lo);
+        uint32_t* hw = reinterpret_cast<uint32_t*>(&hi);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int d = ch * 8 + 2 * j;
+          float s0, c0, s1, c1;
+          sincos_reduced(__fmul_rn(tf, __ldg(p.inv_freq + d)), &s0, &c0);
+          sincos_reduced(__fmul_rn(tf, __ldg(p.inv_freq + d + 1)), &s1, &c1);
+          const float2 l = unpack_bf16x2(lw[j]), h = unpack_bf16x2(hw[j]);
+          lw[j] = pack_bf16x2(l.x * c0 - h.x * s0, l.y * c1 - h.y * s1);
+          hw[j] = pack_bf16x2(h.x * c0 + l.x * s0, h.y * c1 + l.y * s1);
+        }
+        *reinterpret_cast<uint4*>(lo_ptr) = lo;
+        *reinterpret_cast<uint4*>(lo_ptr + kHalfBytes) = hi;
+      }
+    };
+    if (warp >= 2) {
+      int g = 0;
+      for (int ph = 0; ph < sched.n_phases; ++ph) {
+        const bool far = sched.cls[ph] == 1;
+        mbar_wait(&sm.q_full, ph & 1, sm);
+        if (far) {
+          for (int t = 0; t < 2; ++t)
+            rotate_tile(sm.q[t], p.q_pos0, p.q_block, p.q_block_stride, q_row0 + t * kTileM, min(kTileM, max(p.sq - (q_row0 + t * kTileM), 0)));
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        mbar_arrive(&sm.q_ready);
+        for (int jj = 0; jj < sched.n_tiles[ph]; ++jj, ++g) {
+          const int ks = g % kKStages;
+          mbar_wait(&sm.k_full[ks], (g / kKStages) & 1, sm);
+          if (far) {
+            const int64_t row0 = static_cast<int64_t>(sched.j_lo[ph] + jj) * kTileN;
+            rotate_tile(sm.k[ks], p.k_pos0, p.k_block, p.k_block_stride, row0, static_cast<int>(min(static_cast<int64_t>(kTileN), p.sk - row0)));
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          }
+          mbar_arrive(&sm.k_ready[ks]);
+        }
+      }
+    }
   }
   } else {
     // ================================ softmax + epilogue ================================
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;" ::);
-    const int t = (warp - 4) >> 2;                          // query tile 0 / 1
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsHigh));
+    const int sw = warp - 4;
+    const int t = sw / (4 * kSplit);                        // query tile 0 / 1
+    const int part = (sw >> 2) % kSplit;                    // which kCols-wide slice of the row's scores is mine
     const int quad = warp & 3;                              // TMEM lane quadrant this warp may access
     const int row_in_tile = quad * 32 + lane;
     const int q_row = q_row0 + t * kTileM + row_in_tile;
@@ -426,8 +513,11 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
     const int64_t pq_t0 = pq_cta0 + t * kTileM;
     const int64_t pq_t1 = pq_t0 + (tile_rows > 0 ? tile_rows - 1 : 0);
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
-    const uint32_t t_s = tmem + lane_base + t * 128;
-    const uint32_t t_o = tmem + lane_base + 256 + t * 128;
+    const uint32_t t_s = tmem + lane_base + t * 128 + part * kCols;           // my scores; bf16 P overlays their first half
+    const uint32_t t_o = tmem + lane_base + 256 + t * 128 + part * kCols;     // my columns of the output row
+    const int pair_bar = 1 + t * 4 + quad;                                    // named barrier of the two warps that share rows
+    uint16_t* my_max = &sm.xmax[((t * 2 + part) * 128 + row_in_tile) % (kSplit == 2 ? 512 : 4)];
+    const uint16_t* other_max = &sm.xmax[((t * 2 + (part ^ 1)) * 128 + row_in_tile) % (kSplit == 2 ? 512 : 4)];
 
     float m_ref = -INFINITY, l_sum = 0.f;
     int g = 0;
@@ -445,48 +535,50 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
 
         mbar_wait(&sm.s_full[t], g & 1, sm);
         tc_fence_after();
-        // scores -> registers and row maximum (4 independent chains of 3-input max).  The four 32-column
+        // scores -> registers and row maximum (4 independent chains of 3-input max).  The 32-column
         // loads are software-pipelined against the reduction: chunk c+1 is in flight while chunk c is reduced.
-        uint32_t s[128];
+        uint32_t s[kCols];
         float mx;
         {
           float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
           if (uniform) {
             JL_TMEM_LD32(t_s + 0, s, 0);
-            tmem_wait_ld();
-            JL_TMEM_LD32(t_s + 32, s, 32);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) m4[i & 3] = max3(m4[i & 3], __uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1]));
-            tmem_wait_ld();
-            JL_TMEM_LD32(t_s + 64, s, 64);
+            for (int ch = 0; ch < kCols / 32; ++ch) {
+              tmem_wait_ld();
+              if (ch + 1 < kCols / 32) JL_TMEM_LD32(t_s + (ch + 1) * 32, s, (ch + 1) * 32);
 #pragma unroll
-            for (int i = 16; i < 32; ++i) m4[i & 3] = max3(m4[i & 3], __uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1]));
-            tmem_wait_ld();
-            JL_TMEM_LD32(t_s + 96, s, 96);
-#pragma unroll
-            for (int i = 32; i < 48; ++i) m4[i & 3] = max3(m4[i & 3], __uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1]));
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 48; i < 64; ++i) m4[i & 3] = max3(m4[i & 3], __uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1]));
+              for (int i = ch * 16; i < ch * 16 + 16; ++i) m4[i & 3] = max3(m4[i & 3], __uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1]));
+            }
           } else {
-            JL_TMEM_LD32(t_s + 0, s, 0);
-            JL_TMEM_LD32(t_s + 32, s, 32);
-            JL_TMEM_LD32(t_s + 64, s, 64);
-            JL_TMEM_LD32(t_s + 96, s, 96);
-            tmem_wait_ld();
-            const int64_t lo64 = row_lo - tp0, hi64 = row_hi - tp0 + 1;
-            const int c_lo = lo64 < 0 ? 0 : (lo64 > 128 ? 128 : static_cast<int>(lo64));
-            const int c_hi = hi64 < 0 ? 0 : (hi64 > valid ? valid : static_cast<int>(hi64));
 #pragma unroll
-            for (int i = 0; i < 128; ++i)
+            for (int ch = 0; ch < kCols / 32; ++ch) JL_TMEM_LD32(t_s + ch * 32, s, ch * 32);
+            tmem_wait_ld();
+            const int64_t lo64 = row_lo - tp0 - part * kCols, hi64 = row_hi - tp0 + 1 - part * kCols;
+            const int v_here = min(max(valid - part * kCols, 0), kCols);
+            const int c_lo = lo64 < 0 ? 0 : (lo64 > kCols ? kCols : static_cast<int>(lo64));
+            const int c_hi = hi64 < 0 ? 0 : (hi64 > v_here ? v_here : static_cast<int>(hi64));
+#pragma unroll
+            for (int i = 0; i < kCols; ++i)
               if (!(i >= c_lo && i < c_hi)) s[i] = 0xff800000u;        // -inf
 #pragma unroll
-            for (int i = 0; i < 64; ++i) m4[i & 3] = max3(m4[i & 3], __uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1]));
+            for (int i = 0; i < kCols / 2; ++i) m4[i & 3] = max3(m4[i & 3], __uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1]));
           }
           mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
         }
+        if (kSplit == 2) {
+          // The two threads of a row need ONE reference maximum.  Any common value close to the true maximum
+          // will do (it only keeps the exponentials in range), so each rounds its own to bf16, they swap
+          // the 16-bit values and both take the larger.  One buffer is enough: the partner reads it before it
+          // publishes P, and the next scores, hence my next write, exist only after that P has been consumed.
+          const __nv_bfloat16 mine = __float2bfloat16_rn(mx);
+          *my_max = __bfloat16_as_ushort(mine);
+          asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+          mx = fmaxf(__bfloat162float(mine), __bfloat162float(__ushort_as_bfloat16(*reinterpret_cast<const volatile uint16_t*>(other_max))));
+        }
         mx *= p.scale_log2;                                  // scale > 0: max commutes with the scaling
         // lazy rescale: only when some row of the warp outgrew its reference maximum by 2^8
+        // (with two threads per row both see the same maxima and take the same decision)
         const bool grow = mx > m_ref + 8.f;
         if (__any_sync(0xffffffffu, grow)) {
           const float m_new = fmaxf(m_ref, mx);
@@ -495,7 +587,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
           if (g > 0) {
             // O_t is quiescent here: S_t(g) ready implies P_t V(g-1) retired, and P_t V(g) waits for our P
 #pragma unroll
-            for (int cchunk = 0; cchunk < 4; ++cchunk) {
+            for (int cchunk = 0; cchunk < kCols / 32; ++cchunk) {
               uint32_t o[32];
               JL_TMEM_LD32(t_o + cchunk * 32, o, 0);
               tmem_wait_ld();
@@ -507,26 +599,46 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
           m_ref = m_new;
         }
         const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-        // p = 2^(s * scale - m): packed FMA, then the exponentials split between the FMA pipe and the SFU (kPolyMask)
+        // p = 2^(s * scale - m): packed FMA, then the exponentials split between the FMA pipe and the SFU (kPolyMask).
+        // Every 64 scores become 32 packed bf16 columns at the start of those 64 score columns and are published
+        // with their own barrier, so the first four k-steps of P V never wait for the last exponentials.
         const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negm2 = pack2(-m_use, -m_use);
         uint64_t acc2[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t pk[32];
+        for (int half = 0; half < kCols / 64; ++half) {
+          // 16 packed columns at a time: with two threads per row the register budget has no room for 32
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int e = half * 64 + 2 * i;
-            const uint64_t x = fma2(pack2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), scale2, negm2);
-            const uint64_t pp = ((kPolyMask >> (i & 7)) & 1u) ? exp2_pair_fma(x) : exp2_pair_sfu(x);
-            acc2[i & 3] = add2(acc2[i & 3], pp);
-            float p0, p1;
-            unpack2(pp, p0, p1);
-            pk[i] = pack_bf16x2(p0, p1);
+          for (int sub = 0; sub < 2; ++sub) {
+            if (kTwoPass) {
+              // second read of this 32-column chunk (the first pass only took its maximum)
+              JL_TMEM_LD32(t_s + half * 64 + sub * 32, s, half * 64 + sub * 32);
+              tmem_wait_ld();
+              if (!uniform) {
+                const int64_t lo64 = row_lo - tp0 - part * kCols, hi64 = row_hi - tp0 + 1 - part * kCols;
+                const int v_here = min(max(valid - part * kCols, 0), kCols);
+                const int c_lo = lo64 < 0 ? 0 : (lo64 > kCols ? kCols : static_cast<int>(lo64));
+                const int c_hi = hi64 < 0 ? 0 : (hi64 > v_here ? v_here : static_cast<int>(hi64));
+#pragma unroll
+                for (int i = half * 64 + sub * 32; i < half * 64 + sub * 32 + 32; ++i)
+                  if (!(i >= c_lo && i < c_hi)) s[i] = 0xff800000u;
+              }
+            }
+            uint32_t pk[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int e = half * 64 + sub * 32 + 2 * i;
+              const uint64_t x = fma2(pack2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), scale2, negm2);
+              const uint64_t pp = ((kPolyMask >> (i & 7)) & 1u) ? exp2_pair_fma(x) : exp2_pair_sfu(x);
+              acc2[i & 3] = add2(acc2[i & 3], pp);
+              float p0, p1;
+              unpack2(pp, p0, p1);
+              pk[i] = pack_bf16x2(p0, p1);
+            }
+            JL_TMEM_ST16(t_s + (kSplit == 1 ? half * 32 : 0) + sub * 16, pk, 0);
           }
-          JL_TMEM_ST32(t_s + half * 32, pk, 0);
           tmem_wait_st();
           tc_fence_before();
-          mbar_arrive(&sm.p_half[t][half]);
+          mbar_arrive(&sm.p_half[t][kSplit == 1 ? half : part]);
         }
         {
           float a0, a1;
@@ -541,11 +653,18 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
       mbar_wait(&sm.all_done, 0, sm);
       tc_fence_after();
     }
+    if (kSplit == 2) {
+      // row sum = my columns + the partner's; the query tiles in shared memory are dead by now (every MMA has retired)
+      float* sums = reinterpret_cast<float*>(sm.q[0]);
+      sums[(t * 2 + part) * 128 + row_in_tile] = l_sum;
+      asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+      l_sum += *reinterpret_cast<volatile float*>(&sums[(t * 2 + (part ^ 1)) * 128 + row_in_tile]);
+    }
     const bool seen = m_ref != -INFINITY;                 // masked scores add ~1e-38 each to l_sum, never to m_ref
     const float inv = seen ? 1.f / l_sum : 0.f;
-    __nv_bfloat16* orow = p.out + b * p.os_b + static_cast<int64_t>(q_row) * p.os_s + head * p.os_h;
+    __nv_bfloat16* orow = p.out + b * p.os_b + static_cast<int64_t>(q_row) * p.os_s + head * p.os_h + part * kCols;
 #pragma unroll
-    for (int cchunk = 0; cchunk < 4; ++cchunk) {
+    for (int cchunk = 0; cchunk < kCols / 32; ++cchunk) {
       uint32_t o[32];
       if (sched.total > 0) {
         JL_TMEM_LD32(t_o + cchunk * 32, o, 0);
@@ -566,7 +685,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
         }
       }
     }
-    if (row_valid && p.lse != nullptr)
+    if (row_valid && part == 0 && p.lse != nullptr)
       p.lse[(static_cast<int64_t>(b) * p.heads + head) * p.sq + q_row] = seen ? (m_ref + log2f(l_sum)) * kLn2 : -INFINITY;
   }
 
@@ -623,6 +742,11 @@ const char* prefill_tc_unsupported_reason(const jl_prefill_args* a) {
     return "k_block must be a multiple of 128 (the key tile)";
   if (a->q_block > 0 && a->q_block < a->seqlen_q && (a->q_block % tc::kRowsPerCta != 0))
     return "q_block must be a multiple of 256 (the query rows of one CTA)";
+  if (a->remap_far_in_kernel) {
+    if (a->map.kind != JL_MAP_BAND) return "remap_far_in_kernel needs the band map";
+    if (a->inv_freq == nullptr || a->group_size < 1) return "remap_far_in_kernel needs inv_freq and group_size >= 1";
+    return nullptr;
+  }
   int distinct = 0;
   const void* seen[2] = {nullptr, nullptr};
   for (int c = 0; c < a->map.n_classes; ++c) {
@@ -667,17 +791,20 @@ int launch_prefill_tc(const jl_prefill_args* a, cudaStream_t stream) {
   int n_k = 0;
   const void* kptr[2] = {nullptr, nullptr};
   const bool no_keys = a->seqlen_k == 0;      // nothing is loaded then: the key / value maps only have to be well formed
+  const bool remap = a->remap_far_in_kernel != 0;      // the far class then reads the class-0 tensors
   for (int c = 0; c < a->map.n_classes; ++c) {
-    int rc = make_map(&maps.q[c], a->q[c], a->batch, a->seqlen_q, a->heads, a->q_stride_b, a->q_stride_s, a->q_stride_h);
+    const void* qc = remap ? a->q[0] : a->q[c];
+    const void* kc = remap ? a->k[0] : a->k[c];
+    int rc = make_map(&maps.q[c], qc, a->batch, a->seqlen_q, a->heads, a->q_stride_b, a->q_stride_s, a->q_stride_h);
     if (rc != JL_OK) return rc;
     int slot = -1;
     for (int i = 0; i < n_k; ++i)
-      if (kptr[i] == a->k[c]) slot = i;
+      if (kptr[i] == kc) slot = i;
     if (slot < 0) {
       slot = n_k++;
-      kptr[slot] = a->k[c];
+      kptr[slot] = kc;
       rc = no_keys ? make_map(&maps.k[slot], a->q[0], 1, 1, 1, 0, 0, 0)
-                   : make_map(&maps.k[slot], a->k[c], a->batch, a->seqlen_k, a->kv_heads, a->k_stride_b, a->k_stride_s, a->k_stride_h);
+                   : make_map(&maps.k[slot], kc, a->batch, a->seqlen_k, a->kv_heads, a->k_stride_b, a->k_stride_s, a->k_stride_h);
       if (rc != JL_OK) return rc;
     }
     p.k_map[c] = slot;
@@ -700,6 +827,9 @@ int launch_prefill_tc(const jl_prefill_args* a, cudaStream_t stream) {
   p.lse = a->lse;
   p.os_b = a->o_stride_b; p.os_s = a->o_stride_s; p.os_h = a->o_stride_h;
   p.status = status_word();
+  p.remap = a->remap_far_in_kernel != 0;
+  p.group_size = a->group_size > 0 ? a->group_size : 1;
+  p.inv_freq = a->inv_freq;
   const int smem = static_cast<int>(sizeof(tc::Smem)) + 1024;
   // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute
   static bool attr_done[64] = {false};

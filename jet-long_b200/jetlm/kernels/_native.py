@@ -36,6 +36,7 @@ class PrefillArgs(C.Structure):
         ("q_pos0", C.c_int64), ("k_pos0", C.c_int64), ("k_block", C.c_int64), ("k_block_stride", C.c_int64),
         ("softmax_scale", C.c_float), ("map", PosMap), ("impl", C.c_int32),
         ("q_block", C.c_int64), ("q_block_stride", C.c_int64),
+        ("remap_far_in_kernel", C.c_int32), ("group_size", C.c_int32), ("inv_freq", C.c_void_p),
     ]
 
 

@@ -84,6 +84,12 @@ def kernel_status() -> dict:
     return dict(prefill_wait_timeouts=int(N.lib().jl_prefill_status()), peer_exchange_failed=failed)
 
 
+def clear_peer_status() -> None:
+    """Put the status words of every live peer exchange back to zero (after a reported timeout has been handled)."""
+    for ex in list(_PEER_EXCHANGES):
+        ex.status.zero_()
+
+
 def check_status() -> None:
     """Raise if a bounded wait inside jl_prefill or jl_peer_merge gave up: the results produced since the
     last check are then invalid.  Call at a point that synchronises anyway (end of a step, before logits leave)."""
@@ -331,10 +337,18 @@ def posmap_prefill(q_ops: Sequence[torch.Tensor], k_ops: Sequence[torch.Tensor],
                    pmap: PositionMap, q_pos0: int, k_pos0: int = 0, softmax_scale: Optional[float] = None,
                    k_block: int = 0, k_block_stride: int = 0, q_block: int = 0, q_block_stride: int = 0,
                    out: Optional[torch.Tensor] = None,
-                   lse: Optional[torch.Tensor] = None, return_lse: bool = True, impl: int = 0):
+                   lse: Optional[torch.Tensor] = None, return_lse: bool = True, impl: int = 0,
+                   remap_far: Optional[tuple] = None):
     """Single-pass position-mapped causal attention (see jl_prefill).  q_ops[c]: (B,Sq,H,D) views sharing
-    strides; k_ops[c], v: (B,Skv,Hk,D) views (all k_ops share strides).  Returns (out, lse) or out."""
+    strides; k_ops[c], v: (B,Skv,Hk,D) views (all k_ops share strides).  Returns (out, lse) or out.
+    remap_far = (inv_freq, group_size): jetlong band map with the far class formed INSIDE the kernel from the
+    base-rotated operands; pass only [q_base] and [k_base]."""
     op = "posmap_prefill"
+    keep = []
+    if remap_far is not None:
+        if len(q_ops) != 1 or len(k_ops) != 1 or pmap.kind != N.JL_MAP_BAND:
+            raise ValueError(f"{op}: remap_far takes the band map and one base-rotated q and k operand")
+        q_ops, k_ops = [q_ops[0], q_ops[0]], [k_ops[0], k_ops[0]]
     if len(q_ops) != pmap.n_classes or len(k_ops) != pmap.n_classes:
         raise ValueError(f"{op}: the position map has {pmap.n_classes} classes; got {len(q_ops)} q and {len(k_ops)} k operands")
     q0, k0 = q_ops[0], k_ops[0]
@@ -392,6 +406,10 @@ def posmap_prefill(q_ops: Sequence[torch.Tensor], k_ops: Sequence[torch.Tensor],
     a.map = pmap.c_struct()
     a.impl = int(impl)
     a.q_block, a.q_block_stride = int(q_block), int(q_block_stride)
+    if remap_far is not None:
+        inv_freq = remap_far[0].to(device=q0.device, dtype=torch.float32).contiguous()
+        keep.append(inv_freq)
+        a.remap_far_in_kernel, a.group_size, a.inv_freq = 1, int(remap_far[1]), inv_freq.data_ptr()
     with torch.cuda.device(q0.device):
         _call("jl_prefill", lambda: N.lib().jl_prefill(C.byref(a), _stream()))
     return (out, lse) if return_lse else out

@@ -157,3 +157,85 @@ def test_decode_in_kernel_regroup_full_context_spot_heads(B):
         eo, el = orc.jetlong_decode(q[:, :, hs].cpu(), qg[:, :, hs].cpu(), k[:, b:, kvh: kvh + 1].cpu(), v[:, b:, kvh: kvh + 1].cpu(),
                                     kfar, v[:, :b, kvh: kvh + 1].cpu())
         _check(out[:, :, hs], lse[:, hs], eo, el, f"decode in-kernel regroup, ctx 131072, B={B}, kv head {kvh}")
+
+
+def test_million_token_context_g32_decode_and_prefill_rows():
+    """BASELINE config 5 geometry on one GPU at the operator level: positions up to 1,048,576 with G = 32
+    (w = w_0 = 32768), where the fp32 RoPE angles are largest.  (1) decode of the token at position 2^20 - 1 over
+    the whole base-rotated cache with the far keys regrouped in-kernel; (2) a 512-row prefill chunk that ends at
+    2^20 against all keys (operands from jl_rotate), and the same chunk with the far class remapped inside the
+    kernel.  All query heads of one kv head / sampled rows against the fp32 oracle."""
+    ops = _ops()
+    torch.manual_seed(77)
+    H, Hk, D, ctx, w0, G = 8, 2, 128, 1 << 20, 32768, 32
+    inv = orc.default_inv_freq()
+    dinv = inv.cuda()
+    k_raw = torch.randn(1, ctx, Hk, D, device="cuda").bfloat16()
+    v = torch.randn(1, ctx, Hk, D, device="cuda").bfloat16()
+    kb = ops.rope_base(k_raw, dinv)
+    del k_raw
+    rep = H // Hk
+    # ---- (1) decode ----
+    q_raw = torch.randn(1, 1, H, D, device="cuda").bfloat16()
+    qb = ops.rope_base(q_raw, dinv, pos0=ctx - 1)
+    qg = ops.rope_regroup(qb, dinv, group_size=G, pos0=ctx - 1)
+    b = ctx - 1 - w0
+    segs = [ops.KvSegment(kb[:, :b], v[:, :b], 1, rotate=True, pos0=0), ops.KvSegment(kb[:, b:], v[:, b:], 0)]
+    out, lse = ops.decode_segments([qb, qg], segs, inv_freq=dinv, group_size=G)
+    kvh = 1
+    hs = slice(kvh * rep, (kvh + 1) * rep)
+    pos = torch.arange(b).view(1, b)
+    kfar = orc.rotate_bshd(kb[:, :b, kvh: kvh + 1].float().cpu(), orc.regroup_delta(pos, G), inv)
+    eo, el = orc.jetlong_decode(qb[:, :, hs].cpu(), qg[:, :, hs].cpu(), kb[:, b:, kvh: kvh + 1].cpu(), v[:, b:, kvh: kvh + 1].cpu(),
+                                kfar, v[:, :b, kvh: kvh + 1].cpu())
+    _check(out[:, :, hs], lse[:, hs], eo, el, "decode at 2^20 keys, G = 32, in-kernel regroup")
+    # ---- (2) the last 512-row chunk of a chunked prefill ----
+    Sq = 512
+    q_raw = torch.randn(1, Sq, H, D, device="cuda").bfloat16()
+    qb = ops.rope_base(q_raw, dinv, pos0=ctx - Sq)
+    qg = ops.rope_regroup(qb, dinv, group_size=G, pos0=ctx - Sq)
+    kg = ops.rope_regroup(kb, dinv, group_size=G)
+    pm = ops.PositionMap.jetlong(w0)
+    out, lse = ops.posmap_prefill([qb, qg], [kb, kg], v, pmap=pm, q_pos0=ctx - Sq)
+    out_r, lse_r = ops.posmap_prefill([qb], [kb], v, pmap=pm, q_pos0=ctx - Sq, remap_far=(dinv, G))
+    assert _status_clean()
+    d, cos = orc.compare(out_r.float().cpu(), out.float().cpu())
+    dl, _ = orc.compare(lse_r.cpu(), lse.cpu())
+    assert d <= OUT_TOL and cos >= COS_TOL and dl <= LSE_TOL, ("in-kernel remap vs pre-rotated operands", d, cos, dl)
+    for i, r in enumerate((0, 255, 256, Sq - 1)):
+        h = (3 * i + 1) % H
+        kvh = h // rep
+        n_k = ctx - Sq + r + 1
+        # oracle operands: exact fp32 regrouping of the bf16 base-rotated tensors the kernels consumed
+        kpos = torch.arange(n_k).view(1, n_k)
+        kg_ref = orc.rotate_bshd(kb[:, :n_k, kvh: kvh + 1].float().cpu(), orc.regroup_delta(kpos, G), inv)
+        qg_ref = orc.rotate_bshd(qb[:, r: r + 1, h: h + 1].float().cpu(), orc.regroup_delta(torch.tensor([[ctx - Sq + r]]), G), inv)
+        eo, el = orc.jetlong_prefill(qb[:, r: r + 1, h: h + 1].float().cpu(), qg_ref, kb[:, :n_k, kvh: kvh + 1].float().cpu(), kg_ref,
+                                     v[:, :n_k, kvh: kvh + 1].float().cpu(), seqstart=ctx - Sq + r, w0=w0)
+        _check(out[:, r: r + 1, h: h + 1], lse[:, h: h + 1, r: r + 1], eo, el, f"prefill row at position {ctx - Sq + r}, pre-rotated operands")
+        _check(out_r[:, r: r + 1, h: h + 1], lse_r[:, h: h + 1, r: r + 1], eo, el, f"prefill row at position {ctx - Sq + r}, in-kernel remap")
+
+
+@pytest.mark.parametrize("S,Skv,w0,G", [(300, 300, 100, 3), (700, 1500, 200, 4), (1, 900, 64, 7), (513, 513, 0, 2)])
+def test_in_kernel_far_remap_matches_the_oracle(S, Skv, w0, G):
+    """jl_prefill with remap_far_in_kernel: only base-rotated q / k go in; the far class is rotated per tile in
+    shared memory.  Against the oracle's two-branch composition on exactly regrouped fp32 operands, at positions
+    near 131072 so that the angles are large."""
+    ops = _ops()
+    torch.manual_seed(S + G)
+    B, H, Hk, D = 1, 4, 2, 128
+    P0 = 131072 - Skv
+    inv = orc.default_inv_freq()
+    q_raw, k_raw = torch.randn(B, S, H, D).bfloat16(), torch.randn(B, Skv, Hk, D).bfloat16()
+    v = torch.randn(B, Skv, Hk, D).bfloat16()
+    qb = ops.rope_base(q_raw.cuda(), inv.cuda(), pos0=P0 + Skv - S)
+    kb = ops.rope_base(k_raw.cuda(), inv.cuda(), pos0=P0)
+    out, lse = ops.posmap_prefill([qb], [kb], v.cuda(), pmap=ops.PositionMap.jetlong(w0), q_pos0=P0 + Skv - S, k_pos0=P0,
+                                  remap_far=(inv.cuda(), G))
+    assert _status_clean()
+    qpos = (torch.arange(S) + P0 + Skv - S).view(1, S)
+    kpos = (torch.arange(Skv) + P0).view(1, Skv)
+    qg = orc.rotate_bshd(qb.float().cpu(), orc.regroup_delta(qpos, G), inv)
+    kg = orc.rotate_bshd(kb.float().cpu(), orc.regroup_delta(kpos, G), inv)
+    eo, el = orc.jetlong_prefill(qb.float().cpu(), qg, kb.float().cpu(), kg, v.float(), seqstart=Skv - S, w0=w0)
+    _check(out, lse, eo, el, f"in-kernel remap S={S} Skv={Skv} w0={w0} G={G}")
