@@ -55,31 +55,44 @@ struct DecSmem {
   float inv_freq[64];
 };
 
-// Merge the split partials of one (batch, head) for output dim d (the 128 threads of a CTA cover the row).
-// The partials were written by other SMs, so they are read through L2 (ld.cg), never from this SM's L1.
-__device__ __forceinline__ void combine_head(const float* part_o, const float* part_lse, int64_t base, int num_splits,
-                                             int d, __nv_bfloat16* out_row, float* lse_out) {
+// Merge the split partials of one (batch, head) with ONE WARP: every lane owns 4 of the 128 output dims
+// (one 16-byte load per partial), lanes share the split weights by shuffle.  The partials were written by
+// other SMs, so they are read through L2 (ld.cg), never from this SM's L1.
+__device__ __forceinline__ void combine_head_warp(const float* part_o, const float* part_lse, int64_t base, int num_splits,
+                                                  int lane, __nv_bfloat16* out_row, float* lse_out) {
   float m = -INFINITY;
-  for (int s = 0; s < num_splits; ++s) m = fmaxf(m, __ldcg(part_lse + base + s));
+  for (int s = lane; s < num_splits; s += 32) m = fmaxf(m, __ldcg(part_lse + base + s));
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
   const float ms = m == -INFINITY ? 0.f : m;
-  float wsum = 0.f, acc = 0.f;
-  for (int s0 = 0; s0 < num_splits; s0 += 8) {
-    float x[8], l[8];
+  float wsum = 0.f;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float4* po = reinterpret_cast<const float4*>(part_o) + base * 32 + lane;       // 32 float4 per partial row
+  for (int s0 = 0; s0 < num_splits; s0 += 32) {
+    // weights of splits s0 .. s0 + 31: lane i holds the weight of split s0 + i
+    const float w_mine = s0 + lane < num_splits ? exp2f((__ldcg(part_lse + base + s0 + lane) - ms) * kLog2e) : 0.f;
+    const int n = min(32, num_splits - s0);
+    for (int k0 = 0; k0 < n; k0 += 8) {
+      float4 x[8];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {          // 8 independent loads in flight per thread
-      const bool ok = s0 + k < num_splits;
-      x[k] = ok ? __ldcg(part_o + (base + s0 + k) * 128 + d) : 0.f;
-      l[k] = ok ? __ldcg(part_lse + base + s0 + k) : -INFINITY;
-    }
+      for (int k = 0; k < 8; ++k)            // 8 independent 16-byte loads in flight per lane
+        x[k] = k0 + k < n ? __ldcg(po + static_cast<int64_t>(s0 + k0 + k) * 32) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const float w = exp2f((l[k] - ms) * kLog2e);
-      wsum += w;
-      acc = fmaf(w, x[k], acc);
+      for (int k = 0; k < 8; ++k) {
+        const float w = __shfl_sync(0xffffffffu, w_mine, (k0 + k) & 31);
+        const float wk = k0 + k < n ? w : 0.f;
+        wsum += wk;
+        acc.x = fmaf(wk, x[k].x, acc.x); acc.y = fmaf(wk, x[k].y, acc.y);
+        acc.z = fmaf(wk, x[k].z, acc.z); acc.w = fmaf(wk, x[k].w, acc.w);
+      }
     }
   }
-  out_row[d] = __float2bfloat16(wsum > 0.f ? acc / wsum : 0.f);
-  if (lse_out != nullptr && d == 0) *lse_out = wsum > 0.f ? ms + logf(wsum) : -INFINITY;
+  const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+  uint2 packed;
+  packed.x = pack_bf16x2(acc.x * inv, acc.y * inv);
+  packed.y = pack_bf16x2(acc.z * inv, acc.w * inv);
+  *reinterpret_cast<uint2*>(out_row + lane * 4) = packed;
+  if (lse_out != nullptr && lane == 0) *lse_out = wsum > 0.f ? ms + logf(wsum) : -INFINITY;
 }
 
 __global__ void __launch_bounds__(kDecWarps * 32, 2) decode_kernel(const DecParams p) {
@@ -349,22 +362,24 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) decode_kernel(const DecPara
 
   // ---- the last CTA of this (batch, kv head) to get here merges the splits ----
   __shared__ int s_last;
-  __threadfence();                       // this thread's partial writes are visible device-wide ...
-  __syncthreads();                       // ... for every thread of the CTA, before the arrival is counted
+  __syncthreads();                       // every thread's partial writes are ordered before thread 0's fence
   if (threadIdx.x == 0) {
+    __threadfence();                     // ... which makes them visible device-wide before the arrival is counted
     int* counter = p.arrivals + b * p.kv_heads + kvh;
     const int seen = atomicAdd(counter, 1);
     s_last = seen == p.num_splits - 1;
-    if (s_last) *counter = 0;            // nobody else touches it until the next launch
+    if (s_last) {
+      *counter = 0;                      // nobody else touches it until the next launch
+      __threadfence();                   // the other CTAs' partials are visible to the reads below
+    }
   }
   __syncthreads();
   if (!s_last) return;
-  __threadfence();
-  for (int row = 0; row < rep; ++row) {
+  for (int row = warp; row < rep; row += kDecWarps) {       // one warp per query head
     const int head = kvh * rep + row;
     const int64_t bh = static_cast<int64_t>(b) * p.heads + head;
-    combine_head(p.part_o, p.part_lse, bh * p.num_splits, p.num_splits, threadIdx.x, p.out + b * p.os_b + head * p.os_h,
-                 p.lse_out != nullptr ? p.lse_out + bh : nullptr);
+    combine_head_warp(p.part_o, p.part_lse, bh * p.num_splits, p.num_splits, lane, p.out + b * p.os_b + head * p.os_h,
+                      p.lse_out != nullptr ? p.lse_out + bh : nullptr);
   }
 }
 
@@ -393,6 +408,8 @@ int launch_decode(const jl_decode_args* a, cudaStream_t stream) {
   if (a->n_segments < 1 || a->n_segments > JL_MAX_SEGMENTS) return fail(JL_ERR_BAD_ARG, "jl_decode: n_segments must be in [1, %d]", JL_MAX_SEGMENTS);
   if (a->out == nullptr) return fail(JL_ERR_BAD_ARG, "jl_decode: out is NULL");
   if (a->q_stride_b % 8 || a->q_stride_h % 8) return fail(JL_ERR_BAD_ARG, "jl_decode: q strides must be multiples of 8 elements");
+  if ((reinterpret_cast<uintptr_t>(a->out) & 7) || a->o_stride_b % 4 || a->o_stride_h % 4)
+    return fail(JL_ERR_BAD_ARG, "jl_decode: out must be 8-byte aligned with strides that are multiples of 4 elements");
   DecParams p{};
   int64_t total = 0;
   bool any_rotate = false;

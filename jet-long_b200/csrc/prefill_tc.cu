@@ -41,6 +41,11 @@ constexpr int kThreads = 128 + 256 * kSplit;
 #ifndef JL_TWO_PASS
 #define JL_TWO_PASS 0
 #endif
+// Build-time diagnostics for timing experiments only (results are wrong): 1 = exponentials replaced by the
+// identity, 2 = the softmax warps only hand the barriers on, 4 = scores are loaded and their maximum taken, nothing else.
+#ifndef JL_DIAG
+#define JL_DIAG 0
+#endif
 // 1: the scores are read from tensor memory twice (once for the row maximum, once for the exponentials) instead of
 // being kept in registers in between; for the register budget of two threads per row.
 constexpr bool kTwoPass = JL_TWO_PASS != 0;
@@ -535,6 +540,12 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
 
         mbar_wait(&sm.s_full[t], g & 1, sm);
         tc_fence_after();
+#if JL_DIAG == 2
+        tc_fence_before();
+        mbar_arrive(&sm.p_half[t][0]);
+        mbar_arrive(&sm.p_half[t][1]);
+        continue;
+#endif
         // scores -> registers and row maximum (4 independent chains of 3-input max).  The 32-column
         // loads are software-pipelined against the reduction: chunk c+1 is in flight while chunk c is reduced.
         uint32_t s[kCols];
@@ -576,6 +587,13 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
           asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
           mx = fmaxf(__bfloat162float(mine), __bfloat162float(__ushort_as_bfloat16(*reinterpret_cast<const volatile uint16_t*>(other_max))));
         }
+#if JL_DIAG == 4
+        l_sum += mx;
+        tc_fence_before();
+        mbar_arrive(&sm.p_half[t][0]);
+        mbar_arrive(&sm.p_half[t][1]);
+        continue;
+#endif
         mx *= p.scale_log2;                                  // scale > 0: max commutes with the scaling
         // lazy rescale: only when some row of the warp outgrew its reference maximum by 2^8
         // (with two threads per row both see the same maxima and take the same decision)
@@ -628,7 +646,11 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
             for (int i = 0; i < 16; ++i) {
               const int e = half * 64 + sub * 32 + 2 * i;
               const uint64_t x = fma2(pack2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), scale2, negm2);
+#if JL_DIAG == 1
+              const uint64_t pp = x;
+#else
               const uint64_t pp = ((kPolyMask >> (i & 7)) & 1u) ? exp2_pair_fma(x) : exp2_pair_sfu(x);
+#endif
               acc2[i & 3] = add2(acc2[i & 3], pp);
               float p0, p1;
               unpack2(pp, p0, p1);

@@ -206,10 +206,11 @@ def test_million_token_context_g32_decode_and_prefill_rows():
         h = (3 * i + 1) % H
         kvh = h // rep
         n_k = ctx - Sq + r + 1
-        # oracle operands: exact fp32 regrouping of the bf16 base-rotated tensors the kernels consumed
+        # oracle operands: the fp32 regrouping of the bf16 base-rotated tensors, rounded to bf16 as both kernel paths
+        # round the far-class operands before the tensor cores read them
         kpos = torch.arange(n_k).view(1, n_k)
-        kg_ref = orc.rotate_bshd(kb[:, :n_k, kvh: kvh + 1].float().cpu(), orc.regroup_delta(kpos, G), inv)
-        qg_ref = orc.rotate_bshd(qb[:, r: r + 1, h: h + 1].float().cpu(), orc.regroup_delta(torch.tensor([[ctx - Sq + r]]), G), inv)
+        kg_ref = orc.rotate_bshd(kb[:, :n_k, kvh: kvh + 1].float().cpu(), orc.regroup_delta(kpos, G), inv).bfloat16().float()
+        qg_ref = orc.rotate_bshd(qb[:, r: r + 1, h: h + 1].float().cpu(), orc.regroup_delta(torch.tensor([[ctx - Sq + r]]), G), inv).bfloat16().float()
         eo, el = orc.jetlong_prefill(qb[:, r: r + 1, h: h + 1].float().cpu(), qg_ref, kb[:, :n_k, kvh: kvh + 1].float().cpu(), kg_ref,
                                      v[:, :n_k, kvh: kvh + 1].float().cpu(), seqstart=ctx - Sq + r, w0=w0)
         _check(out[:, r: r + 1, h: h + 1], lse[:, h: h + 1, r: r + 1], eo, el, f"prefill row at position {ctx - Sq + r}, pre-rotated operands")
@@ -219,8 +220,9 @@ def test_million_token_context_g32_decode_and_prefill_rows():
 @pytest.mark.parametrize("S,Skv,w0,G", [(300, 300, 100, 3), (700, 1500, 200, 4), (1, 900, 64, 7), (513, 513, 0, 2)])
 def test_in_kernel_far_remap_matches_the_oracle(S, Skv, w0, G):
     """jl_prefill with remap_far_in_kernel: only base-rotated q / k go in; the far class is rotated per tile in
-    shared memory.  Against the oracle's two-branch composition on exactly regrouped fp32 operands, at positions
-    near 131072 so that the angles are large."""
+    shared memory and rounded to bf16 there, as the pre-rotated operands are.  Against the oracle's two-branch
+    composition on the fp32 regrouping of the same tensors rounded to bf16, at positions near 131072 so that the
+    angles are large."""
     ops = _ops()
     torch.manual_seed(S + G)
     B, H, Hk, D = 1, 4, 2, 128
@@ -235,7 +237,7 @@ def test_in_kernel_far_remap_matches_the_oracle(S, Skv, w0, G):
     assert _status_clean()
     qpos = (torch.arange(S) + P0 + Skv - S).view(1, S)
     kpos = (torch.arange(Skv) + P0).view(1, Skv)
-    qg = orc.rotate_bshd(qb.float().cpu(), orc.regroup_delta(qpos, G), inv)
-    kg = orc.rotate_bshd(kb.float().cpu(), orc.regroup_delta(kpos, G), inv)
+    qg = orc.rotate_bshd(qb.float().cpu(), orc.regroup_delta(qpos, G), inv).bfloat16().float()
+    kg = orc.rotate_bshd(kb.float().cpu(), orc.regroup_delta(kpos, G), inv).bfloat16().float()
     eo, el = orc.jetlong_prefill(qb.float().cpu(), qg, kb.float().cpu(), kg, v.float(), seqstart=Skv - S, w0=w0)
     _check(out, lse, eo, el, f"in-kernel remap S={S} Skv={Skv} w0={w0} G={G}")
