@@ -60,31 +60,43 @@ struct DecSmem {
 // other SMs, so they are read through L2 (ld.cg), never from this SM's L1.
 __device__ __forceinline__ void combine_head_warp(const float* part_o, const float* part_lse, int64_t base, int num_splits,
                                                   int lane, __nv_bfloat16* out_row, float* lse_out) {
+  constexpr int kBatch = 16;               // independent 16-byte loads in flight per lane (the accumulators of the main loop are dead here)
+  const float4* po = reinterpret_cast<const float4*>(part_o) + base * 32 + lane;       // 32 float4 per partial row
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  // the first batch of partial rows needs no weight yet: it travels together with the LSE values
+  float4 x[kBatch];
+#pragma unroll
+  for (int k = 0; k < kBatch; ++k) x[k] = k < num_splits ? __ldcg(po + static_cast<int64_t>(k) * 32) : zero4;
   float m = -INFINITY;
   for (int s = lane; s < num_splits; s += 32) m = fmaxf(m, __ldcg(part_lse + base + s));
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
   const float ms = m == -INFINITY ? 0.f : m;
   float wsum = 0.f;
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  const float4* po = reinterpret_cast<const float4*>(part_o) + base * 32 + lane;       // 32 float4 per partial row
+  float4 acc = zero4;
   for (int s0 = 0; s0 < num_splits; s0 += 32) {
-    // weights of splits s0 .. s0 + 31: lane i holds the weight of split s0 + i
-    const float w_mine = s0 + lane < num_splits ? exp2f((__ldcg(part_lse + base + s0 + lane) - ms) * kLog2e) : 0.f;
     const int n = min(32, num_splits - s0);
-    for (int k0 = 0; k0 < n; k0 += 8) {
-      float4 x[8];
+    if (s0 > 0) {
 #pragma unroll
-      for (int k = 0; k < 8; ++k)            // 8 independent 16-byte loads in flight per lane
-        x[k] = k0 + k < n ? __ldcg(po + static_cast<int64_t>(s0 + k0 + k) * 32) : make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int k = 0; k < kBatch; ++k) x[k] = k < n ? __ldcg(po + static_cast<int64_t>(s0 + k) * 32) : zero4;
+    }
+    // weights of splits s0 .. s0 + 31: lane i holds the weight of split s0 + i (these LSE values were just read: L2 hits)
+    const float w_mine = s0 + lane < num_splits ? exp2f((__ldcg(part_lse + base + s0 + lane) - ms) * kLog2e) : 0.f;
+    for (int k0 = 0; k0 < n; k0 += kBatch) {
+      float4 nx[kBatch];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
+      for (int k = 0; k < kBatch; ++k)     // next batch in flight while this one is folded in
+        nx[k] = k0 + kBatch + k < n ? __ldcg(po + static_cast<int64_t>(s0 + k0 + kBatch + k) * 32) : zero4;
+#pragma unroll
+      for (int k = 0; k < kBatch; ++k) {
         const float w = __shfl_sync(0xffffffffu, w_mine, (k0 + k) & 31);
         const float wk = k0 + k < n ? w : 0.f;
         wsum += wk;
         acc.x = fmaf(wk, x[k].x, acc.x); acc.y = fmaf(wk, x[k].y, acc.y);
         acc.z = fmaf(wk, x[k].z, acc.z); acc.w = fmaf(wk, x[k].w, acc.w);
       }
+#pragma unroll
+      for (int k = 0; k < kBatch; ++k) x[k] = nx[k];
     }
   }
   const float inv = wsum > 0.f ? 1.f / wsum : 0.f;

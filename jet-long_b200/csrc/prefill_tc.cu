@@ -17,6 +17,7 @@
 // Rescaling of O is lazy: it happens only when a row maximum grows by more than 2^8.
 // Every wait is bounded; a wait that gives up sets a status word and lets the kernel drain.
 #include <cuda.h>
+#include <cstdio>
 
 #include "jl_common.cuh"
 
@@ -29,27 +30,14 @@ constexpr int kTileM = 128, kTileN = 128, kRowsPerCta = 256;
 constexpr int kKStages = 3, kVStages = 2;
 constexpr int kTileBytes = 128 * 256;           // 128 rows x 128 bf16
 constexpr int kHalfBytes = 128 * 128;           // one 64-column half (a TMA box)
-#ifndef JL_SPLIT
-#define JL_SPLIT 1
-#endif
-// Softmax threads per query row.  1: one thread owns a row's 128 scores.  2: two threads in two warps of the same
-// TMEM lane quadrant own 64 columns each (they agree on the row maximum through shared memory), which halves
-// the dependent instruction stream between "S ready" and "P published".
-constexpr int kSplit = JL_SPLIT;
-constexpr int kCols = 128 / kSplit;             // score columns per softmax thread
-constexpr int kThreads = 128 + 256 * kSplit;
-#ifndef JL_TWO_PASS
-#define JL_TWO_PASS 0
-#endif
-// Build-time diagnostics for timing experiments only (results are wrong): 1 = exponentials replaced by the
-// identity, 2 = the softmax warps only hand the barriers on, 4 = scores are loaded and their maximum taken, nothing else.
+constexpr int kThreads = 384;
+constexpr int kRegsLow = 72, kRegsHigh = 216;   // per-role register budgets; 128 x 72 + 256 x 216 = the launch total 384 x 168
+// Build-time diagnostics for timing experiments only (results are wrong): 1 = exponentials replaced by the identity,
+// 2 = the softmax warps only hand the barriers on, 4 = scores are loaded and their maximum taken, nothing else,
+// 5 = per-role clock counters of CTA 0 printed, 6 = as 2 and the K / V rings are filled only once, 7 = as 2 without Q K^T.
 #ifndef JL_DIAG
 #define JL_DIAG 0
 #endif
-// 1: the scores are read from tensor memory twice (once for the row maximum, once for the exponentials) instead of
-// being kept in registers in between; for the register budget of two threads per row.
-constexpr bool kTwoPass = JL_TWO_PASS != 0;
-constexpr int kRegsLow = 56, kRegsHigh = kSplit == 1 ? 224 : 104;   // per-role budgets; their weighted sum is the launch total
 #ifndef JL_POLY_MASK
 #define JL_POLY_MASK 0x11
 #endif
@@ -90,7 +78,6 @@ struct Smem {
   uint64_t q_ready, k_ready[kKStages];            // in-kernel remap only: the tile has been rotated (or needs no rotation)
   uint32_t tmem_base;
   int failed;
-  uint16_t xmax[kSplit == 2 ? 2 * 2 * 128 : 4];   // [query tile][column half][row]: bf16 row maxima exchanged by the two threads of a row
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -362,11 +349,23 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
           const int row = (sched.j_lo[ph] + jj) * kTileN;
           const int ks = g % kKStages, vs = g % kVStages;
           mbar_wait(&sm.k_empty[ks], ((g / kKStages) & 1) ^ 1, sm);
+#if JL_DIAG == 6
+          if (g >= kKStages) mbar_arrive(&sm.k_full[ks]); else {      // timing experiment: the ring is filled once, never again
+#endif
           mbar_expect_tx(&sm.k_full[ks], kTileBytes);
           for (int h = 0; h < 2; ++h) tma_load_4d(sm.k[ks] + h * kHalfBytes, km, &sm.k_full[ks], h * 64, kvh, row, b);
+#if JL_DIAG == 6
+          }
+#endif
           mbar_wait(&sm.v_empty[vs], ((g / kVStages) & 1) ^ 1, sm);
+#if JL_DIAG == 6
+          if (g >= kVStages) mbar_arrive(&sm.v_full[vs]); else {
+#endif
           mbar_expect_tx(&sm.v_full[vs], kTileBytes);
           for (int h = 0; h < 2; ++h) tma_load_4d(sm.v[vs] + h * kHalfBytes, &maps.v, &sm.v_full[vs], h * 64, kvh, row, b);
+#if JL_DIAG == 6
+          }
+#endif
         }
       }
     }
@@ -387,14 +386,23 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
         const uint64_t qd = q_desc0 + static_cast<uint64_t>((t * kTileBytes) >> 4);
         const uint64_t kd = k_desc0 + static_cast<uint64_t>((ks * kTileBytes) >> 4);
         if (leader) {
+#if JL_DIAG != 7
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
             const uint64_t off = static_cast<uint64_t>(((kk >> 2) * kHalfBytes + (kk & 3) * 32) >> 4);
             mma_ss(tmem + t * 128, qd + off, kd + off, idesc_qk, kk > 0);
           }
+#endif
           mma_commit(&sm.s_full[t]);
         }
       };
+#if JL_DIAG == 5
+      long long w_p[2][2] = {{0, 0}, {0, 0}}, w_k = 0, w_v = 0;
+      const long long t_begin = clock64();
+#define JL_TIMED(acc, stmt) { const long long t0_ = clock64(); stmt; acc += clock64() - t0_; }
+#else
+#define JL_TIMED(acc, stmt) { stmt; }
+#endif
       int g = 0;           // global tile counter (K/V ring index, barrier parities)
       for (int ph = 0; ph < sched.n_phases; ++ph) {
         uint64_t* const q_bar = p.remap ? &sm.q_ready : &sm.q_full;           // with the in-kernel remap the tiles pass
@@ -419,20 +427,20 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
             // the exponentials of the second half
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-              mbar_wait(&sm.p_half[t][h], g & 1, sm);
-              if (t == 0 && h == 0) mbar_wait(&sm.v_full[vs], (g / kVStages) & 1, sm);
+              JL_TIMED(w_p[t][h], mbar_wait(&sm.p_half[t][h], g & 1, sm));
+              if (t == 0 && h == 0) JL_TIMED(w_v, mbar_wait(&sm.v_full[vs], (g / kVStages) & 1, sm));
               tc_fence_after();
               if (leader) {
 #pragma unroll
                 for (int kk = 4 * h; kk < 4 * h + 4; ++kk)
-                  mma_ts(tmem + 256 + t * 128, tmem + t * 128 + (kSplit == 1 ? kk * 8 : (kk >> 2) * 64 + (kk & 3) * 8), vd + static_cast<uint64_t>((kk * 2048) >> 4), idesc_pv,
+                  mma_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8, vd + static_cast<uint64_t>((kk * 2048) >> 4), idesc_pv,
                          (g > 0 || kk > 0) ? 1u : 0u);
                 if (t == 1 && h == 1) mma_commit(&sm.v_empty[vs]);
               }
             }
             if (more) {
               const int gn = g + 1;
-              if (t == 0) { mbar_wait(&k_bar[gn % kKStages], (gn / kKStages) & 1, sm); tc_fence_after(); }
+              if (t == 0) { JL_TIMED(w_k, mbar_wait(&k_bar[gn % kKStages], (gn / kKStages) & 1, sm)); tc_fence_after(); }
               issue_qk(t, gn);
               if (t == 1 && leader) {
                 if (jj + 2 == n) mma_commit(&sm.q_free);       // last QK^T of this phase issued
@@ -444,6 +452,11 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
       }
       if (leader) mma_commit(&sm.all_done);
       __syncwarp();
+#if JL_DIAG == 5
+      if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && g > 0)
+        printf("mma warp: %d tiles, %lld clk/tile; waits per tile: P00 %lld P01 %lld P10 %lld P11 %lld K %lld V %lld\n", g,
+               (clock64() - t_begin) / g, w_p[0][0] / g, w_p[0][1] / g, w_p[1][0] / g, w_p[1][1] / g, w_k / g, w_v / g);
+#endif
     }
   } else if (p.remap) {
     // =========================== in-kernel remap of the far class ===========================
@@ -504,9 +517,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
   } else {
     // ================================ softmax + epilogue ================================
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsHigh));
-    const int sw = warp - 4;
-    const int t = sw / (4 * kSplit);                        // query tile 0 / 1
-    const int part = (sw >> 2) % kSplit;                    // which kCols-wide slice of the row's scores is mine
+    const int t = (warp - 4) >> 2;                          // query tile 0 / 1
     const int quad = warp & 3;                              // TMEM lane quadrant this warp may access
     const int row_in_tile = quad * 32 + lane;
     const int q_row = q_row0 + t * kTileM + row_in_tile;
@@ -518,14 +529,64 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
     const int64_t pq_t0 = pq_cta0 + t * kTileM;
     const int64_t pq_t1 = pq_t0 + (tile_rows > 0 ? tile_rows - 1 : 0);
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
-    const uint32_t t_s = tmem + lane_base + t * 128 + part * kCols;           // my scores; bf16 P overlays their first half
-    const uint32_t t_o = tmem + lane_base + 256 + t * 128 + part * kCols;     // my columns of the output row
-    const int pair_bar = 1 + t * 4 + quad;                                    // named barrier of the two warps that share rows
-    uint16_t* my_max = &sm.xmax[((t * 2 + part) * 128 + row_in_tile) % (kSplit == 2 ? 512 : 4)];
-    const uint16_t* other_max = &sm.xmax[((t * 2 + (part ^ 1)) * 128 + row_in_tile) % (kSplit == 2 ? 512 : 4)];
+    const uint32_t t_s = tmem + lane_base + t * 128;        // my row of scores; the bf16 P overlays its first 64 columns
+    const uint32_t t_o = tmem + lane_base + 256 + t * 128;  // my row of the output accumulator
+    const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2);
 
     float m_ref = -INFINITY, l_sum = 0.f;
     int g = 0;
+#if JL_DIAG == 5
+    long long d_wait = 0, d_h0 = 0, d_h1 = 0;
+#endif
+    // 32 scores s[e0 .. e0 + 31] -> 16 packed bf16 probability pairs at columns col .. col + 15 of the P region,
+    // their sum added to acc2, and (kMax) their maxima folded into m4
+    auto exp_block = [&](const uint32_t (&s)[128], int e0, uint64_t negm2, uint32_t col, uint64_t (&acc2)[4]) {
+      uint32_t pk[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int e = e0 + 2 * i;
+        const uint64_t x = fma2(pack2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), scale2, negm2);
+#if JL_DIAG == 1
+        const uint64_t pp = x;
+#else
+        const uint64_t pp = ((kPolyMask >> (i & 7)) & 1u) ? exp2_pair_fma(x) : exp2_pair_sfu(x);
+#endif
+        acc2[i & 3] = add2(acc2[i & 3], pp);
+        float p0, p1;
+        unpack2(pp, p0, p1);
+        pk[i] = pack_bf16x2(p0, p1);
+      }
+      JL_TMEM_ST16(t_s + col, pk, 0);
+    };
+    auto max_block = [&](const uint32_t (&s)[128], int e0, float (&m4)[4]) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) m4[i & 3] = max3(m4[i & 3], __uint_as_float(s[e0 + 2 * i]), __uint_as_float(s[e0 + 2 * i + 1]));
+    };
+    auto publish = [&](int half) {
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&sm.p_half[t][half]);
+    };
+    // the row maximum grew by more than 2^8 for some row of the warp: new reference, O and the row sum follow
+    auto raise_reference = [&](float mx, bool rescale_o) {
+      const float m_new = fmaxf(m_ref, mx);
+      const float alpha = m_new == -INFINITY ? 1.f : fast_exp2(m_ref - m_new);
+      l_sum *= alpha;
+      if (rescale_o) {
+        // O_t is quiescent here: S_t(g) ready implies P_t V(g-1) retired, and P_t V(g) waits for our P
+#pragma unroll
+        for (int cchunk = 0; cchunk < 4; ++cchunk) {
+          uint32_t o[32];
+          JL_TMEM_LD32(t_o + cchunk * 32, o, 0);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          JL_TMEM_ST32(t_o + cchunk * 32, o, 0);
+        }
+      }
+      m_ref = m_new;
+    };
+
     for (int ph = 0; ph < sched.n_phases; ++ph) {
       const int c = sched.cls[ph];
       int64_t row_lo, row_hi, tile_lo_max, tile_hi_min, dummy;
@@ -538,129 +599,76 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
         const int valid = min(kTileN, p.sk - j * kTileN);
         const bool uniform = valid == kTileN && tile_lo_max <= tp0 && tile_hi_min >= tp0 + kTileN - 1;
 
+#if JL_DIAG == 5
+        const long long c0 = clock64();
+#endif
         mbar_wait(&sm.s_full[t], g & 1, sm);
         tc_fence_after();
-#if JL_DIAG == 2
+#if JL_DIAG == 5
+        const long long c1 = clock64();
+        d_wait += c1 - c0;
+#endif
+#if JL_DIAG == 2 || JL_DIAG == 6 || JL_DIAG == 7
         tc_fence_before();
         mbar_arrive(&sm.p_half[t][0]);
         mbar_arrive(&sm.p_half[t][1]);
         continue;
 #endif
-        // scores -> registers and row maximum (4 independent chains of 3-input max).  The 32-column
-        // loads are software-pipelined against the reduction: chunk c+1 is in flight while chunk c is reduced.
-        uint32_t s[kCols];
-        float mx;
+        uint32_t s[128];
+        uint64_t acc2[4] = {0ull, 0ull, 0ull, 0ull};
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
         {
-          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+          // scores -> registers and row maximum (4 independent chains of 3-input max)
           if (uniform) {
+            // the 32-column loads are software-pipelined against the reduction: chunk c+1 is in flight while chunk c is reduced
             JL_TMEM_LD32(t_s + 0, s, 0);
 #pragma unroll
-            for (int ch = 0; ch < kCols / 32; ++ch) {
+            for (int ch = 0; ch < 4; ++ch) {
               tmem_wait_ld();
-              if (ch + 1 < kCols / 32) JL_TMEM_LD32(t_s + (ch + 1) * 32, s, (ch + 1) * 32);
-#pragma unroll
-              for (int i = ch * 16; i < ch * 16 + 16; ++i) m4[i & 3] = max3(m4[i & 3], __uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1]));
+              if (ch + 1 < 4) JL_TMEM_LD32(t_s + (ch + 1) * 32, s, (ch + 1) * 32);
+              max_block(s, ch * 32, m4);
             }
           } else {
 #pragma unroll
-            for (int ch = 0; ch < kCols / 32; ++ch) JL_TMEM_LD32(t_s + ch * 32, s, ch * 32);
+            for (int ch = 0; ch < 4; ++ch) JL_TMEM_LD32(t_s + ch * 32, s, ch * 32);
             tmem_wait_ld();
-            const int64_t lo64 = row_lo - tp0 - part * kCols, hi64 = row_hi - tp0 + 1 - part * kCols;
-            const int v_here = min(max(valid - part * kCols, 0), kCols);
-            const int c_lo = lo64 < 0 ? 0 : (lo64 > kCols ? kCols : static_cast<int>(lo64));
-            const int c_hi = hi64 < 0 ? 0 : (hi64 > v_here ? v_here : static_cast<int>(hi64));
+            const int64_t lo64 = row_lo - tp0, hi64 = row_hi - tp0 + 1;
+            const int c_lo = lo64 < 0 ? 0 : (lo64 > 128 ? 128 : static_cast<int>(lo64));
+            const int c_hi = hi64 < 0 ? 0 : (hi64 > valid ? valid : static_cast<int>(hi64));
 #pragma unroll
-            for (int i = 0; i < kCols; ++i)
+            for (int i = 0; i < 128; ++i)
               if (!(i >= c_lo && i < c_hi)) s[i] = 0xff800000u;        // -inf
 #pragma unroll
-            for (int i = 0; i < kCols / 2; ++i) m4[i & 3] = max3(m4[i & 3], __uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1]));
+            for (int ch = 0; ch < 4; ++ch) max_block(s, ch * 32, m4);
           }
-          mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-        }
-        if (kSplit == 2) {
-          // The two threads of a row need ONE reference maximum.  Any common value close to the true maximum
-          // will do (it only keeps the exponentials in range), so each rounds its own to bf16, they swap
-          // the 16-bit values and both take the larger.  One buffer is enough: the partner reads it before it
-          // publishes P, and the next scores, hence my next write, exist only after that P has been consumed.
-          const __nv_bfloat16 mine = __float2bfloat16_rn(mx);
-          *my_max = __bfloat16_as_ushort(mine);
-          asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-          mx = fmaxf(__bfloat162float(mine), __bfloat162float(__ushort_as_bfloat16(*reinterpret_cast<const volatile uint16_t*>(other_max))));
-        }
+          const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;
 #if JL_DIAG == 4
-        l_sum += mx;
-        tc_fence_before();
-        mbar_arrive(&sm.p_half[t][0]);
-        mbar_arrive(&sm.p_half[t][1]);
-        continue;
-#endif
-        mx *= p.scale_log2;                                  // scale > 0: max commutes with the scaling
-        // lazy rescale: only when some row of the warp outgrew its reference maximum by 2^8
-        // (with two threads per row both see the same maxima and take the same decision)
-        const bool grow = mx > m_ref + 8.f;
-        if (__any_sync(0xffffffffu, grow)) {
-          const float m_new = fmaxf(m_ref, mx);
-          const float alpha = m_new == -INFINITY ? 1.f : fast_exp2(m_ref - m_new);
-          l_sum *= alpha;
-          if (g > 0) {
-            // O_t is quiescent here: S_t(g) ready implies P_t V(g-1) retired, and P_t V(g) waits for our P
-#pragma unroll
-            for (int cchunk = 0; cchunk < kCols / 32; ++cchunk) {
-              uint32_t o[32];
-              JL_TMEM_LD32(t_o + cchunk * 32, o, 0);
-              tmem_wait_ld();
-#pragma unroll
-              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-              JL_TMEM_ST32(t_o + cchunk * 32, o, 0);
-            }
-          }
-          m_ref = m_new;
-        }
-        const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-        // p = 2^(s * scale - m): packed FMA, then the exponentials split between the FMA pipe and the SFU (kPolyMask).
-        // Every 64 scores become 32 packed bf16 columns at the start of those 64 score columns and are published
-        // with their own barrier, so the first four k-steps of P V never wait for the last exponentials.
-        const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negm2 = pack2(-m_use, -m_use);
-        uint64_t acc2[4] = {0ull, 0ull, 0ull, 0ull};
-#pragma unroll
-        for (int half = 0; half < kCols / 64; ++half) {
-          // 16 packed columns at a time: with two threads per row the register budget has no room for 32
-#pragma unroll
-          for (int sub = 0; sub < 2; ++sub) {
-            if (kTwoPass) {
-              // second read of this 32-column chunk (the first pass only took its maximum)
-              JL_TMEM_LD32(t_s + half * 64 + sub * 32, s, half * 64 + sub * 32);
-              tmem_wait_ld();
-              if (!uniform) {
-                const int64_t lo64 = row_lo - tp0 - part * kCols, hi64 = row_hi - tp0 + 1 - part * kCols;
-                const int v_here = min(max(valid - part * kCols, 0), kCols);
-                const int c_lo = lo64 < 0 ? 0 : (lo64 > kCols ? kCols : static_cast<int>(lo64));
-                const int c_hi = hi64 < 0 ? 0 : (hi64 > v_here ? v_here : static_cast<int>(hi64));
-#pragma unroll
-                for (int i = half * 64 + sub * 32; i < half * 64 + sub * 32 + 32; ++i)
-                  if (!(i >= c_lo && i < c_hi)) s[i] = 0xff800000u;
-              }
-            }
-            uint32_t pk[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int e = half * 64 + sub * 32 + 2 * i;
-              const uint64_t x = fma2(pack2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), scale2, negm2);
-#if JL_DIAG == 1
-              const uint64_t pp = x;
-#else
-              const uint64_t pp = ((kPolyMask >> (i & 7)) & 1u) ? exp2_pair_fma(x) : exp2_pair_sfu(x);
-#endif
-              acc2[i & 3] = add2(acc2[i & 3], pp);
-              float p0, p1;
-              unpack2(pp, p0, p1);
-              pk[i] = pack_bf16x2(p0, p1);
-            }
-            JL_TMEM_ST16(t_s + (kSplit == 1 ? half * 32 : 0) + sub * 16, pk, 0);
-          }
-          tmem_wait_st();
+          l_sum += mx;
           tc_fence_before();
-          mbar_arrive(&sm.p_half[t][kSplit == 1 ? half : part]);
+          mbar_arrive(&sm.p_half[t][0]);
+          mbar_arrive(&sm.p_half[t][1]);
+          continue;
+#endif
+          // lazy rescale: only when some row of the warp outgrew its reference maximum by 2^8
+          if (__any_sync(0xffffffffu, mx > m_ref + 8.f)) raise_reference(mx, g > 0);
+          const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+          const uint64_t negm2 = pack2(-m_use, -m_use);
+          // p = 2^(s * scale - m): packed FMA, then the exponentials split between the FMA pipe and the SFU (kPolyMask).
+          // The probabilities of keys 0..63 are published first, with their own barrier, so that the first four
+          // k-steps of P V never wait for the last exponentials.
+          exp_block(s, 0, negm2, 0, acc2);
+          exp_block(s, 32, negm2, 16, acc2);
+          publish(0);
+#if JL_DIAG == 5
+          const long long c2 = clock64();
+          d_h0 += c2 - c1;
+#endif
+          exp_block(s, 64, negm2, 32, acc2);
+          exp_block(s, 96, negm2, 48, acc2);
+          publish(1);
+#if JL_DIAG == 5
+          d_h1 += clock64() - c2;
+#endif
         }
         {
           float a0, a1;
@@ -670,23 +678,21 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
       }
     }
 
+#if JL_DIAG == 5
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp & 3) == 0 && g > 0)
+      printf("softmax tile %d: %d tiles; per tile: wait S %lld, S ready -> first half published %lld, -> second half published %lld\n",
+             t, g, d_wait / g, d_h0 / g, d_h1 / g);
+#endif
     // ---- epilogue: O / l -> bf16, LSE ----
     if (sched.total > 0) {
       mbar_wait(&sm.all_done, 0, sm);
       tc_fence_after();
     }
-    if (kSplit == 2) {
-      // row sum = my columns + the partner's; the query tiles in shared memory are dead by now (every MMA has retired)
-      float* sums = reinterpret_cast<float*>(sm.q[0]);
-      sums[(t * 2 + part) * 128 + row_in_tile] = l_sum;
-      asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-      l_sum += *reinterpret_cast<volatile float*>(&sums[(t * 2 + (part ^ 1)) * 128 + row_in_tile]);
-    }
     const bool seen = m_ref != -INFINITY;                 // masked scores add ~1e-38 each to l_sum, never to m_ref
     const float inv = seen ? 1.f / l_sum : 0.f;
-    __nv_bfloat16* orow = p.out + b * p.os_b + static_cast<int64_t>(q_row) * p.os_s + head * p.os_h + part * kCols;
+    __nv_bfloat16* orow = p.out + b * p.os_b + static_cast<int64_t>(q_row) * p.os_s + head * p.os_h;
 #pragma unroll
-    for (int cchunk = 0; cchunk < kCols / 32; ++cchunk) {
+    for (int cchunk = 0; cchunk < 4; ++cchunk) {
       uint32_t o[32];
       if (sched.total > 0) {
         JL_TMEM_LD32(t_o + cchunk * 32, o, 0);
@@ -707,7 +713,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
         }
       }
     }
-    if (row_valid && part == 0 && p.lse != nullptr)
+    if (row_valid && p.lse != nullptr)
       p.lse[(static_cast<int64_t>(b) * p.heads + head) * p.sq + q_row] = seen ? (m_ref + log2f(l_sum)) * kLn2 : -INFINITY;
   }
 
