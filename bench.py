@@ -525,6 +525,18 @@ def extra_configs(peaks, args):
         ms = _time_ms(lambda: ops.posmap_prefill(qo, ko, v, pmap=pm, q_pos0=0, out=o, return_lse=False), iters=3, warm=1)
         maps[name] = dict(ms=round(ms, 2), tflops=round(flops3 / (ms * 1e-3) / 1e12, 1),
                           frac_of_burst_bf16=round(flops3 / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"], 4))
+    # north_star subsystem 1 as worded: the far class remapped inside the kernel, from the base-rotated operands alone
+    pm = ops.PositionMap.jetlong(32768)
+    ms = _time_ms(lambda: ops.posmap_prefill([qb], [kb], v, pmap=pm, q_pos0=0, out=o, return_lse=False, remap_far=(inv, 4)),
+                  iters=2, warm=1)
+    ms_pre = _time_ms(lambda: ops.posmap_prefill([qb, ops.rope_regroup(qb, inv, group_size=4)],
+                                                 [kb, ops.rope_regroup(kb, inv, group_size=4)], v, pmap=pm, q_pos0=0, out=o,
+                                                 return_lse=False), iters=2, warm=1)
+    maps["jetlong_far_class_remapped_in_kernel"] = dict(
+        ms=round(ms, 2), tflops=round(flops3 / (ms * 1e-3) / 1e12, 1),
+        pre_rotated_incl_both_rotate_passes_ms=round(ms_pre, 2),
+        pre_rotated_incl_both_rotate_passes_tflops=round(flops3 / (ms_pre * 1e-3) / 1e12, 1),
+        note="jl_prefill with remap_far_in_kernel against the default form (two jl_rotate passes + jl_prefill); the slower one is not the default")
     out["config3_attention_131072_32x8_heads"] = dict(maps, note="one attention launch per map, kernel timed alone (burst peak); "
                                                       "operands from jl_rotate; parity of these maps at this size: tests/test_full_size_gpu.py")
     del cases, qb, kb, kr
