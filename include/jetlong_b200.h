@@ -183,7 +183,11 @@ typedef struct {
 /* Bytes of workspace jl_decode needs for (batch, heads, head_dim) with at most max_splits splits
  * (max_splits <= 0: the library's own upper bound for automatic splitting). */
 size_t jl_decode_workspace_bytes(int32_t batch, int32_t heads, int32_t head_dim, int32_t max_splits);
-/* Number of splits jl_decode would pick for num_splits <= 0. */
+/* Number of splits jl_decode would pick for num_splits <= 0 when no segment rotates.  A call that regroups far keys
+ * in-kernel (a segment with rotate != 0) with kv_heads a multiple of 8 and at most 8 query heads per kv head runs on a
+ * differently gridded kernel (one CTA per key range over eight kv heads, which forms every rotation angle once instead
+ * of once per kv head) and picks up to 148 / (batch * kv_heads / 8) splits: size a workspace that must serve both with
+ * jl_decode_workspace_bytes(..., max_splits <= 0). */
 int32_t jl_decode_auto_splits(int32_t batch, int32_t kv_heads, int64_t total_keys);
 int jl_decode(const jl_decode_args* args, void* cuda_stream);
 

@@ -395,6 +395,288 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2) decode_kernel(const DecPara
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same decode for calls that regroup far keys inside the kernel, re-gridded so that the rotation
+// angles are formed once per key instead of once per key and kv head.
+//
+// The angle (floor(p / G) - p) * inv_freq[d] of a far key depends on its position and the frequency, not on
+// the head.  Here one CTA owns a key range for EIGHT kv heads of a batch row: grid (split, kv_heads / 8,
+// batch), 8 warps, warp w streams the keys of kv head 8 * blockIdx.y + w through its own 3-stage cp.async
+// pipeline, 16 keys per step, all warps on the same 16 keys.  The 256 threads form the (sin, cos) of the NEXT
+// step's 16 keys x 64 frequencies together (4 per thread instead of 32) into a double-buffered table in
+// shared memory; one CTA barrier per step orders the table hand-over.  Every warp owns its head's whole key
+// range, so there is no cross-warp merge; the splits are merged by decode_combine_kernel.
+// ---------------------------------------------------------------------------------------------
+constexpr int kWideWarps = 8;                // kv heads per CTA
+constexpr int kWideTile = 16;                // keys per step
+constexpr int kWideMaxSplits = 148;          // one CTA per SM
+constexpr int kWideScRow = 72;               // float2 per table row: 64 used, padded so that 8 lanes x 16 B never share a bank
+
+struct WideSmem {
+  uint8_t kv[kWideWarps][kDecStages][2][kWideTile * 256];      // [warp][stage][K/V][16 rows x 256 B]
+  uint8_t q[kWideWarps][8 * 256];                              // the (<= 8) query rows of the class in use, per kv head
+  float2 sc[2][kWideTile][kWideScRow];                         // (sin, cos) per key and frequency of the current / next step
+  float inv_freq[64];
+};
+
+__device__ __forceinline__ void ldmatrix_x2(uint32_t& r0, uint32_t& r1, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+
+__global__ void __launch_bounds__(kWideWarps * 32, 1) decode_wide_kernel(const DecParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  WideSmem& sm = *reinterpret_cast<WideSmem*>(smem_raw);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int split = blockIdx.x, kvh = blockIdx.y * kWideWarps + warp, b = blockIdx.z;
+  const int rep = p.heads / p.kv_heads;            // query heads per kv head (<= 8 here)
+
+  // ---- this CTA's key range in the virtual concatenation of the segments (as in decode_kernel, 16-key steps) ----
+  int seg_len[JL_MAX_SEGMENTS];
+  int64_t seg_row0[JL_MAX_SEGMENTS];
+  int64_t total = 0;
+#pragma unroll
+  for (int s = 0; s < JL_MAX_SEGMENTS; ++s) {
+    int len = 0;
+    int64_t r0 = 0;
+    if (s < p.n_seg) {
+      len = p.seg[s].len;
+      if (p.seg[s].len_dev != nullptr) len = min(len, max(p.seg[s].len_dev[b], 0));
+      if (p.seg[s].row0_dev != nullptr) {
+        r0 = min(max(*p.seg[s].row0_dev, static_cast<int64_t>(0)), static_cast<int64_t>(p.seg[s].len));
+        len = min(len, static_cast<int>(p.seg[s].len - r0));
+      }
+    }
+    seg_len[s] = len;
+    seg_row0[s] = r0;
+    total += len;
+  }
+  int64_t per = (total + p.num_splits - 1) / p.num_splits;
+  per = (per + kWideTile - 1) / kWideTile * kWideTile;
+  const int64_t range_lo = min(static_cast<int64_t>(split) * per, total);
+  const int64_t range_hi = min(range_lo + per, total);
+  int seg_lo[JL_MAX_SEGMENTS], seg_tiles[JL_MAX_SEGMENTS], seg_hi[JL_MAX_SEGMENTS];
+  int n_tiles = 0;
+  {
+    int64_t base = 0;
+#pragma unroll
+    for (int s = 0; s < JL_MAX_SEGMENTS; ++s) {
+      const int64_t lo = max(range_lo, base) - base, hi = min(range_hi, base + seg_len[s]) - base;
+      seg_lo[s] = static_cast<int>(lo);
+      seg_hi[s] = static_cast<int>(hi);
+      seg_tiles[s] = hi > lo ? static_cast<int>((hi - lo + kWideTile - 1) / kWideTile) : 0;
+      n_tiles += seg_tiles[s];
+      base += seg_len[s];
+    }
+  }
+  auto locate = [&](int t, int& s_out, int& row0, int& valid) {
+    int s = 0;
+#pragma unroll
+    for (int i = 0; i < JL_MAX_SEGMENTS - 1; ++i)
+      if (s == i && t >= seg_tiles[i]) { t -= seg_tiles[i]; s = i + 1; }
+    s_out = s;
+    row0 = seg_lo[s] + t * kWideTile;
+    valid = min(kWideTile, seg_hi[s] - row0);
+  };
+  auto shift_of = [&](int s) {
+    int64_t r0 = seg_row0[0];
+#pragma unroll
+    for (int i = 1; i < JL_MAX_SEGMENTS; ++i) r0 = s == i ? seg_row0[i] : r0;
+    return r0;
+  };
+
+  // the warp copies the 16 rows of a step for ITS kv head: lane -> (row = lane/16 + 2*j, chunk = lane%16)
+  auto issue = [&](int t) {
+    if (t < n_tiles) {
+      int s, row0, valid;
+      locate(t, s, row0, valid);
+      const DecSeg& sg = p.seg[s];
+      const int64_t shift = shift_of(s);
+      const int stage = t % kDecStages;
+      const __nv_bfloat16* kb = sg.k + b * sg.ks_b + kvh * sg.ks_h;
+      const __nv_bfloat16* vb = sg.v + b * sg.vs_b + kvh * sg.vs_h;
+      const uint32_t ks = smem_u32(sm.kv[warp][stage][0]), vs = smem_u32(sm.kv[warp][stage][1]);
+      const int chunk = lane & 15;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int r = (lane >> 4) + 2 * j;
+        const bool ok = r < valid;
+        const int64_t grow = shift + (ok ? row0 + r : row0);      // keep the address in range when zero-filling
+        cp_async_16(ks + swz256(r, chunk), kb + grow * sg.ks_s + chunk * 8, ok);
+        cp_async_16(vs + swz256(r, chunk), vb + grow * sg.vs_s + chunk * 8, ok);
+      }
+    }
+    cp_async_commit();
+  };
+  // all 256 threads: (sin, cos) of step t's 16 keys x 64 frequencies -> sc[t & 1] (only for a rotating segment)
+  auto fill_table = [&](int t) {
+    if (t >= n_tiles) return;
+    int s, row0, valid;
+    locate(t, s, row0, valid);
+    const DecSeg& sg = p.seg[s];
+    if (!sg.rotate) return;
+    const int64_t first = shift_of(s) + row0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int e = threadIdx.x + 256 * k, key = e >> 6, d = e & 63;
+      const int64_t pos = key_position(first + key, sg.pos0, sg.pos_block, sg.pos_block_stride);
+      const float tf = static_cast<float>(pos / p.group_size - pos);
+      float sn, cs;
+      sincos_reduced(__fmul_rn(tf, sm.inv_freq[d]), &sn, &cs);
+      sm.sc[t & 1][key][d] = make_float2(sn, cs);
+    }
+  };
+
+  float o[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  float m_run = -INFINITY, l_run = 0.f;             // rows 0..7 of the packed query heads (rows 8..15 are padding)
+
+#pragma unroll
+  for (int t = 0; t < kDecStages - 1; ++t) issue(t);
+  if (threadIdx.x < 64) sm.inv_freq[threadIdx.x] = p.inv_freq != nullptr ? p.inv_freq[threadIdx.x] : 0.f;
+  __syncthreads();
+  fill_table(0);
+  int q_loaded = -1;
+
+  for (int t = 0; t < n_tiles; ++t) {
+    __syncthreads();               // table t is complete; nobody still reads the buffer table t + 1 goes to
+    fill_table(t + 1);
+    cp_async_wait<kDecStages - 2>();
+    __syncwarp();
+    issue(t + kDecStages - 1);     // refills the stage consumed in the previous iteration (warp-private)
+
+    int s, row0, valid;
+    locate(t, s, row0, valid);
+    const DecSeg& sg = p.seg[s];
+    if (sg.q_class != q_loaded) {  // the query rows of this segment's class, for this warp's kv head (warp-private tile)
+      __syncwarp();
+      for (int i = lane; i < 8 * 16; i += 32) {
+        const int row = i >> 4, chunk = i & 15;
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if (row < rep) val = *reinterpret_cast<const uint4*>(p.q[sg.q_class] + b * p.qs_b + (kvh * rep + row) * p.qs_h + chunk * 8);
+        *reinterpret_cast<uint4*>(&sm.q[warp][swz256(row, chunk)]) = val;
+      }
+      q_loaded = sg.q_class;
+      __syncwarp();
+    }
+    const int stage = t % kDecStages;
+    const uint32_t ks = smem_u32(sm.kv[warp][stage][0]), vs = smem_u32(sm.kv[warp][stage][1]);
+    const uint32_t qs = smem_u32(sm.q[warp]);
+
+    // ---- K fragments of the 16 keys: kf[kk] = {nblk0 k-lo, nblk0 k-hi, nblk1 k-lo, nblk1 k-hi} ----
+    uint32_t kf[8][4];
+    {
+      const int r = (lane & 7) + ((lane >> 4) << 3);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) ldmatrix_x4(kf[kk], ks + swz256(r, 2 * kk + ((lane >> 3) & 1)));
+    }
+    if (sg.rotate) {
+      // element (key n, dim d) of kf[kk][i]: n = 8*(i/2) + lane/4, d = 16*kk + 8*(i%2) + 2*(lane%4) + {0,1};
+      // its rotation partner d + 64 sits in kf[kk + 4][i].  (sin, cos) of (n, d) and (n, d + 1): one 16-byte read.
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const float2* row = sm.sc[t & 1][half * 8 + (lane >> 2)];
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int i = half * 2 + e;
+            const int d = 16 * kk + 8 * e + 2 * (lane & 3);
+            const float4 t4 = *reinterpret_cast<const float4*>(row + d);      // sin d, cos d, sin d+1, cos d+1
+            const float2 lo = unpack_bf16x2(kf[kk][i]), hi = unpack_bf16x2(kf[kk + 4][i]);
+            kf[kk][i] = pack_bf16x2(lo.x * t4.y - hi.x * t4.x, lo.y * t4.w - hi.y * t4.z);
+            kf[kk + 4][i] = pack_bf16x2(hi.x * t4.y + lo.x * t4.x, hi.y * t4.w + lo.y * t4.z);
+          }
+        }
+      }
+    }
+
+    // ---- S = Q K^T for 8 (packed head) rows x 16 keys; rows 8..15 of the A fragment are zero ----
+    float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      uint32_t a[4] = {0u, 0u, 0u, 0u};
+      ldmatrix_x2(a[0], a[2], qs + swz256(lane & 7, 2 * kk + ((lane >> 3) & 1)));
+      mma_bf16_16816(sc[0], a, kf[kk][0], kf[kk][1]);
+      mma_bf16_16816(sc[1], a, kf[kk][2], kf[kk][3]);
+    }
+
+    // ---- online softmax (base 2); the thread holds row lane/4 in regs 0,1 of each n-block ----
+    float mx = -INFINITY;
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int key = nb * 8 + 2 * (lane & 3) + e;
+        const float v = key < valid ? sc[nb][e] * p.scale_log2 : -INFINITY;
+        sc[nb][e] = v;
+        mx = fmaxf(mx, v);
+      }
+    }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m_run, mx);
+    const float m_use = m_new == -INFINITY ? 0.f : m_new;
+    const float alpha = fast_exp2(m_run - m_use);
+    m_run = m_new;
+    float rs = 0.f;
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float pv = fast_exp2(sc[nb][e] - m_use);
+        sc[nb][e] = pv;
+        rs += pv;
+      }
+    }
+    rs += __shfl_xor_sync(0xffffffffu, rs, 1);
+    rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+    l_run = l_run * alpha + rs;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) { o[i][0] *= alpha; o[i][1] *= alpha; }
+
+    // ---- O += P V (rows 8..15 of P are zero) ----
+    uint32_t pa[4];
+    pa[0] = pack_bf16x2(sc[0][0], sc[0][1]);
+    pa[1] = 0u;
+    pa[2] = pack_bf16x2(sc[1][0], sc[1][1]);
+    pa[3] = 0u;
+    {
+      const int r = (lane & 7) + (((lane >> 3) & 1) << 3);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        uint32_t vf[4];
+        ldmatrix_x4_trans(vf, vs + swz256(r, 2 * j + (lane >> 4)));
+        mma_bf16_16816(o[2 * j], pa, vf[0], vf[1]);
+        mma_bf16_16816(o[2 * j + 1], pa, vf[2], vf[3]);
+      }
+    }
+  }
+  cp_async_wait<0>();
+
+  // ---- one normalised fp32 partial (O, LSE) per query head of this warp's kv head ----
+  const int g = lane >> 2, tq = lane & 3;
+  if (g < rep) {
+    const int head = kvh * rep + g;
+    const int64_t pidx = (static_cast<int64_t>(b) * p.heads + head) * p.num_splits + split;
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      *reinterpret_cast<float2*>(p.part_o + pidx * 128 + i * 8 + 2 * tq) = make_float2(o[i][0] * inv, o[i][1] * inv);
+    if (tq == 0) p.part_lse[pidx] = l_run > 0.f ? ((m_run == -INFINITY ? 0.f : m_run) + log2f(l_run)) * kLn2 : -INFINITY;
+  }
+}
+
+// Merges the splits of the wide kernel: one warp per (batch, head).
+__global__ void __launch_bounds__(128) decode_combine_kernel(const DecParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.x * 4 + warp, b = blockIdx.y;
+  if (head >= p.heads) return;
+  const int64_t bh = static_cast<int64_t>(b) * p.heads + head;
+  combine_head_warp(p.part_o, p.part_lse, bh * p.num_splits, p.num_splits, lane, p.out + b * p.os_b + head * p.os_h,
+                    p.lse_out != nullptr ? p.lse_out + bh : nullptr);
+}
+
 int32_t decode_auto_splits(int32_t batch, int32_t kv_heads, int64_t total_keys) {
   const int64_t ctas = static_cast<int64_t>(batch > 0 ? batch : 1) * (kv_heads > 0 ? kv_heads : 1);
   int64_t s = kDecMaxSplits / ctas;
@@ -408,6 +690,30 @@ size_t decode_workspace_bytes(int32_t batch, int32_t heads, int32_t head_dim, in
   if (batch <= 0 || heads <= 0 || head_dim <= 0) return 0;
   const size_t splits = max_splits > 0 ? static_cast<size_t>(max_splits) : static_cast<size_t>(kDecMaxSplits);
   return kDecCounterBytes + static_cast<size_t>(batch) * heads * splits * (static_cast<size_t>(head_dim) + 1) * sizeof(float);
+}
+
+// Calls that regroup far keys in-kernel go to the kernel that forms each rotation angle once for eight kv heads.
+static bool decode_uses_wide_kernel(const jl_decode_args* a) {
+  if (a->kv_heads <= 0 || a->kv_heads % kWideWarps != 0 || a->heads % a->kv_heads != 0 || a->heads / a->kv_heads > 8) return false;
+  for (int s = 0; s < a->n_segments && s < JL_MAX_SEGMENTS; ++s)
+    if (a->seg[s].rotate != 0 && a->seg[s].len > 0) return true;
+  return false;
+}
+
+// The split count of a call (the caller's, or enough CTAs to fill the GPU), never more than there are key tiles.
+static int decode_plan_splits(const jl_decode_args* a, int64_t total, bool wide) {
+  int64_t splits, tiles;
+  if (wide) {
+    const int64_t ctas = static_cast<int64_t>(a->batch) * (a->kv_heads / kWideWarps);
+    splits = a->num_splits > 0 ? a->num_splits : kWideMaxSplits / (ctas > 0 ? ctas : 1);
+    tiles = (total + kWideTile - 1) / kWideTile;
+  } else {
+    splits = a->num_splits > 0 ? a->num_splits : decode_auto_splits(a->batch, a->kv_heads, total);
+    tiles = (total + kDecTile - 1) / kDecTile;
+  }
+  if (splits > tiles) splits = tiles;
+  if (splits > kDecMaxSplits) splits = kDecMaxSplits;
+  return static_cast<int>(splits > 0 ? splits : 1);
 }
 
 int launch_decode(const jl_decode_args* a, cudaStream_t stream) {
@@ -459,9 +765,8 @@ int launch_decode(const jl_decode_args* a, cudaStream_t stream) {
   }
   if (any_rotate && (a->inv_freq == nullptr || a->group_size < 1))
     return fail(JL_ERR_BAD_ARG, "jl_decode: rotating segments need inv_freq and group_size >= 1");
-  int splits = a->num_splits > 0 ? a->num_splits : decode_auto_splits(a->batch, a->kv_heads, total);
-  const int64_t tiles = (total + kDecTile - 1) / kDecTile;
-  if (splits > tiles) splits = static_cast<int>(tiles > 0 ? tiles : 1);
+  const bool wide = decode_uses_wide_kernel(a);
+  const int splits = decode_plan_splits(a, total, wide);
   const size_t need = decode_workspace_bytes(a->batch, a->heads, a->head_dim, splits);
   if (a->workspace == nullptr || a->workspace_bytes < need)
     return fail(JL_ERR_WORKSPACE, "jl_decode: workspace of %zu bytes needed, %zu given", need, a->workspace_bytes);
@@ -481,16 +786,25 @@ int launch_decode(const jl_decode_args* a, cudaStream_t stream) {
 
   // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute
   static bool attr_set[64] = {false};
-  const int smem = static_cast<int>(sizeof(DecSmem));
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(JL_ERR_LAUNCH, "jl_decode: no current CUDA device");
   if (!attr_set[dev]) {
-    if (cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(DecSmem))) != cudaSuccess ||
+        cudaFuncSetAttribute(decode_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(WideSmem))) != cudaSuccess)
       return check_launch("jl_decode (shared memory opt-in)");
     attr_set[dev] = true;
   }
+  if (wide) {
+    dim3 grid(splits, a->kv_heads / kWideWarps, a->batch);
+    decode_wide_kernel<<<grid, kWideWarps * 32, sizeof(WideSmem), stream>>>(p);
+    const int rc = check_launch("jl_decode (shared-angle kernel)");
+    if (rc != JL_OK) return rc;
+    dim3 cgrid((a->heads + 3) / 4, a->batch);
+    decode_combine_kernel<<<cgrid, 128, 0, stream>>>(p);
+    return check_launch("jl_decode (combine)");
+  }
   dim3 grid(splits, a->kv_heads, a->batch);
-  decode_kernel<<<grid, kDecWarps * 32, smem, stream>>>(p);
+  decode_kernel<<<grid, kDecWarps * 32, sizeof(DecSmem), stream>>>(p);
   return check_launch("jl_decode");
 }
 
@@ -526,9 +840,7 @@ int launch_decode_static(const jl_decode_args* a, cudaStream_t stream) {
     return fail(JL_ERR_BAD_ARG, "jl_decode_static: batch/heads/kv_heads/n_segments out of range");
   int64_t total = 0;
   for (int s = 0; s < a->n_segments; ++s) total += a->seg[s].len > 0 ? a->seg[s].len : 0;
-  int splits = a->num_splits > 0 ? a->num_splits : decode_auto_splits(a->batch, a->kv_heads, total);
-  const int64_t tiles = (total + kDecTile - 1) / kDecTile;
-  if (splits > tiles) splits = static_cast<int>(tiles > 0 ? tiles : 1);
+  const int splits = decode_plan_splits(a, total, decode_uses_wide_kernel(a));
   const size_t need = decode_workspace_bytes(a->batch, a->heads, a->head_dim, splits);
   if (need > kStaticScratchBytes)
     return fail(JL_ERR_WORKSPACE,

@@ -554,8 +554,8 @@ def decode_segments(q_ops: Sequence[Optional[torch.Tensor]], segments: Sequence[
     a.lse = lse.data_ptr() if lse is not None else None
     a.o_stride_b, a.o_stride_h = _st(out, 0), _st(out, 2)
     lib = N.lib()
-    splits = num_splits if num_splits > 0 else lib.jl_decode_auto_splits(B, Hk, total)
-    need = lib.jl_decode_workspace_bytes(B, H, D, splits)
+    # the library picks the split count (and the kernel) itself: size the scratch for its upper bound unless told
+    need = lib.jl_decode_workspace_bytes(B, H, D, int(num_splits) if num_splits > 0 else 0)
     ws = workspace if workspace is not None else _workspace(q0.device, need)
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel() * ws.element_size()
     with torch.cuda.device(q0.device):
