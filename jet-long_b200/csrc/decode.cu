@@ -507,23 +507,31 @@ __global__ void __launch_bounds__(kWideWarps * 32, 1) decode_wide_kernel(const D
     }
     cp_async_commit();
   };
-  // all 256 threads: (sin, cos) of step t's 16 keys x 64 frequencies -> sc[t & 1] (only for a rotating segment)
-  auto fill_table = [&](int t) {
-    if (t >= n_tiles) return;
+  // All 256 threads: (sin, cos) of step t's 16 keys x 64 frequencies (only for a rotating segment).  Thread -> one key
+  // and four consecutive frequencies, so one position and one division by G per thread.  The values are formed in
+  // registers BEFORE the step's barrier (the wait for the slowest warp hides their latency) and stored after it.
+  const int tab_key = threadIdx.x >> 4, tab_d0 = (threadIdx.x & 15) * 4;
+  auto table_values = [&](int t, float4& a, float4& b2) -> bool {
+    if (t >= n_tiles) return false;
     int s, row0, valid;
     locate(t, s, row0, valid);
     const DecSeg& sg = p.seg[s];
-    if (!sg.rotate) return;
-    const int64_t first = shift_of(s) + row0;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const int e = threadIdx.x + 256 * k, key = e >> 6, d = e & 63;
-      const int64_t pos = key_position(first + key, sg.pos0, sg.pos_block, sg.pos_block_stride);
-      const float tf = static_cast<float>(pos / p.group_size - pos);
-      float sn, cs;
-      sincos_reduced(__fmul_rn(tf, sm.inv_freq[d]), &sn, &cs);
-      sm.sc[t & 1][key][d] = make_float2(sn, cs);
-    }
+    if (!sg.rotate) return false;
+    const int64_t pos = key_position(shift_of(s) + row0 + tab_key, sg.pos0, sg.pos_block, sg.pos_block_stride);
+    const int64_t grouped = (pos >= 0 && pos < (int64_t(1) << 31))
+                                ? static_cast<int64_t>(static_cast<uint32_t>(pos) / static_cast<uint32_t>(p.group_size))
+                                : pos / p.group_size;
+    const float tf = static_cast<float>(grouped - pos);
+    sincos_reduced(__fmul_rn(tf, sm.inv_freq[tab_d0 + 0]), &a.x, &a.y);
+    sincos_reduced(__fmul_rn(tf, sm.inv_freq[tab_d0 + 1]), &a.z, &a.w);
+    sincos_reduced(__fmul_rn(tf, sm.inv_freq[tab_d0 + 2]), &b2.x, &b2.y);
+    sincos_reduced(__fmul_rn(tf, sm.inv_freq[tab_d0 + 3]), &b2.z, &b2.w);
+    return true;
+  };
+  auto table_store = [&](int t, const float4& a, const float4& b2) {
+    float4* dst = reinterpret_cast<float4*>(&sm.sc[t & 1][tab_key][tab_d0]);
+    dst[0] = a;
+    dst[1] = b2;
   };
 
   float o[16][4];
@@ -535,12 +543,17 @@ __global__ void __launch_bounds__(kWideWarps * 32, 1) decode_wide_kernel(const D
   for (int t = 0; t < kDecStages - 1; ++t) issue(t);
   if (threadIdx.x < 64) sm.inv_freq[threadIdx.x] = p.inv_freq != nullptr ? p.inv_freq[threadIdx.x] : 0.f;
   __syncthreads();
-  fill_table(0);
+  {
+    float4 a, b2;
+    if (table_values(0, a, b2)) table_store(0, a, b2);
+  }
   int q_loaded = -1;
 
   for (int t = 0; t < n_tiles; ++t) {
+    float4 tab_a, tab_b;
+    const bool tab_next = table_values(t + 1, tab_a, tab_b);
     __syncthreads();               // table t is complete; nobody still reads the buffer table t + 1 goes to
-    fill_table(t + 1);
+    if (tab_next) table_store(t + 1, tab_a, tab_b);
     cp_async_wait<kDecStages - 2>();
     __syncwarp();
     issue(t + kDecStages - 1);     // refills the stage consumed in the previous iteration (warp-private)

@@ -407,6 +407,39 @@ def test_decode_kv_shards_merge():
     _check(out, lse, eo, el, "sharded decode + merge")
 
 
+@pytest.mark.parametrize("B,H,Hk,near,far,splits,blk", [(1, 32, 8, 300, 1000, 0, 0), (2, 16, 8, 17, 513, 5, 0), (1, 64, 16, 129, 2050, 0, 0),
+                                                       (3, 8, 8, 1, 95, 1, 0), (1, 32, 8, 700, 4096, 0, 256)])
+def test_decode_in_kernel_regroup_shared_angle_kernel(B, H, Hk, near, far, splits, blk):
+    """kv_heads a multiple of 8 and a rotating segment: the call runs on the kernel that forms every rotation angle
+    once for eight kv heads (one CTA per key range, one warp per kv head).  Ragged lengths, several split counts,
+    per-sequence lengths on the far segment, and a block-cyclic stripe (positions p0 + (row // blk) * 4 * blk + row % blk)."""
+    ops = _ops()
+    torch.manual_seed(B * 1000 + far)
+    D, G = 128, 5
+    inv = orc.default_inv_freq()
+    qb, qg = torch.randn(B, 1, H, D).bfloat16(), torch.randn(B, 1, H, D).bfloat16()
+    ctx = near + far
+    kc = torch.randn(B, Hk, ctx, D).bfloat16().transpose(1, 2)          # (B,S,Hk,D) view of a (B,Hk,S,D) cache
+    vc = torch.randn(B, Hk, ctx, D).bfloat16().transpose(1, 2)
+    rows = torch.arange(far)
+    pos = (1000 + (rows // blk) * 4 * blk + rows % blk) if blk else 1000 + rows
+    geo = dict(pos0=1000, pos_block=blk, pos_block_stride=4 * blk) if blk else dict(pos0=1000)
+    kfar = orc.rotate_bshd(kc[:, :far].float(), orc.regroup_delta(pos.view(1, -1).expand(B, -1), G), inv)
+    eo, el = orc.jetlong_decode(qb, qg, kc[:, far:], vc[:, far:], kfar, vc[:, :far])
+    dk, dv = kc.cuda(), vc.cuda()
+    segs = [ops.KvSegment(dk[:, :far], dv[:, :far], 1, rotate=True, **geo), ops.KvSegment(dk[:, far:], dv[:, far:], 0)]
+    out, lse = ops.decode_segments(_dev(qb, qg), segs, inv_freq=inv.cuda(), group_size=G, num_splits=splits)
+    _check(out, lse, eo, el, f"shared-angle decode B={B} H={H}/{Hk} near={near} far={far} splits={splits} blk={blk}")
+    if B > 1:          # per-sequence lengths: sequence 0 only sees the first far // 3 far keys
+        lens = torch.full((B,), far, dtype=torch.int32)
+        lens[0] = far // 3
+        segs[0].len_dev = lens.cuda()
+        out, lse = ops.decode_segments(_dev(qb, qg), segs, inv_freq=inv.cuda(), group_size=G, num_splits=splits)
+        n0 = far // 3
+        eo0, el0 = orc.jetlong_decode(qb[:1], qg[:1], kc[:1, far:], vc[:1, far:], kfar[:1, :n0], vc[:1, :n0])
+        _check(out[:1], lse[:1], eo0, el0, "shared-angle decode with device lengths")
+
+
 # ------------------------------------------------------------------------------------------------
 # backend entry points on the tensors the unmodified reference modeling file produced
 # ------------------------------------------------------------------------------------------------

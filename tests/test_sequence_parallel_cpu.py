@@ -122,3 +122,20 @@ def test_stripe_geometry_partitions_the_keys():
             ranges = [SequenceShard(r, world).contiguous_range(n_keys) for r in range(world)]
             assert ranges[0][0] == 0 and ranges[-1][1] == n_keys
             assert all(ranges[i][1] == ranges[i + 1][0] for i in range(world - 1))
+
+
+def test_token_sharded_prefill_picks_the_smaller_exchange(monkeypatch):
+    """K/V gather while the cache is at most H/Hk times longer than the chunk (its bytes are then the smaller ones),
+    Q exchange for the late chunks of a long chunked prefill; the environment variable overrides."""
+    sys.path[:0] = [PKG]
+    from jetlm.kernels.cute_jetlong_backend import token_sharded_prefill_mode as mode
+    monkeypatch.delenv("JETLONG_SP_PREFILL", raising=False)
+    assert mode(8, 131072, 131072, 32, 8) == "kv_gather"            # a fresh prompt
+    assert mode(8, 4 * 32768, 32768, 32, 8) == "kv_gather"          # cache = 4 chunks at 32 / 8 heads: the break-even
+    assert mode(8, 5 * 32768, 32768, 32, 8) == "q_exchange"
+    assert mode(8, 1048576, 32768, 32, 8) == "q_exchange"           # the last chunk of a 1M-token prompt
+    assert mode(2, 65536, 65536, 16, 16) == "kv_gather"             # no grouped-query advantage, still no return trip
+    monkeypatch.setenv("JETLONG_SP_PREFILL", "q")
+    assert mode(8, 131072, 131072, 32, 8) == "q_exchange"
+    monkeypatch.setenv("JETLONG_SP_PREFILL", "kv")
+    assert mode(8, 1048576, 32768, 32, 8) == "kv_gather"

@@ -9,6 +9,8 @@ import ctypes as C
 import pytest
 import torch
 
+import jetlong_oracle as orc
+
 pytestmark = pytest.mark.gpu
 
 
@@ -60,6 +62,12 @@ def test_static_scratch_decode_matches_workspace_decode_twice_in_a_row():
             assert float((out_st.float() - out_ws.float()).abs().max()) <= 2e-2, (trial, call)
             assert float((lse_st - lse_ws).abs().max()) <= 1e-3, (trial, call)
             assert torch.equal(out_st, out_ws) and torch.equal(lse_st, lse_ws), (trial, call)
+        # and directly against the CPU oracle, at the parity bars of every other kernel test
+        eo, el = orc.jetlong_decode(q[0].cpu(), q[1].cpu(), k[:, boundary:].cpu(), v[:, boundary:].cpu(),
+                                    k[:, :boundary].cpu(), v[:, :boundary].cpu())
+        d, cos = orc.compare(out_st.float().cpu(), eo)
+        dl, _ = orc.compare(lse_st.cpu().view(B, H, 1), el)
+        assert d <= 2e-2 and cos >= 0.9999 and dl <= 1e-3, (trial, d, cos, dl)
 
 
 def test_static_scratch_decode_refuses_requests_beyond_its_array():
