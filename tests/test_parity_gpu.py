@@ -424,7 +424,9 @@ def test_decode_in_kernel_regroup_shared_angle_kernel(B, H, Hk, near, far, split
     rows = torch.arange(far)
     pos = (1000 + (rows // blk) * 4 * blk + rows % blk) if blk else 1000 + rows
     geo = dict(pos0=1000, pos_block=blk, pos_block_stride=4 * blk) if blk else dict(pos0=1000)
-    kfar = orc.rotate_bshd(kc[:, :far].float(), orc.regroup_delta(pos.view(1, -1).expand(B, -1), G), inv)
+    # the kernel rounds the regrouped keys to bf16 before the tensor cores read them, as the reference's own path
+    # does (correction_rotate_per_sample returns bf16); with as few as 32 keys that rounding is visible in the LSE
+    kfar = orc.rotate_bshd(kc[:, :far].float(), orc.regroup_delta(pos.view(1, -1).expand(B, -1), G), inv).bfloat16().float()
     eo, el = orc.jetlong_decode(qb, qg, kc[:, far:], vc[:, far:], kfar, vc[:, :far])
     dk, dv = kc.cuda(), vc.cuda()
     segs = [ops.KvSegment(dk[:, :far], dv[:, :far], 1, rotate=True, **geo), ops.KvSegment(dk[:, far:], dv[:, far:], 0)]
