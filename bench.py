@@ -662,7 +662,7 @@ def long_generate(args, cfg, model, shard, world):
                 kv_rows_per_rank=layer.rows, tokens_in_cache=cache.get_seq_length(),
                 first_tokens=toks[0, :8].tolist(),
                 config=dict(model=args.model, w=args.w, w_0=args.w0, layers=cfg.num_hidden_layers,
-                            cache="preallocated, block-cyclic stripes of 1024 tokens over ranks" if world > 1 else "preallocated"))
+                            cache=f"preallocated, block-cyclic stripes of {SP_BLOCK} tokens over ranks" if world > 1 else "preallocated"))
 
 
 def main():

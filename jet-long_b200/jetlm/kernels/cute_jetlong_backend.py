@@ -80,20 +80,27 @@ def token_sharded_prefill_mode(world: int, n_keys_total: int, n_queries_total: i
     return "kv_gather" if n_keys_total * kv_heads <= n_queries_total * heads else "q_exchange"
 
 
-def _prefill_kv_gather(query_base, key_base, value, *, q_start, inv_freq, group_size, window_size_left, softmax_scale):
-    """Token-sharded prefill by gathering the keys: see token_sharded_prefill_mode.  The ranks' stripes arrive
-    rank-major; one strided copy puts them into position order, the far-class keys are regrouped locally from the
-    gathered base keys (one jl_rotate pass), and ONE jl_prefill launch attends this rank's block-cyclic query
-    stripe to the whole key range."""
+class KvGather:
+    """An all-gather of this rank's K_base / V stripes that is already in flight (token_sharded_kv_gather_begin):
+    the model starts it as soon as the keys and values of a layer exist, so that it runs behind the query projection."""
+
+    def __init__(self, bufs, work, rows):
+        self.bufs, self.work, self.rows = bufs, work, rows
+
+
+def token_sharded_kv_gather_begin(key_base, value) -> KvGather:
+    """Start the K/V gather of the "kv_gather" exchange: key_base / value (B, R, Hk, D) views of this rank's cache
+    stripe.  Returns the handle fused_jetlong_prefill_token_sharded(..., gather=handle) finishes."""
     import torch.distributed as dist
     sh = _SHARD
+    if sh is None:
+        raise RuntimeError("token-sharded prefill needs configure_sequence_sharding(...) first")
     N, blk, me = sh.world, sh.block, sh.rank
-    B, S_loc, H, D = query_base.shape
-    R, Hk = key_base.shape[1], key_base.shape[2]
+    B, R, Hk, D = key_base.shape
     if R % blk != 0:
         raise ValueError(f"token-sharded prefill needs whole blocks per rank: {R} cache rows, block {blk}")
-    dev, dt = query_base.device, query_base.dtype
-    key = ("kvg", me, N, B, S_loc, R, H, Hk, D, dt, dev)
+    dev, dt = key_base.device, key_base.dtype
+    key = ("kvg", me, N, B, R, Hk, D, dt, dev)
     bufs = _BUFFERS.get(key)
     if bufs is None:
         for old in [k for k in _BUFFERS if k[0] == "kvg"]:      # a chunked prefill changes R every call: keep one set
@@ -101,22 +108,39 @@ def _prefill_kv_gather(query_base, key_base, value, *, q_start, inv_freq, group_
         bufs = _BUFFERS[key] = dict(
             stage=torch.empty(N, 2, B, R, Hk, D, dtype=dt, device=dev),        # [rank][K / V] stripes as they arrive
             full=torch.empty(2, B, R * N, Hk, D, dtype=dt, device=dev),        # K_base / V in position order
-            k_grp=torch.empty(B, R * N, Hk, D, dtype=dt, device=dev),
-            q_grp=torch.empty(B, S_loc, H, D, dtype=dt, device=dev))
-    stage, full, k_grp, q_grp = bufs["stage"], bufs["full"], bufs["k_grp"], bufs["q_grp"]
+            k_grp=torch.empty(B, R * N, Hk, D, dtype=dt, device=dev))
+    stage = bufs["stage"]
     stage[me, 0].copy_(key_base)
     stage[me, 1].copy_(value)
-    gather = dist.all_gather_into_tensor(stage.view(-1), stage[me].view(-1), group=sh.group, async_op=True)
+    work = dist.all_gather_into_tensor(stage.view(-1), stage[me].view(-1), group=sh.group, async_op=True)
+    return KvGather(bufs, work, R)
+
+
+def _prefill_kv_gather(query_base, key_base, value, *, q_start, inv_freq, group_size, window_size_left, softmax_scale,
+                       gather=None):
+    """Token-sharded prefill by gathering the keys: see token_sharded_prefill_mode.  The ranks' stripes arrive
+    rank-major; one strided copy puts them into position order, the far-class keys are regrouped locally from the
+    gathered base keys (one jl_rotate pass), and ONE jl_prefill launch attends this rank's block-cyclic query
+    stripe to the whole key range."""
+    sh = _SHARD
+    N, blk, me = sh.world, sh.block, sh.rank
+    B, S_loc, H, D = query_base.shape
+    if gather is None:
+        gather = token_sharded_kv_gather_begin(key_base, value)
+    elif gather.rows != key_base.shape[1]:
+        raise ValueError("the K/V gather handle was started for a different cache length")
+    stage, full, k_grp = gather.bufs["stage"], gather.bufs["full"], gather.bufs["k_grp"]
     stride = N * blk
     regroup = int(group_size) > 1
+    q_grp = query_base
     if regroup:     # the regrouped queries need no remote data: formed while the gather is in flight
-        ops.rope_regroup(query_base, inv_freq, group_size=int(group_size), pos0=int(q_start) + me * blk, pos_block=blk,
-                         pos_block_stride=stride, out=q_grp)
-    gather.wait()
+        q_grp = ops.rope_regroup(query_base, inv_freq, group_size=int(group_size), pos0=int(q_start) + me * blk, pos_block=blk,
+                                 pos_block_stride=stride)
+    gather.work.wait()
     interleave_stripes(stage, blk, full)
     if regroup:
         ops.rope_regroup(full[0], inv_freq, group_size=int(group_size), pos0=0, out=k_grp)
-    return ops.posmap_prefill([query_base, q_grp if regroup else query_base], [full[0], k_grp if regroup else full[0]], full[1],
+    return ops.posmap_prefill([query_base, q_grp], [full[0], k_grp if regroup else full[0]], full[1],
                               pmap=ops.PositionMap.jetlong(int(window_size_left)), q_pos0=int(q_start) + me * blk,
                               q_block=blk, q_block_stride=stride, k_pos0=0, softmax_scale=softmax_scale, return_lse=False)
 
@@ -125,7 +149,8 @@ LAST_TOKEN_SHARDED_MODE = None      # "kv_gather" / "q_exchange": what the most 
 
 
 def fused_jetlong_prefill_token_sharded(query_base, key_base, key_group, value, *, q_start: int, inv_freq,
-                                        group_size: int, window_size_left: int, softmax_scale: float, mode=None):
+                                        group_size: int, window_size_left: int, softmax_scale: float, mode=None,
+                                        gather=None):
     """Bifocal prefill when the TOKENS are sharded block-cyclically over the ranks (every rank ran the
     projections only for its own stripe of the prompt and keeps only its stripe of the KV cache).
 
@@ -133,7 +158,8 @@ def fused_jetlong_prefill_token_sharded(query_base, key_base, key_group, value, 
     q_start + rank*blk + (i // blk) * world*blk + i % blk.  key_base / key_group / value
     (B, Skv_loc, Hk, D) views: this rank's cache stripe (same geometry from position 0); key_group may be
     None (it is only read by the "q_exchange" form, which regroups on demand).
-    mode None picks the cheaper exchange (token_sharded_prefill_mode).  The "q_exchange" form:
+    mode None picks the cheaper exchange (token_sharded_prefill_mode); gather: a K/V gather the caller has already
+    started with token_sharded_kv_gather_begin (kv_gather mode only).  The "q_exchange" form:
     all-gather the base-rotated queries (the regrouped ones are re-derived locally), attend
     every rank's query stripe to the local key stripe, send each partial (O, LSE) to the rank that
     owns those query rows (all-to-all), merge the N partials of the local rows.  Returns (B, S_loc, H, D).
@@ -147,7 +173,7 @@ def fused_jetlong_prefill_token_sharded(query_base, key_base, key_group, value, 
     LAST_TOKEN_SHARDED_MODE = mode
     if mode == "kv_gather":
         return _prefill_kv_gather(query_base, key_base, value, q_start=q_start, inv_freq=inv_freq, group_size=group_size,
-                                  window_size_left=window_size_left, softmax_scale=softmax_scale)
+                                  window_size_left=window_size_left, softmax_scale=softmax_scale, gather=gather)
     if key_group is None:
         key_group = key_base
         if int(group_size) > 1:

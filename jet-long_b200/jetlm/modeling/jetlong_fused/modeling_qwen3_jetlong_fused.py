@@ -151,9 +151,18 @@ class Qwen3JetLongFusedAttention(nn.Module):
         bsz, seq = hidden_states.shape[:2]
         out_shape = (bsz, seq)
         H, Hk, D = self.num_heads, self.num_kv_heads, self.head_dim
-        q = self.q_proj(hidden_states).view(bsz, seq, H, D)          # per-head RMSNorm is applied below
-        k = self.k_proj(hidden_states).view(bsz, seq, Hk, D)
+        k = self.k_proj(hidden_states).view(bsz, seq, Hk, D)         # per-head RMSNorm is applied below
         v = self.v_proj(hidden_states).view(bsz, seq, Hk, D)
+        plan0 = position_embeddings[5] if len(position_embeddings) > 5 else None
+        if plan0 is not None and plan0.step is None and plan0.token_shard is not None and not plan0.replicated:
+            # sequence-parallel prefill: the keys and values go first, so that their exchange between the ranks can
+            # already run behind the query projection
+            from jetlm.kernels import cute_jetlong_backend as backend
+            from jetlm.kernels import jetlong_ops as ops
+            make_q = lambda: self.q_proj(hidden_states).view(bsz, seq, H, D)
+            return self._token_sharded(make_q, k, v, plan0, position_embeddings[2], position_embeddings[3], past_key_values,
+                                       out_shape, backend, ops)
+        q = self.q_proj(hidden_states).view(bsz, seq, H, D)
 
         if len(position_embeddings) < 4:
             return self._within_window(self.q_norm(q), self.k_norm(k), v, position_embeddings, attention_mask,
@@ -349,7 +358,6 @@ class Qwen3JetLongFusedAttention(nn.Module):
 
         geo = dict(pos_block=sh.block, pos_block_stride=sh.world * sh.block)
         pos0 = plan.q_pos0 + sh.rank * sh.block
-        q_base = ops.norm_rope(q, self.q_norm.weight, inv_freq, eps=q_eps, pos0=pos0, **geo)
         if slot is not None:
             k_new, v_dst = slot.reserve(seq * sh.world)
             if k_new.shape[1] != seq:
@@ -367,6 +375,10 @@ class Qwen3JetLongFusedAttention(nn.Module):
         else:
             k_all, v_all = k_new, v
         mode = backend.token_sharded_prefill_mode(sh.world, k_all.shape[1] * sh.world, seq * sh.world, self.num_heads, Hk)
+        gather = backend.token_sharded_kv_gather_begin(k_all, v_all) if mode == "kv_gather" else None
+        if callable(q):                  # prefill: the query projection runs while the K/V gather is in flight
+            q = q()
+        q_base = ops.norm_rope(q, self.q_norm.weight, inv_freq, eps=q_eps, pos0=pos0, **geo)
         k_group = None                   # the K/V-gather form regroups the gathered keys itself
         if mode == "q_exchange":
             if group > 1:
@@ -377,7 +389,8 @@ class Qwen3JetLongFusedAttention(nn.Module):
                 k_group = k_all
         attn = backend.fused_jetlong_prefill_token_sharded(
             q_base, k_all, k_group, v_all, q_start=plan.q_pos0,
-            inv_freq=inv_freq, group_size=group, window_size_left=self.jetlong_w_0, softmax_scale=self.scaling, mode=mode)
+            inv_freq=inv_freq, group_size=group, window_size_left=self.jetlong_w_0, softmax_scale=self.scaling, mode=mode,
+            gather=gather)
         return self.o_proj(attn.reshape(bsz, seq, -1)), None
 
 
