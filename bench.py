@@ -525,6 +525,10 @@ def extra_configs(peaks, args):
         ms = _time_ms(lambda: ops.posmap_prefill(qo, ko, v, pmap=pm, q_pos0=0, out=o, return_lse=False), iters=3, warm=1)
         maps[name] = dict(ms=round(ms, 2), tflops=round(flops3 / (ms * 1e-3) / 1e12, 1),
                           frac_of_burst_bf16=round(flops3 / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"], 4))
+        # the same launch on the CTA-pair kernel (cta_group::2, impl = 2; built, measured, not the default)
+        ms2 = _time_ms(lambda: ops.posmap_prefill(qo, ko, v, pmap=pm, q_pos0=0, out=o, return_lse=False, impl=2), iters=3, warm=1)
+        maps[name]["cta_pair_kernel_ms"] = round(ms2, 2)
+        maps[name]["cta_pair_kernel_tflops"] = round(flops3 / (ms2 * 1e-3) / 1e12, 1)
     # north_star subsystem 1 as worded: the far class remapped inside the kernel, from the base-rotated operands alone
     pm = ops.PositionMap.jetlong(32768)
     ms = _time_ms(lambda: ops.posmap_prefill([qb], [kb], v, pmap=pm, q_pos0=0, out=o, return_lse=False, remap_far=(inv, 4)),

@@ -102,9 +102,12 @@ typedef struct {
   int64_t k_block_stride;
   float softmax_scale;
   jl_posmap map;
-  int32_t impl;             /* 0 = the tcgen05 kernel; 1 = the mma.sync kernel kept as an on-GPU cross-check.  impl 0 refuses
-                               (JL_ERR_UNSUPPORTED, never a silent change of kernel) a k_block that is not a multiple of
-                               128, a q_block that is not a multiple of 256, and more than two distinct key tensors */
+  int32_t impl;             /* 0 = the tcgen05 kernel (one CTA per 256 query rows); 1 = the mma.sync kernel kept as an on-GPU
+                               cross-check; 2 = the tcgen05 CTA-pair kernel (a cluster of two CTAs per 256 query rows,
+                               cta_group::2 MMAs, every K / V tile split between the two), same results as impl 0.
+                               impl 0 and 2 refuse (JL_ERR_UNSUPPORTED, never a silent change of kernel) a k_block that is
+                               not a multiple of 128, a q_block that is not a multiple of 256, and more than two distinct
+                               key tensors; impl 2 also refuses remap_far_in_kernel */
   int64_t q_block;          /* <= 0 means contiguous */
   int64_t q_block_stride;
   /* Far-field positions remapped INSIDE the kernel (band map, impl 0 only): with remap_far_in_kernel != 0 the far

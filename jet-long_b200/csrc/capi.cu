@@ -21,6 +21,8 @@ size_t decode_static_scratch_bytes();
 int launch_prefill_mma(const jl_prefill_args* a, cudaStream_t stream);
 int launch_prefill_tc(const jl_prefill_args* a, cudaStream_t stream);
 const char* prefill_tc_unsupported_reason(const jl_prefill_args* a);
+int launch_prefill_pair(const jl_prefill_args* a, cudaStream_t stream);
+const char* prefill_pair_unsupported_reason(const jl_prefill_args* a);
 int prefill_tc_status();
 int32_t decode_auto_splits(int32_t batch, int32_t kv_heads, int64_t total_keys);
 size_t decode_workspace_bytes(int32_t batch, int32_t heads, int32_t head_dim, int32_t max_splits);
@@ -78,7 +80,7 @@ static int validate_prefill(const jl_prefill_args* a) {
   if ((keys && a->v == nullptr) || a->out == nullptr) return fail(JL_ERR_BAD_ARG, "jl_prefill: v/out is NULL");
   uintptr_t bits = reinterpret_cast<uintptr_t>(a->v) | reinterpret_cast<uintptr_t>(a->out);
   for (int c = 0; c < a->map.n_classes; ++c) {
-    if (c > 0 && a->remap_far_in_kernel && a->impl == 0) continue;      // formed in-kernel from class 0
+    if (c > 0 && a->remap_far_in_kernel && a->impl != 1) continue;      // formed in-kernel from class 0
     if (a->q[c] == nullptr || (keys && a->k[c] == nullptr)) return fail(JL_ERR_BAD_ARG, "jl_prefill: operand of class %d is NULL", c);
     bits |= reinterpret_cast<uintptr_t>(a->q[c]) | reinterpret_cast<uintptr_t>(a->k[c]);
   }
@@ -207,7 +209,12 @@ int jl_prefill(const jl_prefill_args* args, void* cuda_stream) {
     if (args->remap_far_in_kernel) return jl::fail(JL_ERR_UNSUPPORTED, "jl_prefill: remap_far_in_kernel needs impl 0");
     return jl::launch_prefill_mma(args, stream);
   }
-  if (args->impl != 0) return jl::fail(JL_ERR_BAD_ARG, "jl_prefill: impl must be 0 or 1, got %d", args->impl);
+  if (args->impl == 2) {                                                  // the CTA-pair kernel, asked for by name
+    if (const char* why = jl::prefill_pair_unsupported_reason(args))
+      return jl::fail(JL_ERR_UNSUPPORTED, "jl_prefill: %s", why);
+    return jl::launch_prefill_pair(args, stream);
+  }
+  if (args->impl != 0) return jl::fail(JL_ERR_BAD_ARG, "jl_prefill: impl must be 0, 1 or 2, got %d", args->impl);
   if (const char* why = jl::prefill_tc_unsupported_reason(args))
     return jl::fail(JL_ERR_UNSUPPORTED, "jl_prefill: %s", why);
   return jl::launch_prefill_tc(args, stream);

@@ -108,7 +108,8 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 // hanging (its output is then invalid and the status word tells the host).  CTAs that start after
 // the device status word has been raised skip their waits from the beginning.
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000 * 1000;      // 1 s: far beyond any legitimate wait, even on a time-sliced GPU
-__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, Smem& sm) {
+template <class SmemT>
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, SmemT& sm) {
   if (mbar_try_wait(bar, parity)) return;
   volatile int* failed = reinterpret_cast<volatile int*>(&sm.failed);
   if (*failed) return;
@@ -726,6 +727,508 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
   if (threadIdx.x == 0 && sm.failed && p.status != nullptr) atomicExch(p.status, 1);
 }
 
+// ---------------------------------------------------------------------------------------------
+// The paired kernel: a cluster of two CTAs works on 256 query rows (128 each) with cta_group::2 MMAs
+// ---------------------------------------------------------------------------------------------
+// Every key / value tile is split between the two CTAs (each loads 64 of the 128 keys of K and 64 of the 128
+// columns of V; the tensor cores of the pair read both halves), so a CTA holds only its own 128 query rows and
+// half of every streamed tile.  Its tensor memory then has room for two score buffers and two probability
+// buffers beside ONE output accumulator:
+//     S_a | S_b | O | P_a | P_b   =  128 + 128 + 128 + 64 + 64 = 512 columns
+// The two softmax warpgroups take alternate key tiles of the same 128 rows (warps 4-7: even tiles, buffers a;
+// warps 8-11: odd tiles, buffers b), one thread per row as in the single-CTA kernel.  A score buffer is handed
+// back as soon as its scores are in registers, and Q K^T runs three tiles ahead of P V, so neither the softmax
+// threads nor the tensor pipe wait for each other's full round trip.
+// Both threads of a row add into the same O, so they share the row's reference maximum: it lives in shared
+// memory, is decided in tile order (the thread of tile g waits until the decision of tile g-1 is posted, which
+// happens a tile earlier in time) and the thread that raises it rescales O once P V of the previous tile has
+// retired and before its own P lets the next P V start.
+// Only the even CTA of the pair issues MMAs; its barriers collect the arrivals of both CTAs, its commits are
+// multicast to both.  All query classes stay resident in shared memory, so the look-ahead crosses phases.
+namespace pair {
+
+constexpr int kRows = 128;                       // query rows per CTA
+constexpr int kKStages = 4, kVStages = 3;
+constexpr int kQBytes = 128 * 256;               // 128 rows x 128 bf16 (two 64-column halves of 16 KB)
+constexpr int kQHalf = 128 * 128;
+constexpr int kKBytes = 64 * 256;                // this CTA's 64 keys x 128 bf16 (two 64-column halves of 8 KB)
+constexpr int kKHalf = 64 * 128;
+constexpr int kVBytes = 128 * 128;               // 128 keys x this CTA's 64 columns
+
+struct Maps {
+  CUtensorMap q[JL_MAX_CLASSES];     // box 64 x 1 x 128 x 1
+  CUtensorMap k[2];                  // box 64 x 1 x 64 x 1
+  CUtensorMap v;                     // box 64 x 1 x 128 x 1
+};
+
+struct Smem {
+  alignas(1024) uint8_t q[JL_MAX_CLASSES][kQBytes];
+  alignas(1024) uint8_t k[kKStages][kKBytes];
+  alignas(1024) uint8_t v[kVStages][kVBytes];
+  float ref_val[kRows];                          // the row's reference maximum (log2 domain) after the last decided tile
+  int ref_seq[4];                                // per 32 rows: number of tiles whose reference has been decided
+  float row_sum[2][kRows];
+  // leader-only barriers (both CTAs arrive on the even CTA's copy): q_full, k_full, v_full, s_free, p_full
+  uint64_t q_full[JL_MAX_CLASSES], k_full[kKStages], v_full[kVStages], s_free[2], p_full[2][2];
+  // per-CTA barriers, signalled by multicast commits of the leader's MMA warp
+  uint64_t k_empty[kKStages], v_empty[kVStages], s_full[2], pv_done[2], all_done;
+  uint32_t tmem_base;
+  int failed;
+};
+
+__device__ __forceinline__ uint32_t leader_addr(const void* local) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(r) : "r"(smem_u32(local)));
+  return r;
+}
+__device__ __forceinline__ void arrive_leader(uint32_t leader_bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(leader_bar) : "memory");
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// TMA load of this CTA's part of a tile; the bytes are counted on the leader's barrier
+__device__ __forceinline__ void tma_load_pair(void* dst, const CUtensorMap* map, uint32_t leader_bar, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(leader_bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void mma2_ss(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+               ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mma2_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n}"
+               ::"r"(d_tmem), "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// commit of the pair's MMAs, delivered to the barrier at the same offset in both CTAs
+__device__ __forceinline__ void commit_both(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(static_cast<uint16_t>(3)) : "memory");
+}
+__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+// Bounded wait until the reference of `need` tiles has been decided for the 32 rows of a quadrant
+__device__ __forceinline__ int load_acquire(const int* p) {
+  int v;
+  asm volatile("ld.acquire.cta.shared::cta.s32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
+  return v;
+}
+__device__ __forceinline__ void store_release(int* p, int v) {
+  asm volatile("st.release.cta.shared::cta.s32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ void wait_ref_seq(const int* seq, int need, Smem& sm) {
+  if (load_acquire(seq) >= need) return;
+  volatile int* failed = reinterpret_cast<volatile int*>(&sm.failed);
+  const uint64_t t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+      if (load_acquire(seq) >= need) return;
+    if (*failed) return;
+    if (globaltimer_ns() - t0 > kWaitLimitNs) { *failed = 1; return; }
+  }
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+prefill_pair_kernel(const __grid_constant__ Maps maps, const Params p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // the same offset in both CTAs: the dynamic shared memory of the two CTAs starts at the same window address
+  Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = static_cast<int>(blockIdx.x & 1);                       // rank in the pair; 0 issues the MMAs
+  const int pair_idx = static_cast<int>(gridDim.x >> 1) - 1 - static_cast<int>(blockIdx.x >> 1);      // latest (heaviest) rows first
+  const int head = blockIdx.y, b = blockIdx.z;
+  const int kvh = head / (p.heads / p.kv_heads);
+  const int q_row0_pair = pair_idx * kRowsPerCta;
+  const int q_row0 = q_row0_pair + rank * kRows;
+  const Schedule sched = make_schedule(p, q_row0_pair);                    // both CTAs walk the same tiles
+
+  if (threadIdx.x == 0) {
+    sm.failed = (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
+    for (int c = 0; c < JL_MAX_CLASSES; ++c) mbar_init(&sm.q_full[c], 1);
+    for (int i = 0; i < kKStages; ++i) { mbar_init(&sm.k_full[i], 1); mbar_init(&sm.k_empty[i], 1); }
+    for (int i = 0; i < kVStages; ++i) { mbar_init(&sm.v_full[i], 1); mbar_init(&sm.v_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sm.s_full[i], 1);
+      mbar_init(&sm.s_free[i], 8);                // one arrival per warp of the buffer's warpgroup, either CTA
+      mbar_init(&sm.p_full[i][0], 8);
+      mbar_init(&sm.p_full[i][1], 8);
+      mbar_init(&sm.pv_done[i], 1);
+    }
+    mbar_init(&sm.all_done, 1);
+    for (int i = 0; i < 4; ++i) sm.ref_seq[i] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (threadIdx.x < kRows) sm.ref_val[threadIdx.x] = -INFINITY;
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(512u));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+
+  // tile g of the schedule -> (class, key tile)
+  auto tile_of = [&](int g, int& c, int& j, bool& first_of_phase) {
+    int ph = 0, base = 0;
+    while (ph + 1 < sched.n_phases && g >= base + sched.n_tiles[ph]) { base += sched.n_tiles[ph]; ++ph; }
+    c = sched.cls[ph];
+    j = sched.j_lo[ph] + (g - base);
+    first_of_phase = g == base;
+  };
+
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsLow));
+    if (warp == 0) {
+      // ============================ TMA producer of Q and K (both CTAs) ============================
+      if (lane == 0 && sched.total > 0) {
+        for (int ph = 0; ph < sched.n_phases; ++ph) {
+          const int c = sched.cls[ph];
+          if (rank == 0) mbar_expect_tx(&sm.q_full[c], 2 * kQBytes);
+          const uint32_t bar = leader_addr(&sm.q_full[c]);
+          for (int h = 0; h < 2; ++h) tma_load_pair(sm.q[c] + h * kQHalf, &maps.q[c], bar, h * 64, head, q_row0, b);
+        }
+        for (int g = 0; g < sched.total; ++g) {
+          int c, j;
+          bool first;
+          tile_of(g, c, j, first);
+          const CUtensorMap* km = &maps.k[p.k_map[c]];
+          const int ks = g % kKStages;
+          mbar_wait(&sm.k_empty[ks], ((g / kKStages) & 1) ^ 1, sm);
+          if (rank == 0) mbar_expect_tx(&sm.k_full[ks], 2 * kKBytes);
+          const uint32_t kbar = leader_addr(&sm.k_full[ks]);
+          for (int h = 0; h < 2; ++h) tma_load_pair(sm.k[ks] + h * kKHalf, km, kbar, h * 64, kvh, j * kTileN + rank * 64, b);
+        }
+      }
+    } else if (warp == 3) {
+      // ================================ TMA producer of V (both CTAs) ================================
+      if (lane == 0) {
+        for (int g = 0; g < sched.total; ++g) {
+          int c, j;
+          bool first;
+          tile_of(g, c, j, first);
+          const int vs = g % kVStages;
+          mbar_wait(&sm.v_empty[vs], ((g / kVStages) & 1) ^ 1, sm);
+          if (rank == 0) mbar_expect_tx(&sm.v_full[vs], 2 * kVBytes);
+          tma_load_pair(sm.v[vs], &maps.v, leader_addr(&sm.v_full[vs]), rank * 64, kvh, j * kTileN, b);
+        }
+      }
+    } else if (warp == 1 && rank == 0) {
+      // ============================== Q K^T issuer (leader CTA) ==============================
+      // Two issuing warps, so that a late P never holds back a Q K^T whose score buffer is already free
+      // (and the other way round): this warp is gated by K tiles and freed score buffers only.
+      if (sched.total > 0) {
+        uint32_t leader;
+        asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(leader));
+        const uint32_t idesc_qk = instr_desc(256, kTileN, 0);
+        const uint64_t q_desc0 = smem_desc(smem_u32(sm.q[0]), 16, 1024);
+        const uint64_t k_desc0 = smem_desc(smem_u32(sm.k[0]), 16, 1024);
+#if JL_DIAG == 5
+        long long w_k = 0, w_sf = 0;
+        const long long t_begin = clock64();
+#endif
+        for (int g = 0; g < sched.total; ++g) {
+          int c, j;
+          bool first;
+          tile_of(g, c, j, first);
+          if (first) mbar_wait(&sm.q_full[c], 0, sm);
+          const int ks = g % kKStages;
+          JL_TIMED(w_k, mbar_wait(&sm.k_full[ks], (g / kKStages) & 1, sm));
+          if (g >= 2) JL_TIMED(w_sf, mbar_wait(&sm.s_free[g & 1], ((g >> 1) - 1) & 1, sm));      // the scores of tile g-2 are in registers
+          tc_fence_after();
+          const uint64_t qd = q_desc0 + static_cast<uint64_t>((c * kQBytes) >> 4);
+          const uint64_t kd = k_desc0 + static_cast<uint64_t>((ks * kKBytes) >> 4);
+          if (leader) {
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+              const uint64_t off_a = static_cast<uint64_t>(((kk >> 2) * kQHalf + (kk & 3) * 32) >> 4);
+              const uint64_t off_b = static_cast<uint64_t>(((kk >> 2) * kKHalf + (kk & 3) * 32) >> 4);
+              mma2_ss(tmem + (g & 1) * 128, qd + off_a, kd + off_b, idesc_qk, kk > 0);
+            }
+            commit_both(&sm.s_full[g & 1]);
+            commit_both(&sm.k_empty[ks]);
+          }
+          __syncwarp();
+        }
+#if JL_DIAG == 5
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0)
+          printf("pair QK warp: %d tiles, %lld clk/tile; waits per tile: K %lld S-free %lld\n", sched.total,
+                 (clock64() - t_begin) / sched.total, w_k / sched.total, w_sf / sched.total);
+#endif
+      }
+    } else if (warp == 2 && rank == 0) {
+      // =============================== P V issuer (leader CTA) ===============================
+      if (sched.total > 0) {
+        uint32_t leader;
+        asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(leader));
+        const uint32_t idesc_pv = instr_desc(256, kHeadDim, 1);
+        const uint64_t v_desc0 = smem_desc(smem_u32(sm.v[0]), kVBytes, 1024);
+#if JL_DIAG == 5
+        long long w_v = 0, w_p0 = 0, w_p1 = 0;
+        const long long t_begin = clock64();
+#endif
+        for (int g = 0; g < sched.total; ++g) {
+          const int vs = g % kVStages, pb = g & 1;
+          const uint64_t vd = v_desc0 + static_cast<uint64_t>((vs * kVBytes) >> 4);
+          JL_TIMED(w_v, mbar_wait(&sm.v_full[vs], (g / kVStages) & 1, sm));
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            if (h == 0) { JL_TIMED(w_p0, mbar_wait(&sm.p_full[pb][h], (g >> 1) & 1, sm)); }
+            else { JL_TIMED(w_p1, mbar_wait(&sm.p_full[pb][h], (g >> 1) & 1, sm)); }
+            tc_fence_after();
+            if (leader) {
+#pragma unroll
+              for (int kk = 4 * h; kk < 4 * h + 4; ++kk)
+                mma2_ts(tmem + 256, tmem + 384 + pb * 64 + kk * 8, vd + static_cast<uint64_t>((kk * 2048) >> 4), idesc_pv,
+                        (g > 0 || kk > 0) ? 1u : 0u);
+              if (h == 1) {
+                commit_both(&sm.pv_done[pb]);
+                commit_both(&sm.v_empty[vs]);
+              }
+            }
+            __syncwarp();
+          }
+        }
+        if (leader) commit_both(&sm.all_done);
+        __syncwarp();
+#if JL_DIAG == 5
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0)
+          printf("pair PV warp: %d tiles, %lld clk/tile; waits per tile: V %lld P0 %lld P1 %lld\n", sched.total,
+                 (clock64() - t_begin) / sched.total, w_v / sched.total, w_p0 / sched.total, w_p1 / sched.total);
+#endif
+      }
+    }
+  } else {
+    // ===================== softmax + epilogue (one thread per row, alternate key tiles) =====================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsHigh));
+    const int wg = (warp - 4) >> 2;                        // takes the tiles g with (g & 1) == wg; epilogue: output columns 64 wg ..
+    const int quad = warp & 3;
+    const int r_in_tile = quad * 32 + lane;
+    const int q_row = q_row0 + r_in_tile;
+    const bool row_valid = q_row < p.sq;
+    const int64_t pq = key_position(q_row, p.q_pos0, p.q_block, p.q_block_stride);
+    const int tile_rows = min(kRows, p.sq - q_row0);
+    const int64_t pq_t0 = key_position(q_row0, p.q_pos0, p.q_block, p.q_block_stride);
+    const int64_t pq_t1 = pq_t0 + (tile_rows > 0 ? tile_rows - 1 : 0);
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t t_s = tmem + lane_base + wg * 128;             // my row of my score buffer
+    const uint32_t t_p = tmem + lane_base + 384 + wg * 64;        // my row of my probability buffer
+    const uint32_t t_o = tmem + lane_base + 256;                  // the row's output accumulator (shared with the other warpgroup)
+    const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2);
+    const uint32_t s_free_bar = leader_addr(&sm.s_free[wg]);
+    const uint32_t p_full_bar[2] = {leader_addr(&sm.p_full[wg][0]), leader_addr(&sm.p_full[wg][1])};
+    volatile float* ref_val = sm.ref_val;
+
+    float my_ref = -INFINITY, l_sum = 0.f;                 // l_sum is expressed relative to my_ref
+#if JL_DIAG == 5
+    long long d_ws = 0, d_ld = 0, d_ref = 0, d_pv = 0, d_exp = 0;
+    int d_n = 0;
+#endif
+    auto exp_block = [&](const uint32_t (&s)[128], int e0, uint64_t negm2, uint32_t col, uint64_t (&acc2)[4]) {
+      uint32_t pk[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int e = e0 + 2 * i;
+        const uint64_t x = fma2(pack2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), scale2, negm2);
+        const uint64_t pp = ((kPolyMask >> (i & 7)) & 1u) ? exp2_pair_fma(x) : exp2_pair_sfu(x);
+        acc2[i & 3] = add2(acc2[i & 3], pp);
+        float p0, p1;
+        unpack2(pp, p0, p1);
+        pk[i] = pack_bf16x2(p0, p1);
+      }
+      JL_TMEM_ST16(t_p + col, pk, 0);
+    };
+    auto max_block = [&](const uint32_t (&s)[128], int e0, float (&m4)[4]) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) m4[i & 3] = max3(m4[i & 3], __uint_as_float(s[e0 + 2 * i]), __uint_as_float(s[e0 + 2 * i + 1]));
+    };
+    auto publish = [&](int half) {
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) arrive_leader(p_full_bar[half]);
+    };
+
+    int g = 0;
+    for (int ph = 0; ph < sched.n_phases; ++ph) {
+      const int c = sched.cls[ph];
+      int64_t row_lo, row_hi, tile_lo_max, tile_hi_min, dummy;
+      class_interval(p, c, pq, row_lo, row_hi);
+      class_interval(p, c, pq_t1, tile_lo_max, dummy);
+      class_interval(p, c, pq_t0, dummy, tile_hi_min);
+      for (int jj = 0; jj < sched.n_tiles[ph]; ++jj, ++g) {
+        if ((g & 1) != wg) continue;
+        const int n = g >> 1;                              // my n-th tile
+        const int j = sched.j_lo[ph] + jj;
+        const int64_t tp0 = key_position(static_cast<int64_t>(j) * kTileN, p.k_pos0, p.k_block, p.k_block_stride);
+        const int valid = min(kTileN, p.sk - j * kTileN);
+        const bool uniform = valid == kTileN && tile_lo_max <= tp0 && tile_hi_min >= tp0 + kTileN - 1;
+
+#if JL_DIAG == 5
+        const long long c0 = clock64();
+#endif
+        mbar_wait(&sm.s_full[wg], n & 1, sm);
+        tc_fence_after();
+#if JL_DIAG == 5
+        const long long c1 = clock64();
+#endif
+#if JL_DIAG == 2
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) arrive_leader(s_free_bar);
+        if (n >= 1) mbar_wait(&sm.pv_done[wg], (n - 1) & 1, sm);
+        if (lane == 0) { arrive_leader(p_full_bar[0]); arrive_leader(p_full_bar[1]); }
+        continue;
+#endif
+        uint32_t s[128];
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        // scores -> registers and row maximum; the score buffer goes back to the tensor pipe as soon as it has been read
+        JL_TMEM_LD32(t_s + 0, s, 0);
+        // under the latency of the first load: P V of my previous tile has read the probability buffer (it has
+        // long retired; P V of tile g-3 then has too, which the parity wait of a rescale below relies on), and
+        // the reference tile g-1 left, if it is already posted
+        if (n >= 1) {
+          mbar_wait(&sm.pv_done[wg], (n - 1) & 1, sm);
+          tc_fence_after();
+        }
+        const bool ref_early = load_acquire(&sm.ref_seq[quad]) >= g;
+        float ref_prev = ref_val[r_in_tile];
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          tmem_wait_ld();
+          if (ch + 1 < 4) {
+            JL_TMEM_LD32(t_s + (ch + 1) * 32, s, (ch + 1) * 32);
+          } else {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) arrive_leader(s_free_bar);
+          }
+          if (uniform) max_block(s, ch * 32, m4);
+        }
+        if (!uniform) {
+          const int64_t lo64 = row_lo - tp0, hi64 = row_hi - tp0 + 1;
+          const int c_lo = lo64 < 0 ? 0 : (lo64 > 128 ? 128 : static_cast<int>(lo64));
+          const int c_hi = hi64 < 0 ? 0 : (hi64 > valid ? valid : static_cast<int>(hi64));
+#pragma unroll
+          for (int i = 0; i < 128; ++i)
+            if (!(i >= c_lo && i < c_hi)) s[i] = 0xff800000u;        // -inf
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) max_block(s, ch * 32, m4);
+        }
+        const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;
+#if JL_DIAG == 5
+        const long long c2 = clock64();
+#endif
+        // the reference of this tile: the one tile g-1 left, raised if some row of the warp outgrew it by 2^8
+        if (!ref_early) {
+          wait_ref_seq(&sm.ref_seq[quad], g, sm);
+          ref_prev = ref_val[r_in_tile];
+        }
+        const bool raise = __any_sync(0xffffffffu, mx > ref_prev + 8.f);
+        const float ref_new = raise ? fmaxf(ref_prev, mx) : ref_prev;
+        if (raise) ref_val[r_in_tile] = ref_new;
+        __syncwarp();                                      // orders the lanes' writes before lane 0's release
+        if (lane == 0) store_release(&sm.ref_seq[quad], g + 1);
+        if (raise && g > 0) {
+          // O follows the reference: P V of tile g-1 has to retire first, P V of tile g waits for this thread's P
+          const float alpha = ref_new == -INFINITY ? 1.f : fast_exp2(ref_prev - ref_new);
+          mbar_wait(&sm.pv_done[(g - 1) & 1], ((g - 1) >> 1) & 1, sm);
+          tc_fence_after();
+#pragma unroll
+          for (int cchunk = 0; cchunk < 4; ++cchunk) {
+            uint32_t o[32];
+            JL_TMEM_LD32(t_o + cchunk * 32, o, 0);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            JL_TMEM_ST32(t_o + cchunk * 32, o, 0);
+          }
+        }
+        if (ref_new != my_ref) {
+          l_sum *= ref_new == -INFINITY ? 1.f : fast_exp2(my_ref - ref_new);
+          my_ref = ref_new;
+        }
+#if JL_DIAG == 5
+        const long long c3 = clock64();
+        const long long c4 = c3;
+#endif
+        const float m_use = my_ref == -INFINITY ? 0.f : my_ref;
+        const uint64_t negm2 = pack2(-m_use, -m_use);
+        uint64_t acc2[4] = {0ull, 0ull, 0ull, 0ull};
+        exp_block(s, 0, negm2, 0, acc2);
+        exp_block(s, 32, negm2, 16, acc2);
+        publish(0);
+        exp_block(s, 64, negm2, 32, acc2);
+        exp_block(s, 96, negm2, 48, acc2);
+        publish(1);
+        float a0, a1;
+        unpack2(add2(add2(acc2[0], acc2[1]), add2(acc2[2], acc2[3])), a0, a1);
+        l_sum += a0 + a1;
+#if JL_DIAG == 5
+        d_ws += c1 - c0; d_ld += c2 - c1; d_ref += c3 - c2; d_pv += c4 - c3; d_exp += clock64() - c4; ++d_n;
+#endif
+      }
+    }
+#if JL_DIAG == 5
+    if (blockIdx.x < 2 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && quad == 0 && d_n > 0)
+      printf("pair softmax rank %d wg %d: %d tiles; per tile: wait S %lld, load+max %lld, reference %lld, wait P buffer %lld, exps+publish %lld\n",
+             rank, wg, d_n, d_ws / d_n, d_ld / d_n, d_ref / d_n, d_pv / d_n, d_exp / d_n);
+#endif
+
+    // ---- epilogue: O / l -> bf16, LSE ----
+    if (sched.total > 0) {
+      mbar_wait(&sm.all_done, 0, sm);
+      tc_fence_after();
+#if JL_DIAG != 2
+      wait_ref_seq(&sm.ref_seq[quad], sched.total, sm);
+#endif
+    }
+    const float ref_fin = ref_val[r_in_tile];
+    const bool seen = ref_fin != -INFINITY;
+    sm.row_sum[wg][r_in_tile] = (seen && my_ref != -INFINITY) ? l_sum * fast_exp2(my_ref - ref_fin) : 0.f;
+    softmax_bar();
+    const float l_row = sm.row_sum[0][r_in_tile] + sm.row_sum[1][r_in_tile];
+    const float inv = seen ? 1.f / l_row : 0.f;
+    __nv_bfloat16* orow = p.out + b * p.os_b + static_cast<int64_t>(q_row) * p.os_s + head * p.os_h + wg * 64;
+#pragma unroll
+    for (int cchunk = 0; cchunk < 2; ++cchunk) {
+      uint32_t o[32];
+      if (sched.total > 0) {
+        JL_TMEM_LD32(t_o + wg * 64 + cchunk * 32, o, 0);
+        tmem_wait_ld();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = 0u;
+      }
+      if (row_valid) {
+#pragma unroll
+        for (int v4 = 0; v4 < 4; ++v4) {
+          uint4 w;
+          w.x = pack_bf16x2(__uint_as_float(o[v4 * 8 + 0]) * inv, __uint_as_float(o[v4 * 8 + 1]) * inv);
+          w.y = pack_bf16x2(__uint_as_float(o[v4 * 8 + 2]) * inv, __uint_as_float(o[v4 * 8 + 3]) * inv);
+          w.z = pack_bf16x2(__uint_as_float(o[v4 * 8 + 4]) * inv, __uint_as_float(o[v4 * 8 + 5]) * inv);
+          w.w = pack_bf16x2(__uint_as_float(o[v4 * 8 + 6]) * inv, __uint_as_float(o[v4 * 8 + 7]) * inv);
+          *reinterpret_cast<uint4*>(orow + cchunk * 32 + v4 * 8) = w;
+        }
+      }
+    }
+    if (wg == 0 && row_valid && p.lse != nullptr)
+      p.lse[(static_cast<int64_t>(b) * p.heads + head) * p.sq + q_row] = seen ? (ref_fin + log2f(l_row)) * kLn2 : -INFINITY;
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();               // neither CTA leaves (or frees tensor memory) while the other may still signal it
+  if (warp == 2) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u));
+  }
+  if (threadIdx.x == 0 && sm.failed && p.status != nullptr) atomicExch(p.status, 1);
+}
+
+}  // namespace pair
+
 }  // namespace tc
 
 // ---------------------------------------------------------------------------------------------
@@ -745,8 +1248,8 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// (B, S, Hx, 128) bf16 view -> 4-D map (d, h, s, b), box 64 x 1 x 128 x 1, 128-byte swizzle, zero fill past the end.
-static int make_map(CUtensorMap* m, const void* base, int batch, int seq, int heads, int64_t sb, int64_t ss, int64_t sh) {
+// (B, S, Hx, 128) bf16 view -> 4-D map (d, h, s, b), box 64 x 1 x box_rows x 1, 128-byte swizzle, zero fill past the end.
+static int make_map(CUtensorMap* m, const void* base, int batch, int seq, int heads, int64_t sb, int64_t ss, int64_t sh, int box_rows = 128) {
   EncodeTiledFn enc = encode_fn();
   if (enc == nullptr) return fail(JL_ERR_LAUNCH, "jl_prefill: cuTensorMapEncodeTiled is not available from the driver");
   // size-1 dimensions may arrive with stride 0; the encoder wants positive multiples of 16 bytes
@@ -755,7 +1258,7 @@ static int make_map(CUtensorMap* m, const void* base, int batch, int seq, int he
   const cuuint64_t strides[3] = {static_cast<cuuint64_t>((heads > 1 && sh > 0 ? sh : dflt / 2) * 2),
                                  static_cast<cuuint64_t>((seq > 1 && ss > 0 ? ss : dflt / 2) * 2),
                                  static_cast<cuuint64_t>((batch > 1 && sb > 0 ? sb : dflt / 2) * 2)};
-  const cuuint32_t box[4] = {64, 1, 128, 1};
+  const cuuint32_t box[4] = {64, 1, static_cast<cuuint32_t>(box_rows), 1};
   const cuuint32_t es[4] = {1, 1, 1, 1};
   const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, es,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -813,9 +1316,8 @@ int prefill_tc_status() {
   return v;
 }
 
-int launch_prefill_tc(const jl_prefill_args* a, cudaStream_t stream) {
-  tc::Maps maps;
-  tc::Params p{};
+// Tensor maps and kernel parameters of a request (shared by the two tcgen05 kernels; k_box_rows = key rows per TMA box).
+static int prepare(const jl_prefill_args* a, CUtensorMap* qmaps, CUtensorMap* kmaps, CUtensorMap* vmap, tc::Params& p, int k_box_rows) {
   int n_k = 0;
   const void* kptr[2] = {nullptr, nullptr};
   const bool no_keys = a->seqlen_k == 0;      // nothing is loaded then: the key / value maps only have to be well formed
@@ -823,7 +1325,7 @@ int launch_prefill_tc(const jl_prefill_args* a, cudaStream_t stream) {
   for (int c = 0; c < a->map.n_classes; ++c) {
     const void* qc = remap ? a->q[0] : a->q[c];
     const void* kc = remap ? a->k[0] : a->k[c];
-    int rc = make_map(&maps.q[c], qc, a->batch, a->seqlen_q, a->heads, a->q_stride_b, a->q_stride_s, a->q_stride_h);
+    int rc = make_map(&qmaps[c], qc, a->batch, a->seqlen_q, a->heads, a->q_stride_b, a->q_stride_s, a->q_stride_h);
     if (rc != JL_OK) return rc;
     int slot = -1;
     for (int i = 0; i < n_k; ++i)
@@ -831,16 +1333,16 @@ int launch_prefill_tc(const jl_prefill_args* a, cudaStream_t stream) {
     if (slot < 0) {
       slot = n_k++;
       kptr[slot] = kc;
-      rc = no_keys ? make_map(&maps.k[slot], a->q[0], 1, 1, 1, 0, 0, 0)
-                   : make_map(&maps.k[slot], kc, a->batch, a->seqlen_k, a->kv_heads, a->k_stride_b, a->k_stride_s, a->k_stride_h);
+      rc = no_keys ? make_map(&kmaps[slot], a->q[0], 1, 1, 1, 0, 0, 0, k_box_rows)
+                   : make_map(&kmaps[slot], kc, a->batch, a->seqlen_k, a->kv_heads, a->k_stride_b, a->k_stride_s, a->k_stride_h, k_box_rows);
       if (rc != JL_OK) return rc;
     }
     p.k_map[c] = slot;
   }
-  for (int c = a->map.n_classes; c < JL_MAX_CLASSES; ++c) maps.q[c] = maps.q[0];
-  if (n_k == 1) maps.k[1] = maps.k[0];
-  int rc = no_keys ? make_map(&maps.v, a->q[0], 1, 1, 1, 0, 0, 0)
-                   : make_map(&maps.v, a->v, a->batch, a->seqlen_k, a->kv_heads, a->v_stride_b, a->v_stride_s, a->v_stride_h);
+  for (int c = a->map.n_classes; c < JL_MAX_CLASSES; ++c) qmaps[c] = qmaps[0];
+  if (n_k == 1) kmaps[1] = kmaps[0];
+  int rc = no_keys ? make_map(vmap, a->q[0], 1, 1, 1, 0, 0, 0)
+                   : make_map(vmap, a->v, a->batch, a->seqlen_k, a->kv_heads, a->v_stride_b, a->v_stride_s, a->v_stride_h);
   if (rc != JL_OK) return rc;
   p.sq = a->seqlen_q; p.sk = a->seqlen_k; p.heads = a->heads; p.kv_heads = a->kv_heads; p.batch = a->batch;
   p.q_pos0 = a->q_pos0; p.k_pos0 = a->k_pos0;
@@ -858,6 +1360,14 @@ int launch_prefill_tc(const jl_prefill_args* a, cudaStream_t stream) {
   p.remap = a->remap_far_in_kernel != 0;
   p.group_size = a->group_size > 0 ? a->group_size : 1;
   p.inv_freq = a->inv_freq;
+  return JL_OK;
+}
+
+int launch_prefill_tc(const jl_prefill_args* a, cudaStream_t stream) {
+  tc::Maps maps;
+  tc::Params p{};
+  const int rc = prepare(a, maps.q, maps.k, &maps.v, p, 128);
+  if (rc != JL_OK) return rc;
   const int smem = static_cast<int>(sizeof(tc::Smem)) + 1024;
   // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute
   static bool attr_done[64] = {false};
@@ -871,6 +1381,32 @@ int launch_prefill_tc(const jl_prefill_args* a, cudaStream_t stream) {
   dim3 grid((a->seqlen_q + tc::kRowsPerCta - 1) / tc::kRowsPerCta, a->heads, a->batch);
   tc::prefill_tc_kernel<<<grid, tc::kThreads, smem, stream>>>(maps, p);
   return check_launch("jl_prefill (tcgen05)");
+}
+
+// NULL if the paired (two-CTA) kernel covers the request, else the reason it does not.
+const char* prefill_pair_unsupported_reason(const jl_prefill_args* a) {
+  if (a->remap_far_in_kernel) return "the in-kernel remap runs on the single-CTA kernel";
+  return prefill_tc_unsupported_reason(a);
+}
+
+int launch_prefill_pair(const jl_prefill_args* a, cudaStream_t stream) {
+  tc::pair::Maps maps;
+  tc::Params p{};
+  const int rc = prepare(a, maps.q, maps.k, &maps.v, p, 64);
+  if (rc != JL_OK) return rc;
+  const int smem = static_cast<int>(sizeof(tc::pair::Smem)) + 1024;
+  static bool attr_done[64] = {false};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(JL_ERR_LAUNCH, "jl_prefill: no current CUDA device");
+  if (!attr_done[dev]) {
+    if (cudaFuncSetAttribute(tc::pair::prefill_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return check_launch("jl_prefill (shared memory opt-in)");
+    attr_done[dev] = true;
+  }
+  // one cluster of two CTAs per 256 query rows (the cluster shape is a compile-time attribute of the kernel)
+  dim3 grid(2 * ((a->seqlen_q + tc::kRowsPerCta - 1) / tc::kRowsPerCta), a->heads, a->batch);
+  tc::pair::prefill_pair_kernel<<<grid, tc::kThreads, smem, stream>>>(maps, p);
+  return check_launch("jl_prefill (tcgen05, CTA pairs)");
 }
 
 }  // namespace jl

@@ -70,11 +70,27 @@ def test_prefill_refuses_shapes_the_tcgen05_kernel_does_not_cover():
         ops.posmap_prefill([q, q], [k, k], k, pmap=ops.PositionMap.jetlong(40), q_pos0=0, q_block=128, q_block_stride=256)
 
 
-def test_prefill_without_keys_returns_empty_rows():
+def test_prefill_cta_pair_kernel_refuses_what_it_does_not_cover():
+    """impl 2 (the CTA-pair kernel) has no in-kernel remap of the far class; an unknown impl is a bad argument."""
+    from jetlm.kernels import jetlong_ops as ops
+    from jetlm.kernels._native import JL_ERR_BAD_ARG, JL_ERR_UNSUPPORTED, NativeError
+    q = torch.randn(1, 256, 4, 128, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(1, 256, 2, 128, device="cuda", dtype=torch.bfloat16)
+    inv = torch.ones(64, device="cuda")
+    with pytest.raises(NativeError, match="in-kernel remap") as err:
+        ops.posmap_prefill([q], [k], k, pmap=ops.PositionMap.jetlong(40), q_pos0=0, remap_far=(inv, 4), impl=2)
+    assert err.value.status == JL_ERR_UNSUPPORTED
+    with pytest.raises(NativeError, match="impl must be 0, 1 or 2") as err:
+        ops.posmap_prefill([q, q], [k, k], k, pmap=ops.PositionMap.jetlong(40), q_pos0=0, impl=3)
+    assert err.value.status == JL_ERR_BAD_ARG
+
+
+@pytest.mark.parametrize("impl", [0, 2])
+def test_prefill_without_keys_returns_empty_rows(impl):
     from jetlm.kernels import jetlong_ops as ops
     q = torch.randn(1, 300, 4, 128, device="cuda", dtype=torch.bfloat16)
     k = torch.empty(1, 0, 2, 128, device="cuda", dtype=torch.bfloat16)
-    out, lse = ops.posmap_prefill([q, q], [k, k], k, pmap=ops.PositionMap.jetlong(40), q_pos0=0)
+    out, lse = ops.posmap_prefill([q, q], [k, k], k, pmap=ops.PositionMap.jetlong(40), q_pos0=0, impl=impl)
     assert torch.all(out == 0) and torch.all(torch.isinf(lse) & (lse < 0))
 
 

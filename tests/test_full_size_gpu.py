@@ -113,7 +113,8 @@ def test_block_cyclic_stripes_full_size_spot_rows():
     _spot_rows("jetlong", dict(w_0=w0, G=4), [qb, qg], [kb, kg], v, out, lse, rows, H, Hk, q_positions, k_positions)
 
 
-def test_block_cyclic_query_stripe_against_all_keys_spot_rows():
+@pytest.mark.parametrize("impl", [0, 2])
+def test_block_cyclic_query_stripe_against_all_keys_spot_rows(impl):
     """The other multi-GPU form: one rank's block-cyclic query stripe (blocks of 256, rank 6 of 8) against ALL
     131072 keys in position order (gathered K / V)."""
     ops = _ops()
@@ -123,7 +124,7 @@ def test_block_cyclic_query_stripe_against_all_keys_spot_rows():
     qb, qg = (torch.randn(1, n_loc, H, D, device="cuda").bfloat16() for _ in range(2))
     kb, kg, v = (torch.randn(1, S, Hk, D, device="cuda").bfloat16() for _ in range(3))
     out, lse = ops.posmap_prefill([qb, qg], [kb, kg], v, pmap=ops.PositionMap.jetlong(w0),
-                                  q_pos0=rq * blk, q_block=blk, q_block_stride=world * blk)
+                                  q_pos0=rq * blk, q_block=blk, q_block_stride=world * blk, impl=impl)
     assert _status_clean()
     i = torch.arange(n_loc)
     q_positions = rq * blk + (i // blk) * world * blk + i % blk

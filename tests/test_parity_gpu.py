@@ -192,7 +192,7 @@ def test_norm_rope_fused_pass():
 # prefill
 # ------------------------------------------------------------------------------------------------
 
-@pytest.mark.parametrize("impl", [0, 1])
+@pytest.mark.parametrize("impl", [0, 1, 2])
 @pytest.mark.parametrize("name", ["prefill_fresh.npz", "prefill_chunked.npz"])
 def test_prefill_golden(golden, name, impl):
     g = golden(name)
@@ -204,11 +204,17 @@ def test_prefill_golden(golden, name, impl):
     _check(out, lse, g["out"], g["lse"], f"{name} impl={impl}")
 
 
-def _prefill_case(seed, B, S, Skv, H, Hk, w0, impl, strided=False):
+def _prefill_case(seed, B, S, Skv, H, Hk, w0, impl, strided=False, q_scale=1.0, k_ramp=0.0):
     torch.manual_seed(seed)
     D = 128
     qb, qg = torch.randn(B, S, H, D).bfloat16(), torch.randn(B, S, H, D).bfloat16()
     kb, kg, v = (torch.randn(B, Skv, Hk, D).bfloat16() for _ in range(3))
+    qb, qg = (qb.float() * q_scale).bfloat16(), (qg.float() * q_scale).bfloat16()
+    if q_scale != 1.0:   # near one-hot rows return single values of V: keep them below 1 so that a bf16 step stays under the tolerance
+        v = (v.float() * 0.25).bfloat16()
+    if k_ramp:      # key norms grow with the position: the row maximum keeps rising from tile to tile
+        r = (1.0 + k_ramp * torch.arange(Skv).float() / Skv).view(1, Skv, 1, 1)
+        kb, kg = (kb.float() * r).bfloat16(), (kg.float() * r).bfloat16()
     eo, el = orc.jetlong_prefill(qb, qg, kb, kg, v, seqstart=Skv - S, w0=w0)
     dq, dqg, dkb, dkg, dv = _dev(qb, qg, kb, kg, v)
     if strided:   # (B,H,S,D) storage viewed as (B,S,H,D), the layout the modeling file hands over
@@ -218,7 +224,7 @@ def _prefill_case(seed, B, S, Skv, H, Hk, w0, impl, strided=False):
     _check(out, lse, eo, el, f"prefill seed={seed} S={S} Skv={Skv} w0={w0} impl={impl}")
 
 
-@pytest.mark.parametrize("impl", [0, 1])
+@pytest.mark.parametrize("impl", [0, 1, 2])
 @pytest.mark.parametrize("S,Skv,w0", [(1, 1, 0), (5, 5, 0), (64, 64, 1), (127, 127, 63), (128, 128, 64), (129, 129, 65),
                                       (300, 300, 0), (300, 300, 1000), (257, 257, 128), (96, 480, 100), (2, 700, 31),
                                       (384, 384, 127), (384, 384, 128), (384, 384, 129)])
@@ -226,13 +232,23 @@ def test_prefill_shapes(S, Skv, w0, impl):
     _prefill_case(S * 7 + w0, 1, S, Skv, 4, 2, w0, impl)
 
 
-@pytest.mark.parametrize("impl", [0, 1])
+@pytest.mark.parametrize("impl", [0, 2])
+@pytest.mark.parametrize("q_scale,k_ramp,w0", [(6.0, 0.0, 300), (30.0, 0.0, 300), (4.0, 20.0, 3000), (20.0, 8.0, 100)])
+def test_prefill_row_maximum_jumps(q_scale, k_ramp, w0, impl):
+    """Scores whose row maximum jumps by far more than 2^8 between key tiles, again and again: the running
+    reference of the online softmax is raised and the output accumulator rescaled many times per row (in the
+    CTA-pair kernel by either of the two threads that share a row)."""
+    _prefill_case(11, 1, 1024, 2048, 4, 2, w0, impl, q_scale=q_scale, k_ramp=k_ramp)
+    _prefill_case(12, 1, 1500, 2300, 8, 4, w0, impl, q_scale=q_scale, k_ramp=k_ramp)
+
+
+@pytest.mark.parametrize("impl", [0, 1, 2])
 def test_prefill_batch_heads_strided(impl):
     _prefill_case(5, 2, 200, 328, 8, 2, 50, impl, strided=True)
     _prefill_case(6, 1, 260, 260, 6, 6, 77, impl)
 
 
-@pytest.mark.parametrize("impl", [0, 1])
+@pytest.mark.parametrize("impl", [0, 1, 2])
 def test_prefill_config1_geometry(impl):
     """16 query heads, 8 kv heads, head_dim 128, S = 4096, w_0 = 1024, real regrouped operands (G = 2)."""
     torch.manual_seed(0)
@@ -249,18 +265,20 @@ def test_prefill_config1_geometry(impl):
 
 
 def test_prefill_impls_agree_large():
-    """At a size the CPU oracle cannot reach, the two GPU kernels must agree with each other."""
+    """At a size the CPU oracle cannot reach, the three GPU kernels must agree with each other."""
     torch.manual_seed(9)
     B, S, H, Hk, D, w0 = 1, 8192 + 37, 4, 2, 128, 2048
     ts = [torch.randn(B, S, h, D, device="cuda").bfloat16() for h in (H, H, Hk, Hk, Hk)]
     pm = _ops().PositionMap.jetlong(w0)
     o0, l0 = _ops().posmap_prefill(ts[:2], ts[2:4], ts[4], pmap=pm, q_pos0=0, impl=0)
     o1, l1 = _ops().posmap_prefill(ts[:2], ts[2:4], ts[4], pmap=pm, q_pos0=0, impl=1)
+    o2, l2 = _ops().posmap_prefill(ts[:2], ts[2:4], ts[4], pmap=pm, q_pos0=0, impl=2)
     _check(o0, l0, o1.float().cpu(), l1.cpu(), "impl 0 vs impl 1")
+    _check(o2, l2, o1.float().cpu(), l1.cpu(), "impl 2 vs impl 1")
 
 
-@pytest.mark.parametrize("S,H,Hk,w0", [(65536, 16, 8, 32768), (131072, 32, 8, 32768)])
-def test_prefill_full_size_spot_rows(S, H, Hk, w0):
+@pytest.mark.parametrize("S,H,Hk,w0,impl", [(65536, 16, 8, 32768, 0), (131072, 32, 8, 32768, 0), (65536, 16, 8, 32768, 2)])
+def test_prefill_full_size_spot_rows(S, H, Hk, w0, impl):
     """The benchmark geometries (Qwen3-1.7B at 65536 tokens, Qwen3-4B/8B at 131072 tokens, w_0 = 32768) in one
     launch; sampled (row, head) pairs — first rows, both sides of the class boundary, tile edges, the last
     row — are recomputed by the fp32 oracle from the same bf16 operands."""
@@ -269,7 +287,7 @@ def test_prefill_full_size_spot_rows(S, H, Hk, w0):
     D = 128
     mk = lambda h: torch.randn(1, S, h, D, device="cuda").bfloat16()
     qb, qg, kb, kg, v = mk(H), mk(H), mk(Hk), mk(Hk), mk(Hk)
-    out, lse = ops.posmap_prefill([qb, qg], [kb, kg], v, pmap=ops.PositionMap.jetlong(w0), q_pos0=0)
+    out, lse = ops.posmap_prefill([qb, qg], [kb, kg], v, pmap=ops.PositionMap.jetlong(w0), q_pos0=0, impl=impl)
     assert _native_status_clean()
     rows = [0, 1, 127, 128, 255, 256, w0 - 1, w0, w0 + 1, w0 + 129, S // 2 + 77, S - w0 - 1, S - 257, S - 1]
     rep = H // Hk
@@ -288,7 +306,8 @@ def _native_status_clean():
     return _native.lib().jl_prefill_status() == 0
 
 
-def test_prefill_block_cyclic_keys():
+@pytest.mark.parametrize("impl", [0, 2])
+def test_prefill_block_cyclic_keys(impl):
     """A rank's block-cyclic stripe of the keys + merge of the stripes == attention over all keys."""
     ops = _ops()
     torch.manual_seed(12)
@@ -301,7 +320,7 @@ def test_prefill_block_cyclic_keys():
         idx = torch.cat([torch.arange(b0, b0 + blk) for b0 in range(r * blk, S, R * blk)])
         o, l = ops.posmap_prefill(_dev(qb, qg), _dev(kb[:, idx].contiguous(), kg[:, idx].contiguous()),
                                   v[:, idx].contiguous().cuda(), pmap=ops.PositionMap.jetlong(w0), q_pos0=0,
-                                  k_pos0=r * blk, k_block=blk, k_block_stride=R * blk)
+                                  k_pos0=r * blk, k_block=blk, k_block_stride=R * blk, impl=impl)
         outs.append(o)
         lses.append(l)
     out, lse = ops.merge_partials(outs, lses)
@@ -472,7 +491,7 @@ def test_backend_entry_points_on_model_boundary(golden):
 # other position maps through the same kernels
 # ------------------------------------------------------------------------------------------------
 
-def _posmap_gpu(g, kind):
+def _posmap_gpu(g, kind, impl=0):
     """Rotation kernels vs the fp32 oracle rotation; the attention kernel vs the oracle attention on
     the very operands the kernel consumed; and end to end vs the reference's own output."""
     ops = _ops()
@@ -507,7 +526,7 @@ def _posmap_gpu(g, kind):
     # (2) attention kernel on those operands
     eo, el = orc.posmap_attention_from_operands(kind, [t.cpu() for t in qo], [t.cpu() for t in ko], v[:, :S],
                                                 q_positions=pos[:S], k_positions=pos[:S], params=params)
-    out, lse = ops.posmap_prefill(qo, ko, dv[:, :S], pmap=pm, q_pos0=0)
+    out, lse = ops.posmap_prefill(qo, ko, dv[:, :S], pmap=pm, q_pos0=0, impl=impl)
     _check(out, lse, eo, el, f"{kind} prefill")
     # (3) end to end against the reference's fp32 eager output (it never rounds inputs or operands to bf16)
     d, cos = orc.compare(out.float().cpu(), g["out_prefill"])
@@ -516,7 +535,7 @@ def _posmap_gpu(g, kind):
     qo, ko = q_ops(dq[:, S:], S), k_ops(dk)
     eo, el = orc.posmap_attention_from_operands(kind, [t.cpu() for t in qo], [t.cpu() for t in ko], v,
                                                 q_positions=pos[S:], k_positions=pos, params=params)
-    out, lse = ops.posmap_prefill(qo, ko, dv, pmap=pm, q_pos0=S)
+    out, lse = ops.posmap_prefill(qo, ko, dv, pmap=pm, q_pos0=S, impl=impl)
     _check(out, lse, eo, el, f"{kind} decode-as-prefill")
     d, cos = orc.compare(out.float().cpu(), g["out_decode"])
     assert d < 3e-2 and cos > 0.999, (kind, d, cos)
@@ -532,6 +551,12 @@ def test_posmap_selfext(golden):
     segs = [ops.KvSegment(ko[1][:, :b], dv[:, :b], 1), ops.KvSegment(ko[0][:, b:], dv[:, b:], 0)]
     out, lse = ops.decode_segments(qo, segs)
     _check(out, lse, eo, el, "selfext decode kernel")
+
+
+@pytest.mark.parametrize("kind", ["selfext", "dca"])
+def test_posmap_maps_on_the_cta_pair_kernel(golden, kind):
+    """The band map of self-extend and the three-class chunk map of DCA through the CTA-pair kernel."""
+    _posmap_gpu(golden(kind + "_tiny.npz"), kind, impl=2)
 
 
 def test_posmap_dca(golden):
@@ -665,7 +690,7 @@ def test_position_maps_at_long_positions(kind):
             assert d <= 2 ** -5 and cos > 0.99999, (kind, d, cos)
     eo, el = orc.posmap_attention_from_operands(kind, [t.cpu() for t in qo], [t.cpu() for t in ko], v,
                                                 q_positions=pos, k_positions=pos, params=params)
-    for impl in (0, 1):
+    for impl in (0, 1, 2):
         out, lse = ops.posmap_prefill(qo, ko, dv, pmap=pm, q_pos0=P0, k_pos0=P0, impl=impl)
         _check(out, lse, eo, el, f"{kind} at positions ~131072, impl={impl}")
 
