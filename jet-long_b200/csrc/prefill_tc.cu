@@ -743,8 +743,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
 // memory, is decided in tile order (the thread of tile g waits until the decision of tile g-1 is posted, which
 // happens a tile earlier in time) and the thread that raises it rescales O once P V of the previous tile has
 // retired and before its own P lets the next P V start.
-// Only the even CTA of the pair issues MMAs; its barriers collect the arrivals of both CTAs, its commits are
-// multicast to both.  All query classes stay resident in shared memory, so the look-ahead crosses phases.
+// Only the even CTA of the pair issues MMAs; its barriers collect the arrivals of both CTAs, its commits go
+// to the barriers of both.  All query classes stay resident in shared memory, so the look-ahead crosses phases.
 namespace pair {
 
 constexpr int kRows = 128;                       // query rows per CTA
@@ -770,7 +770,7 @@ struct Smem {
   float row_sum[2][kRows];
   // leader-only barriers (both CTAs arrive on the even CTA's copy): q_full, k_full, v_full, s_free, p_full
   uint64_t q_full[JL_MAX_CLASSES], k_full[kKStages], v_full[kVStages], s_free[2], p_full[2][2];
-  // per-CTA barriers, signalled by multicast commits of the leader's MMA warp
+  // per-CTA barriers, signalled by the commits of the leader's MMA warps
   uint64_t k_empty[kKStages], v_empty[kVStages], s_full[2], pv_done[2], all_done;
   uint32_t tmem_base;
   int failed;
@@ -800,10 +800,14 @@ __device__ __forceinline__ void mma2_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
   asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n}"
                ::"r"(d_tmem), "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
 }
-// commit of the pair's MMAs, delivered to the barrier at the same offset in both CTAs
+// commit of the pair's MMAs, delivered to the barrier at the same offset in both CTAs (one plain commit per CTA:
+// the second names the other CTA's barrier by its cluster address)
 __device__ __forceinline__ void commit_both(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-               ::"r"(smem_u32(bar)), "h"(static_cast<uint16_t>(3)) : "memory");
+  const uint32_t own = smem_u32(bar);
+  uint32_t other;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, 1;" : "=r"(other) : "r"(own));
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(own) : "memory");
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(other) : "memory");
 }
 __device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 // Bounded wait until the reference of `need` tiles has been decided for the 32 rows of a quadrant
