@@ -60,6 +60,7 @@ struct Params {
   // In-kernel remap of the far class (BAND map): class 1 reads the class-0 tensors and warps 2-3 rotate every
   // landed tile in shared memory by (floor(p / group_size) - p) * inv_freq before the tensor pipe reads it.
   int remap, group_size;
+  int head_group;                 // query heads whose CTAs are interleaved along grid x (heaviest rows first across all of them)
   const float* inv_freq;
 };
 
@@ -302,8 +303,9 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q_tile_pair = gridDim.x - 1 - blockIdx.x;          // latest (heaviest) rows first
-  const int head = blockIdx.y, b = blockIdx.z;
+  // grid x = (query tile pair, head within the group), the latest (heaviest) rows first over the whole group of heads
+  const int q_tile_pair = static_cast<int>(gridDim.x / p.head_group) - 1 - static_cast<int>(blockIdx.x / p.head_group);
+  const int head = blockIdx.y * p.head_group + static_cast<int>(blockIdx.x % p.head_group), b = blockIdx.z;
   const int kvh = head / (p.heads / p.kv_heads);
   const int q_row0 = q_tile_pair * kRowsPerCta;
   const Schedule sched = make_schedule(p, q_row0);
@@ -839,8 +841,10 @@ prefill_pair_kernel(const __grid_constant__ Maps maps, const Params p) {
   Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = static_cast<int>(blockIdx.x & 1);                       // rank in the pair; 0 issues the MMAs
-  const int pair_idx = static_cast<int>(gridDim.x >> 1) - 1 - static_cast<int>(blockIdx.x >> 1);      // latest (heaviest) rows first
-  const int head = blockIdx.y, b = blockIdx.z;
+  // grid x = (pair of query tiles, head within the group, rank), the latest (heaviest) rows first over the group of heads
+  const int slot = static_cast<int>(blockIdx.x >> 1);
+  const int pair_idx = static_cast<int>((gridDim.x >> 1) / p.head_group) - 1 - slot / p.head_group;
+  const int head = blockIdx.y * p.head_group + slot % p.head_group, b = blockIdx.z;
   const int kvh = head / (p.heads / p.kv_heads);
   const int q_row0_pair = pair_idx * kRowsPerCta;
   const int q_row0 = q_row0_pair + rank * kRows;
@@ -1367,6 +1371,13 @@ static int prepare(const jl_prefill_args* a, CUtensorMap* qmaps, CUtensorMap* km
   return JL_OK;
 }
 
+// Query heads interleaved along grid x: those of two kv heads where the head count allows, else of one, else one head.
+static int head_group_of(const jl_prefill_args* a) {
+  const int rep = a->heads / a->kv_heads;
+  if (a->heads % (2 * rep) == 0) return 2 * rep;
+  return a->heads % rep == 0 ? rep : 1;
+}
+
 int launch_prefill_tc(const jl_prefill_args* a, cudaStream_t stream) {
   tc::Maps maps;
   tc::Params p{};
@@ -1382,7 +1393,13 @@ int launch_prefill_tc(const jl_prefill_args* a, cudaStream_t stream) {
       return check_launch("jl_prefill (shared memory opt-in)");
     attr_done[dev] = true;
   }
-  dim3 grid((a->seqlen_q + tc::kRowsPerCta - 1) / tc::kRowsPerCta, a->heads, a->batch);
+  // The query heads of two kv heads share a run of the grid, so that the longest CTAs of all of them start first (a
+  // head at a time leaves the last head's longest CTA as a tail; all heads at once stream every kv head's K / V through
+  // L2 together and lose its reuse: 32768 / 131072 / 16384 tokens, 32 / 8 heads: 1296 / 1204 / 942 TFLOP/s a head at a
+  // time, 1310 / 1209 / 966 with 8 heads per run, 1279 / 1148 / 898 with all 32).
+  p.head_group = head_group_of(a);
+  const int hg = p.head_group;
+  dim3 grid(((a->seqlen_q + tc::kRowsPerCta - 1) / tc::kRowsPerCta) * hg, a->heads / hg, a->batch);
   tc::prefill_tc_kernel<<<grid, tc::kThreads, smem, stream>>>(maps, p);
   return check_launch("jl_prefill (tcgen05)");
 }
@@ -1408,7 +1425,9 @@ int launch_prefill_pair(const jl_prefill_args* a, cudaStream_t stream) {
     attr_done[dev] = true;
   }
   // one cluster of two CTAs per 256 query rows (the cluster shape is a compile-time attribute of the kernel)
-  dim3 grid(2 * ((a->seqlen_q + tc::kRowsPerCta - 1) / tc::kRowsPerCta), a->heads, a->batch);
+  const int hg = head_group_of(a);           // as in launch_prefill_tc
+  p.head_group = hg;
+  dim3 grid(2 * ((a->seqlen_q + tc::kRowsPerCta - 1) / tc::kRowsPerCta) * hg, a->heads / hg, a->batch);
   tc::pair::prefill_pair_kernel<<<grid, tc::kThreads, smem, stream>>>(maps, p);
   return check_launch("jl_prefill (tcgen05, CTA pairs)");
 }

@@ -91,7 +91,7 @@ class PartialBuffer:
         return [self.out_view(r) for r in range(sh.world)], [self.lse_view(r) for r in range(sh.world)]
 
 
-PEER_EXCHANGE_VALIDATED_WORLDS = (2, 4)      # rank counts on which jl_peer_merge has been run against the NCCL path
+PEER_EXCHANGE_VALIDATED_WORLDS = (2, 4, 8)      # rank counts on which jl_peer_merge has been run against the NCCL path
 
 
 class PeerExchange:
