@@ -121,6 +121,14 @@ typedef struct {
   int32_t remap_far_in_kernel;
   int32_t group_size;
   const float* inv_freq;    /* (head_dim/2,) fp32 device array; needed only with remap_far_in_kernel */
+  /* Stripe batching (impl 0 and 2; no reference counterpart — the reference has no sequence parallelism): with
+   * q_batch_wrap > 0, q[], out and lse hold q_batch_wrap batch elements (their batch strides apply), this launch
+   * processes `batch` of them, element (q_batch_first + i) % q_batch_wrap for i = 0 .. batch - 1, the rows of element
+   * e sit at positions q_pos0 + e * q_pos0_batch_step (+ the q_block rule), and ALL of them attend batch element 0 of
+   * k[] and v.  One launch then covers the query stripes of several ranks against this rank's key stripe. */
+  int32_t q_batch_first;
+  int32_t q_batch_wrap;
+  int64_t q_pos0_batch_step;
 } jl_prefill_args;
 
 int jl_prefill(const jl_prefill_args* args, void* cuda_stream);

@@ -76,6 +76,9 @@ static int validate_prefill(const jl_prefill_args* a) {
   if (a->map.n_classes != want) return fail(JL_ERR_BAD_ARG, "jl_prefill: map kind %d needs n_classes == %d", a->map.kind, want);
   if (a->map.kind == JL_MAP_BAND && a->map.near_span < 0) return fail(JL_ERR_BAD_ARG, "jl_prefill: near_span must be >= 0");
   if (a->map.kind == JL_MAP_CHUNK && a->map.chunk < 1) return fail(JL_ERR_BAD_ARG, "jl_prefill: chunk must be >= 1");
+  if (a->q_batch_wrap < 0 || (a->q_batch_wrap > 0 && (a->q_batch_first < 0 || a->q_batch_first >= a->q_batch_wrap || a->batch > a->q_batch_wrap)))
+    return fail(JL_ERR_BAD_ARG, "jl_prefill: stripe batching needs 0 <= q_batch_first < q_batch_wrap and batch <= q_batch_wrap");
+  if (a->q_batch_wrap > 0 && a->impl == 1) return fail(JL_ERR_UNSUPPORTED, "jl_prefill: stripe batching needs impl 0 or 2");
   const bool keys = a->seqlen_k > 0;          // an empty key range may come with NULL key / value pointers
   if ((keys && a->v == nullptr) || a->out == nullptr) return fail(JL_ERR_BAD_ARG, "jl_prefill: v/out is NULL");
   uintptr_t bits = reinterpret_cast<uintptr_t>(a->v) | reinterpret_cast<uintptr_t>(a->out);

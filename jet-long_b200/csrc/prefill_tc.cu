@@ -61,6 +61,10 @@ struct Params {
   // landed tile in shared memory by (floor(p / group_size) - p) * inv_freq before the tensor pipe reads it.
   int remap, group_size;
   int head_group;                 // query heads whose CTAs are interleaved along grid x (heaviest rows first across all of them)
+  // Stripe batching: with batch_wrap > 0 grid z = i addresses batch element (batch_first + i) % batch_wrap of q, out and
+  // lse, whose rows start at position q_pos0 + element * q_pos0_batch_step; every element reads batch element 0 of k / v.
+  int batch_first, batch_wrap;
+  int64_t q_pos0_batch_step;
   const float* inv_freq;
 };
 
@@ -272,13 +276,13 @@ struct Schedule {
   int total;
 };
 
-__device__ __forceinline__ Schedule make_schedule(const Params& p, int q_row0) {
+__device__ __forceinline__ Schedule make_schedule(const Params& p, int q_row0, int64_t q_pos0) {
   Schedule s;
   s.n_phases = 0;
   s.total = 0;
   const int rows = min(kRowsPerCta, p.sq - q_row0);
   // the CTA's 256 rows never straddle a position block (q_block is a multiple of 256)
-  const int64_t pq_first = key_position(q_row0, p.q_pos0, p.q_block, p.q_block_stride), pq_last = pq_first + rows - 1;
+  const int64_t pq_first = key_position(q_row0, q_pos0, p.q_block, p.q_block_stride), pq_last = pq_first + rows - 1;
   for (int c = p.n_classes - 1; c >= 0; --c) {       // far classes first, the diagonal last
     int64_t lo, hi, dummy;
     class_interval(p, c, pq_first, lo, dummy);
@@ -305,10 +309,13 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // grid x = (query tile pair, head within the group), the latest (heaviest) rows first over the whole group of heads
   const int q_tile_pair = static_cast<int>(gridDim.x / p.head_group) - 1 - static_cast<int>(blockIdx.x / p.head_group);
-  const int head = blockIdx.y * p.head_group + static_cast<int>(blockIdx.x % p.head_group), b = blockIdx.z;
+  const int head = blockIdx.y * p.head_group + static_cast<int>(blockIdx.x % p.head_group);
+  const int b = p.batch_wrap > 0 ? (p.batch_first + static_cast<int>(blockIdx.z)) % p.batch_wrap : static_cast<int>(blockIdx.z);
+  const int b_kv = p.batch_wrap > 0 ? 0 : b;
+  const int64_t q_pos0 = p.q_pos0 + b * p.q_pos0_batch_step;
   const int kvh = head / (p.heads / p.kv_heads);
   const int q_row0 = q_tile_pair * kRowsPerCta;
-  const Schedule sched = make_schedule(p, q_row0);
+  const Schedule sched = make_schedule(p, q_row0, q_pos0);
 
   if (threadIdx.x == 0) {
     sm.failed = (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
@@ -356,7 +363,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
           if (g >= kKStages) mbar_arrive(&sm.k_full[ks]); else {      // timing experiment: the ring is filled once, never again
 #endif
           mbar_expect_tx(&sm.k_full[ks], kTileBytes);
-          for (int h = 0; h < 2; ++h) tma_load_4d(sm.k[ks] + h * kHalfBytes, km, &sm.k_full[ks], h * 64, kvh, row, b);
+          for (int h = 0; h < 2; ++h) tma_load_4d(sm.k[ks] + h * kHalfBytes, km, &sm.k_full[ks], h * 64, kvh, row, b_kv);
 #if JL_DIAG == 6
           }
 #endif
@@ -365,7 +372,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
           if (g >= kVStages) mbar_arrive(&sm.v_full[vs]); else {
 #endif
           mbar_expect_tx(&sm.v_full[vs], kTileBytes);
-          for (int h = 0; h < 2; ++h) tma_load_4d(sm.v[vs] + h * kHalfBytes, &maps.v, &sm.v_full[vs], h * 64, kvh, row, b);
+          for (int h = 0; h < 2; ++h) tma_load_4d(sm.v[vs] + h * kHalfBytes, &maps.v, &sm.v_full[vs], h * 64, kvh, row, b_kv);
 #if JL_DIAG == 6
           }
 #endif
@@ -500,7 +507,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
         mbar_wait(&sm.q_full, ph & 1, sm);
         if (far) {
           for (int t = 0; t < 2; ++t)
-            rotate_tile(sm.q[t], p.q_pos0, p.q_block, p.q_block_stride, q_row0 + t * kTileM, min(kTileM, max(p.sq - (q_row0 + t * kTileM), 0)));
+            rotate_tile(sm.q[t], q_pos0, p.q_block, p.q_block_stride, q_row0 + t * kTileM, min(kTileM, max(p.sq - (q_row0 + t * kTileM), 0)));
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         }
         mbar_arrive(&sm.q_ready);
@@ -525,7 +532,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
     const int row_in_tile = quad * 32 + lane;
     const int q_row = q_row0 + t * kTileM + row_in_tile;
     const bool row_valid = q_row < p.sq;
-    const int64_t pq_cta0 = key_position(q_row0, p.q_pos0, p.q_block, p.q_block_stride);     // position of the CTA's first row
+    const int64_t pq_cta0 = key_position(q_row0, q_pos0, p.q_block, p.q_block_stride);     // position of the CTA's first row
     const int64_t pq = pq_cta0 + (row_valid ? q_row : p.sq - 1) - q_row0;
     // bounds of this tile's valid rows, for the uniform-tile test
     const int tile_rows = min(kTileM, p.sq - (q_row0 + t * kTileM));
@@ -844,11 +851,14 @@ prefill_pair_kernel(const __grid_constant__ Maps maps, const Params p) {
   // grid x = (pair of query tiles, head within the group, rank), the latest (heaviest) rows first over the group of heads
   const int slot = static_cast<int>(blockIdx.x >> 1);
   const int pair_idx = static_cast<int>((gridDim.x >> 1) / p.head_group) - 1 - slot / p.head_group;
-  const int head = blockIdx.y * p.head_group + slot % p.head_group, b = blockIdx.z;
+  const int head = blockIdx.y * p.head_group + slot % p.head_group;
+  const int b = p.batch_wrap > 0 ? (p.batch_first + static_cast<int>(blockIdx.z)) % p.batch_wrap : static_cast<int>(blockIdx.z);
+  const int b_kv = p.batch_wrap > 0 ? 0 : b;
+  const int64_t q_pos0 = p.q_pos0 + b * p.q_pos0_batch_step;
   const int kvh = head / (p.heads / p.kv_heads);
   const int q_row0_pair = pair_idx * kRowsPerCta;
   const int q_row0 = q_row0_pair + rank * kRows;
-  const Schedule sched = make_schedule(p, q_row0_pair);                    // both CTAs walk the same tiles
+  const Schedule sched = make_schedule(p, q_row0_pair, q_pos0);            // both CTAs walk the same tiles
 
   if (threadIdx.x == 0) {
     sm.failed = (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
@@ -906,7 +916,7 @@ prefill_pair_kernel(const __grid_constant__ Maps maps, const Params p) {
           mbar_wait(&sm.k_empty[ks], ((g / kKStages) & 1) ^ 1, sm);
           if (rank == 0) mbar_expect_tx(&sm.k_full[ks], 2 * kKBytes);
           const uint32_t kbar = leader_addr(&sm.k_full[ks]);
-          for (int h = 0; h < 2; ++h) tma_load_pair(sm.k[ks] + h * kKHalf, km, kbar, h * 64, kvh, j * kTileN + rank * 64, b);
+          for (int h = 0; h < 2; ++h) tma_load_pair(sm.k[ks] + h * kKHalf, km, kbar, h * 64, kvh, j * kTileN + rank * 64, b_kv);
         }
       }
     } else if (warp == 3) {
@@ -919,7 +929,7 @@ prefill_pair_kernel(const __grid_constant__ Maps maps, const Params p) {
           const int vs = g % kVStages;
           mbar_wait(&sm.v_empty[vs], ((g / kVStages) & 1) ^ 1, sm);
           if (rank == 0) mbar_expect_tx(&sm.v_full[vs], 2 * kVBytes);
-          tma_load_pair(sm.v[vs], &maps.v, leader_addr(&sm.v_full[vs]), rank * 64, kvh, j * kTileN, b);
+          tma_load_pair(sm.v[vs], &maps.v, leader_addr(&sm.v_full[vs]), rank * 64, kvh, j * kTileN, b_kv);
         }
       }
     } else if (warp == 1 && rank == 0) {
@@ -1015,9 +1025,9 @@ prefill_pair_kernel(const __grid_constant__ Maps maps, const Params p) {
     const int r_in_tile = quad * 32 + lane;
     const int q_row = q_row0 + r_in_tile;
     const bool row_valid = q_row < p.sq;
-    const int64_t pq = key_position(q_row, p.q_pos0, p.q_block, p.q_block_stride);
+    const int64_t pq = key_position(q_row, q_pos0, p.q_block, p.q_block_stride);
     const int tile_rows = min(kRows, p.sq - q_row0);
-    const int64_t pq_t0 = key_position(q_row0, p.q_pos0, p.q_block, p.q_block_stride);
+    const int64_t pq_t0 = key_position(q_row0, q_pos0, p.q_block, p.q_block_stride);
     const int64_t pq_t1 = pq_t0 + (tile_rows > 0 ? tile_rows - 1 : 0);
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t t_s = tmem + lane_base + wg * 128;             // my row of my score buffer
@@ -1330,10 +1340,12 @@ static int prepare(const jl_prefill_args* a, CUtensorMap* qmaps, CUtensorMap* km
   const void* kptr[2] = {nullptr, nullptr};
   const bool no_keys = a->seqlen_k == 0;      // nothing is loaded then: the key / value maps only have to be well formed
   const bool remap = a->remap_far_in_kernel != 0;      // the far class then reads the class-0 tensors
+  const bool striped = a->q_batch_wrap > 0;            // stripe batching: q / out hold q_batch_wrap elements, k / v one
+  const int q_batches = striped ? a->q_batch_wrap : a->batch, kv_batches = striped ? 1 : a->batch;
   for (int c = 0; c < a->map.n_classes; ++c) {
     const void* qc = remap ? a->q[0] : a->q[c];
     const void* kc = remap ? a->k[0] : a->k[c];
-    int rc = make_map(&qmaps[c], qc, a->batch, a->seqlen_q, a->heads, a->q_stride_b, a->q_stride_s, a->q_stride_h);
+    int rc = make_map(&qmaps[c], qc, q_batches, a->seqlen_q, a->heads, a->q_stride_b, a->q_stride_s, a->q_stride_h);
     if (rc != JL_OK) return rc;
     int slot = -1;
     for (int i = 0; i < n_k; ++i)
@@ -1342,7 +1354,7 @@ static int prepare(const jl_prefill_args* a, CUtensorMap* qmaps, CUtensorMap* km
       slot = n_k++;
       kptr[slot] = kc;
       rc = no_keys ? make_map(&kmaps[slot], a->q[0], 1, 1, 1, 0, 0, 0, k_box_rows)
-                   : make_map(&kmaps[slot], kc, a->batch, a->seqlen_k, a->kv_heads, a->k_stride_b, a->k_stride_s, a->k_stride_h, k_box_rows);
+                   : make_map(&kmaps[slot], kc, kv_batches, a->seqlen_k, a->kv_heads, a->k_stride_b, a->k_stride_s, a->k_stride_h, k_box_rows);
       if (rc != JL_OK) return rc;
     }
     p.k_map[c] = slot;
@@ -1350,7 +1362,7 @@ static int prepare(const jl_prefill_args* a, CUtensorMap* qmaps, CUtensorMap* km
   for (int c = a->map.n_classes; c < JL_MAX_CLASSES; ++c) qmaps[c] = qmaps[0];
   if (n_k == 1) kmaps[1] = kmaps[0];
   int rc = no_keys ? make_map(vmap, a->q[0], 1, 1, 1, 0, 0, 0)
-                   : make_map(vmap, a->v, a->batch, a->seqlen_k, a->kv_heads, a->v_stride_b, a->v_stride_s, a->v_stride_h);
+                   : make_map(vmap, a->v, kv_batches, a->seqlen_k, a->kv_heads, a->v_stride_b, a->v_stride_s, a->v_stride_h);
   if (rc != JL_OK) return rc;
   p.sq = a->seqlen_q; p.sk = a->seqlen_k; p.heads = a->heads; p.kv_heads = a->kv_heads; p.batch = a->batch;
   p.q_pos0 = a->q_pos0; p.k_pos0 = a->k_pos0;
@@ -1368,6 +1380,9 @@ static int prepare(const jl_prefill_args* a, CUtensorMap* qmaps, CUtensorMap* km
   p.remap = a->remap_far_in_kernel != 0;
   p.group_size = a->group_size > 0 ? a->group_size : 1;
   p.inv_freq = a->inv_freq;
+  p.batch_first = striped ? a->q_batch_first : 0;
+  p.batch_wrap = striped ? a->q_batch_wrap : 0;
+  p.q_pos0_batch_step = striped ? a->q_pos0_batch_step : 0;
   return JL_OK;
 }
 

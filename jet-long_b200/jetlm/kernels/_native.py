@@ -37,6 +37,7 @@ class PrefillArgs(C.Structure):
         ("softmax_scale", C.c_float), ("map", PosMap), ("impl", C.c_int32),
         ("q_block", C.c_int64), ("q_block_stride", C.c_int64),
         ("remap_far_in_kernel", C.c_int32), ("group_size", C.c_int32), ("inv_freq", C.c_void_p),
+        ("q_batch_first", C.c_int32), ("q_batch_wrap", C.c_int32), ("q_pos0_batch_step", C.c_int64),
     ]
 
 

@@ -194,7 +194,7 @@ def fused_jetlong_prefill_token_sharded(query_base, key_base, key_group, value, 
     if bufs is None:
         bufs = _BUFFERS[key] = dict(
             q_all=torch.empty(N, B, S_loc, H, D, dtype=dt, device=dev),
-            q_grp=torch.empty(B, S_loc, H, D, dtype=dt, device=dev),
+            q_grp=torch.empty(N, B, S_loc, H, D, dtype=dt, device=dev),
             send_o=torch.empty(N, B, S_loc, H, D, dtype=dt, device=dev),
             send_l=torch.empty(N, B, H, S_loc, dtype=torch.float32, device=dev),
             recv_o=torch.empty(N, B, S_loc, H, D, dtype=dt, device=dev),
@@ -205,14 +205,35 @@ def fused_jetlong_prefill_token_sharded(query_base, key_base, key_group, value, 
     stride = N * blk
     me = sh.rank
 
+    def regroup(qb, r):
+        ops.rope_regroup(qb, inv_freq, group_size=int(group_size), pos0=int(q_start) + r * blk, pos_block=blk,
+                         pos_block_stride=stride, out=q_grp[r])
+
     def attend(qb, r, out, lse):
         """Queries of rank r's stripe (base-rotated, (B,S_loc,H,D)) against the local key stripe."""
-        ops.rope_regroup(qb, inv_freq, group_size=int(group_size), pos0=int(q_start) + r * blk, pos_block=blk,
-                         pos_block_stride=stride, out=q_grp)
-        ops.posmap_prefill([qb, q_grp], [key_base, key_group], value, pmap=pmap,
+        regroup(qb, r)
+        ops.posmap_prefill([qb, q_grp[r]], [key_base, key_group], value, pmap=pmap,
                            q_pos0=int(q_start) + r * blk, q_block=blk, q_block_stride=stride,
                            k_pos0=me * blk, k_block=blk, k_block_stride=stride, softmax_scale=softmax_scale,
                            out=out, lse=lse)
+
+    def attend_stripes(ranks):
+        """The query stripes of consecutive ranks (mod N) against the local key stripe, partials into the send
+        buffers.  With one sequence per batch the stripes are the batch of ONE launch (the kernel takes the stripe
+        index modulo N and offsets the positions by a block per stripe), so the launch has enough CTAs to fill
+        every SM for many rounds; N launches of one stripe each leave the last round of each partly empty."""
+        if not ranks:
+            return
+        if B != 1:
+            for r in ranks:
+                attend(q_all[r], r, send_o[r], send_l[r])
+            return
+        for r in ranks:
+            regroup(q_all[r], r)
+        ops.posmap_prefill([q_all[:, 0], q_grp[:, 0]], [key_base, key_group], value, pmap=pmap,
+                           q_pos0=int(q_start), q_block=blk, q_block_stride=stride,
+                           k_pos0=me * blk, k_block=blk, k_block_stride=stride, softmax_scale=softmax_scale,
+                           out=send_o[:, 0], lse=send_l[:, 0], stripes=(ranks[0], len(ranks), blk))
 
     def exchange(dests, async_op):
         """Send the partials of the query stripes owned by `dests`; receive my rows' partials from the
@@ -236,11 +257,9 @@ def fused_jetlong_prefill_token_sharded(query_base, key_base, key_group, value, 
     # 2. the other stripes in two phases; the first phase's partials travel while the second is computed
     order = [(me + k) % N for k in range(1, N)]
     first, second = order[: (N - 1 + 1) // 2], order[(N - 1 + 1) // 2:]
-    for r in first:
-        attend(q_all[r], r, send_o[r], send_l[r])
+    attend_stripes(first)
     pending = exchange(set(first), async_op=bool(second))
-    for r in second:
-        attend(q_all[r], r, send_o[r], send_l[r])
+    attend_stripes(second)
     if second:
         for w in pending:
             w.wait()

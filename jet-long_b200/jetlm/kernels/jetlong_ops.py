@@ -338,11 +338,14 @@ def posmap_prefill(q_ops: Sequence[torch.Tensor], k_ops: Sequence[torch.Tensor],
                    k_block: int = 0, k_block_stride: int = 0, q_block: int = 0, q_block_stride: int = 0,
                    out: Optional[torch.Tensor] = None,
                    lse: Optional[torch.Tensor] = None, return_lse: bool = True, impl: int = 0,
-                   remap_far: Optional[tuple] = None):
+                   remap_far: Optional[tuple] = None, stripes: Optional[tuple] = None):
     """Single-pass position-mapped causal attention (see jl_prefill).  q_ops[c]: (B,Sq,H,D) views sharing
     strides; k_ops[c], v: (B,Skv,Hk,D) views (all k_ops share strides).  Returns (out, lse) or out.
     remap_far = (inv_freq, group_size): jetlong band map with the far class formed INSIDE the kernel from the
-    base-rotated operands; pass only [q_base] and [k_base]."""
+    base-rotated operands; pass only [q_base] and [k_base].
+    stripes = (first, count, pos_step): stripe batching.  q_ops / out / lse then hold W query stripes along dim 0
+    (stripe e at positions q_pos0 + e * pos_step, plus the q_block rule), k_ops / v hold ONE batch element, and this
+    launch processes stripes (first + i) % W for i < count, all against the same keys."""
     op = "posmap_prefill"
     keep = []
     if remap_far is not None:
@@ -371,8 +374,14 @@ def posmap_prefill(q_ops: Sequence[torch.Tensor], k_ops: Sequence[torch.Tensor],
             raise ValueError(f"{op}: key operands must share shape and strides")
     if k0.shape != v.shape:
         raise ValueError(f"{op}: keys and value must share shape")
-    if q0.shape[0] != k0.shape[0] or q0.shape[3] != k0.shape[3]:
-        raise ValueError(f"{op}: Q/K batch and head-dim must match")
+    if stripes is not None:
+        if k0.shape[0] != 1 or not (0 <= int(stripes[0]) < q0.shape[0]) or not (1 <= int(stripes[1]) <= q0.shape[0]):
+            raise ValueError(f"{op}: stripes = (first, count, pos_step) needs one key batch element, "
+                             f"0 <= first < {q0.shape[0]} and 1 <= count <= {q0.shape[0]}")
+    elif q0.shape[0] != k0.shape[0]:
+        raise ValueError(f"{op}: Q/K batch must match")
+    if q0.shape[3] != k0.shape[3]:
+        raise ValueError(f"{op}: Q/K head-dim must match")
     if q0.shape[2] % k0.shape[2] != 0:
         raise ValueError(f"{op}: q heads must be divisible by kv heads")
     _require_arch(op, q0.device)
@@ -406,6 +415,9 @@ def posmap_prefill(q_ops: Sequence[torch.Tensor], k_ops: Sequence[torch.Tensor],
     a.map = pmap.c_struct()
     a.impl = int(impl)
     a.q_block, a.q_block_stride = int(q_block), int(q_block_stride)
+    if stripes is not None:
+        a.batch = int(stripes[1])
+        a.q_batch_first, a.q_batch_wrap, a.q_pos0_batch_step = int(stripes[0]), B, int(stripes[2])
     if remap_far is not None:
         inv_freq = remap_far[0].to(device=q0.device, dtype=torch.float32).contiguous()
         keep.append(inv_freq)

@@ -83,6 +83,11 @@ def test_prefill_cta_pair_kernel_refuses_what_it_does_not_cover():
     with pytest.raises(NativeError, match="impl must be 0, 1 or 2") as err:
         ops.posmap_prefill([q, q], [k, k], k, pmap=ops.PositionMap.jetlong(40), q_pos0=0, impl=3)
     assert err.value.status == JL_ERR_BAD_ARG
+    with pytest.raises(NativeError, match="stripe batching needs impl 0 or 2") as err:
+        ops.posmap_prefill([q, q], [k, k], k, pmap=ops.PositionMap.jetlong(40), q_pos0=0, impl=1, stripes=(0, 1, 256))
+    assert err.value.status == JL_ERR_UNSUPPORTED
+    with pytest.raises(ValueError, match="stripes"):
+        ops.posmap_prefill([q, q], [k, k], k, pmap=ops.PositionMap.jetlong(40), q_pos0=0, stripes=(1, 1, 256))
 
 
 @pytest.mark.parametrize("impl", [0, 2])

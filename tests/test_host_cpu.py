@@ -51,7 +51,7 @@ def test_struct_layout_matches_header(tmp_path):
     sizes = [int(x) for x in subprocess.check_output([str(exe)]).split()]
     assert sizes == [C.sizeof(t) for _, t in pairs], list(zip([p[0] for p in pairs], sizes, [C.sizeof(t) for _, t in pairs]))
     # and the last fields sit where the header puts them (a missing trailing field shows up here)
-    assert n.PrefillArgs.inv_freq.offset + 8 == C.sizeof(n.PrefillArgs)
+    assert n.PrefillArgs.q_pos0_batch_step.offset + 8 == C.sizeof(n.PrefillArgs)
     assert n.PeerMergeArgs.status.offset + 8 == C.sizeof(n.PeerMergeArgs)
 
 

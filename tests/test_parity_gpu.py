@@ -307,6 +307,33 @@ def _native_status_clean():
 
 
 @pytest.mark.parametrize("impl", [0, 2])
+def test_prefill_stripe_batching_matches_per_stripe_launches(impl):
+    """Stripe batching (the sequence-parallel Q exchange): the block-cyclic query stripes of four ranks against one
+    key tensor in two launches (stripes 1,2 and 3,0 - the second wraps) == one launch per stripe, bit for bit; the
+    per-stripe form is the one the block-cyclic tests check against the oracle."""
+    ops = _ops()
+    torch.manual_seed(21)
+    W, blk, S_loc, H, Hk, D, w0 = 4, 256, 512, 4, 2, 128, 300
+    Skv = W * S_loc
+    q, qg = (torch.randn(W, S_loc, H, D, device="cuda").bfloat16() for _ in range(2))
+    k, kg, v = (torch.randn(1, Skv, Hk, D, device="cuda").bfloat16() for _ in range(3))
+    pm = ops.PositionMap.jetlong(w0)
+    geo = dict(q_block=blk, q_block_stride=W * blk)
+    ref_o, ref_l = [], []
+    for r in range(W):
+        o, l = ops.posmap_prefill([q[r:r + 1], qg[r:r + 1]], [k, kg], v, pmap=pm, q_pos0=r * blk, impl=impl, **geo)
+        ref_o.append(o)
+        ref_l.append(l)
+    out = torch.full((W, S_loc, H, D), float("nan"), device="cuda", dtype=torch.bfloat16)
+    lse = torch.full((W, H, S_loc), float("nan"), device="cuda")
+    ops.posmap_prefill([q, qg], [k, kg], v, pmap=pm, q_pos0=0, impl=impl, out=out, lse=lse, stripes=(1, 2, blk), **geo)
+    assert torch.isnan(out[0].float()).all() and torch.isnan(out[3].float()).all()          # untouched stripes
+    ops.posmap_prefill([q, qg], [k, kg], v, pmap=pm, q_pos0=0, impl=impl, out=out, lse=lse, stripes=(3, 2, blk), **geo)
+    assert torch.equal(out, torch.cat(ref_o)) and torch.equal(lse, torch.cat(ref_l))
+    assert _native_status_clean()
+
+
+@pytest.mark.parametrize("impl", [0, 2])
 def test_prefill_block_cyclic_keys(impl):
     """A rank's block-cyclic stripe of the keys + merge of the stripes == attention over all keys."""
     ops = _ops()
