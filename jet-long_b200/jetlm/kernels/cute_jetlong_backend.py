@@ -250,22 +250,31 @@ def fused_jetlong_prefill_token_sharded(query_base, key_base, key_group, value, 
                                      group=sh.group, async_op=async_op))
         return works
 
-    # 1. the query all-gather runs behind the attention of my own stripe (which needs no remote data)
+    # 1. the query all-gather; the other ranks' stripes follow in two phases, the first phase's partials travel while
+    #    the second is computed
     gather = dist.all_gather_into_tensor(q_all.view(-1), query_base.contiguous().view(-1), group=sh.group, async_op=True)
-    attend(query_base, me, recv_o[me], recv_l[me])
-    gather.wait()
-    # 2. the other stripes in two phases; the first phase's partials travel while the second is computed
     order = [(me + k) % N for k in range(1, N)]
     first, second = order[: (N - 1 + 1) // 2], order[(N - 1 + 1) // 2:]
-    attend_stripes(first)
+    if B == 1:
+        # my own stripe rides in the first batched launch (a launch of one stripe leaves the SMs' last round half
+        # empty; the gather it could hide is a hundredth of a late chunk's attention); its partial stays where it lands
+        gather.wait()
+        attend_stripes([me] + first)
+        own_o, own_l = send_o[me], send_l[me]
+    else:
+        attend(query_base, me, recv_o[me], recv_l[me])       # needs no remote data: runs under the gather
+        gather.wait()
+        attend_stripes(first)
+        own_o, own_l = recv_o[me], recv_l[me]
     pending = exchange(set(first), async_op=bool(second))
     attend_stripes(second)
     if second:
         for w in pending:
             w.wait()
         exchange(set(second), async_op=False)
-    out = ops.merge_partials(list(bufs["recv_o"].unbind(0)), list(bufs["recv_l"].unbind(0)), return_lse=False)
-    return out
+    outs = [own_o if r == me else recv_o[r] for r in range(N)]
+    lses = [own_l if r == me else recv_l[r] for r in range(N)]
+    return ops.merge_partials(outs, lses, return_lse=False)
 
 
 def fused_jetlong_prefill(query_base, query_group, key_base, key_group, value, *, seqstart_q: int,
