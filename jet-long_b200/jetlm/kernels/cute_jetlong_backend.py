@@ -199,8 +199,14 @@ def fused_jetlong_prefill_token_sharded(query_base, key_base, key_group, value, 
             send_l=torch.empty(N, B, H, S_loc, dtype=torch.float32, device=dev),
             recv_o=torch.empty(N, B, S_loc, H, D, dtype=dt, device=dev),
             recv_l=torch.empty(N, B, H, S_loc, dtype=torch.float32, device=dev))
+    if "peer" not in bufs:
+        from .sequence_parallel import make_stripe_exchange
+        bufs["peer"] = make_stripe_exchange(sh, B, S_loc, H, D, dt, dev)       # None: the NCCL all-to-all below
+    peer = bufs["peer"]
     q_all, q_grp = bufs["q_all"], bufs["q_grp"]
     send_o, send_l, recv_o, recv_l = bufs["send_o"], bufs["send_l"], bufs["recv_o"], bufs["recv_l"]
+    if peer is not None:
+        recv_o, recv_l = peer.begin()
     pmap = ops.PositionMap.jetlong(int(window_size_left))
     stride = N * blk
     me = sh.rank
@@ -266,12 +272,18 @@ def fused_jetlong_prefill_token_sharded(query_base, key_base, key_group, value, 
         gather.wait()
         attend_stripes(first)
         own_o, own_l = recv_o[me], recv_l[me]
-    pending = exchange(set(first), async_op=bool(second))
-    attend_stripes(second)
-    if second:
-        for w in pending:
-            w.wait()
-        exchange(set(second), async_op=False)
+    if peer is not None:
+        peer.push(first, send_o, send_l)          # peer-to-peer copies on a side stream, under the second launch
+        attend_stripes(second)
+        peer.push(second, send_o, send_l)
+        peer.finish()
+    else:
+        pending = exchange(set(first), async_op=bool(second))
+        attend_stripes(second)
+        if second:
+            for w in pending:
+                w.wait()
+            exchange(set(second), async_op=False)
     outs = [own_o if r == me else recv_o[r] for r in range(N)]
     lses = [own_l if r == me else recv_l[r] for r in range(N)]
     return ops.merge_partials(outs, lses, return_lse=False)

@@ -147,6 +147,77 @@ def make_peer_exchange(shard: SequenceShard, batch: int, heads: int, head_dim: i
     return ex if int(agree) == 1 else None
 
 
+class StripeExchange:
+    """Receive buffers of the sequence-parallel Q exchange in symmetric memory.  A rank writes the partial (O, LSE) it
+    computed for the query stripe of rank d straight into rank d's buffer with peer-to-peer copies on a side stream:
+    the copy engines move them, no SM is needed, so they run under the next attention launch (an NCCL send / receive
+    kernel does not get an SM while the attention grid has blocks to place: its CTAs hold every register of theirs).
+    One small all-reduce per call, issued after this rank's side stream has drained, tells every rank that all
+    partials addressed to it have landed.  Two buffers alternate from call to call, so a fast rank that is already
+    writing the next call's partials never touches what a slow rank is still merging (it cannot be two calls ahead:
+    the all-reduce in between needs the slow rank, whose stream reaches it only after that merge)."""
+
+    def __init__(self, shard: SequenceShard, batch: int, rows: int, heads: int, head_dim: int, dtype, device):
+        import torch.distributed._symmetric_memory as symm_mem
+        N = shard.world
+        self.shard = shard
+        self.o_shape, self.l_shape = (N, batch, rows, heads, head_dim), (N, batch, heads, rows)
+        esz = torch.empty(0, dtype=dtype).element_size()
+        o_bytes = (N * batch * rows * heads * head_dim * esz + 255) // 256 * 256
+        slot = o_bytes + (N * batch * heads * rows * 4 + 255) // 256 * 256
+        group = shard.group if shard.group is not None else dist.group.WORLD
+        self.buf = symm_mem.empty(2 * slot, dtype=torch.uint8, device=device)
+        self.handle = symm_mem.rendezvous(self.buf, group)
+        view = lambda r, p: (self.handle.get_buffer(r, self.o_shape, dtype, (p * slot) // esz),
+                             self.handle.get_buffer(r, self.l_shape, torch.float32, (p * slot + o_bytes) // 4))
+        self.views = [[view(r, p) for r in range(N)] for p in range(2)]          # [buffer][rank] -> (O, LSE) of that rank
+        self.side = torch.cuda.Stream(device=device)
+        self.token = torch.zeros(1, dtype=torch.int32, device=device)
+        self.parity = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
+
+    def begin(self):
+        """Start a call: returns this rank's receive views (O (N,B,rows,H,D), LSE (N,B,H,rows)) of the call's buffer."""
+        self.parity ^= 1
+        return self.views[self.parity][self.shard.rank]
+
+    def push(self, dests, send_o, send_l):
+        """Copy send_o[d] / send_l[d] (the partial of rank d's stripe, computed by kernels already enqueued on the
+        current stream) into rank d's slot for this rank, on the side stream."""
+        me = self.shard.rank
+        self.side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.side):
+            for d in dests:
+                o, l = self.views[self.parity][d]
+                o[me].copy_(send_o[d], non_blocking=True)
+                l[me].copy_(send_l[d], non_blocking=True)
+
+    def finish(self):
+        """All pushes of all ranks are complete when this returns (on the current stream)."""
+        torch.cuda.current_stream().wait_stream(self.side)
+        dist.all_reduce(self.token, group=self.shard.group)
+
+
+def make_stripe_exchange(shard: SequenceShard, batch: int, rows: int, heads: int, head_dim: int, dtype, device):
+    """A StripeExchange if EVERY rank could set one up (agreed through an all-reduce), else None (the NCCL all-to-all
+    is used).  JETLONG_PREFILL_PEER_COPY=0 disables it."""
+    import os
+    import warnings
+    ok, ex = 1, None
+    if os.environ.get("JETLONG_PREFILL_PEER_COPY", "") == "0":
+        ok = 0
+    else:
+        try:
+            ex = StripeExchange(shard, batch, rows, heads, head_dim, dtype, device)
+        except Exception as err:                # no symmetric-memory support on this system
+            warnings.warn(f"peer-copy exchange unavailable ({err}); using the NCCL all-to-all")
+            ok = 0
+    agree = torch.tensor([ok], dtype=torch.int32, device=device)
+    dist.all_reduce(agree, op=dist.ReduceOp.MIN, group=shard.group)
+    return ex if int(agree) == 1 else None
+
+
 def interleave_stripes(stage: torch.Tensor, block: int, out: torch.Tensor) -> torch.Tensor:
     """Block-cyclic stripes, rank-major as an all-gather delivers them, into position order.
     stage (N, C, B, R, ...): rank r's R rows are positions r*block + (i // block) * N*block + i % block;
