@@ -76,6 +76,17 @@ def test_null_args_are_rejected_without_a_gpu():
     a = n.PrefillArgs()
     a.head_dim = 64
     assert lib.jl_prefill(C.byref(a), None) == n.JL_ERR_UNSUPPORTED
+    # stripe batching: the argument checks come before anything touches a device
+    a = n.PrefillArgs()
+    a.head_dim, a.batch, a.heads, a.kv_heads, a.seqlen_q, a.seqlen_k = 128, 3, 4, 2, 256, 256
+    a.map.kind, a.map.n_classes, a.map.near_span = n.JL_MAP_BAND, 2, 10
+    a.q_batch_wrap, a.q_batch_first = 2, 0                  # more stripes asked for than the tensors hold
+    assert lib.jl_prefill(C.byref(a), None) == n.JL_ERR_BAD_ARG
+    assert b"stripe batching" in lib.jl_last_error()
+    a.batch, a.q_batch_first = 2, 2                         # first stripe out of range
+    assert lib.jl_prefill(C.byref(a), None) == n.JL_ERR_BAD_ARG
+    a.q_batch_first, a.impl = 1, 1                          # the cross-check kernel has no stripe batching
+    assert lib.jl_prefill(C.byref(a), None) == n.JL_ERR_UNSUPPORTED
 
 
 def test_backend_guards_match_reference_behaviour():
