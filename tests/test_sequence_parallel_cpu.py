@@ -139,3 +139,99 @@ def test_token_sharded_prefill_picks_the_smaller_exchange(monkeypatch):
     assert mode(8, 131072, 131072, 32, 8) == "q_exchange"
     monkeypatch.setenv("JETLONG_SP_PREFILL", "kv")
     assert mode(8, 1048576, 32768, 32, 8) == "kv_gather"
+
+
+def _q_exchange_worker(rank, world, port, block, results):
+    """The token-sharded Q-exchange driver (stripe batching, own stripe in the first launch, exchange, N-way merge)
+    with the CPU oracle standing in for the kernels and point-to-point sends standing in for the all-to-all (gloo
+    has none); symmetric memory does not exist on CPU ranks, so the driver takes its collective path."""
+    sys.path[:0] = [PKG, os.path.join(ROOT, "oracle")]
+    import types
+    import jetlong_oracle as orc
+    from jetlm.kernels import cute_jetlong_backend as be
+    from jetlm.kernels.sequence_parallel import SequenceShard
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), JETLONG_PREFILL_PEER_COPY="0")
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.manual_seed(11)                                  # same tensors on every rank
+        B, H, Hk, D, w0, G = 1, 4, 2, 128, 90, 3
+        n_blocks_q, n_blocks_cached = 2, 1                     # per rank: the chunk holds 2 blocks, 1 block was cached before
+        S_loc = n_blocks_q * block
+        S, cached = S_loc * world, n_blocks_cached * block * world
+        Skv = cached + S
+        inv = orc.default_inv_freq()
+        pos = torch.arange(Skv)
+        q = torch.randn(B, S, H, D)
+        k, v = torch.randn(B, Skv, Hk, D), torch.randn(B, Skv, Hk, D)
+        regroup = lambda x, p: orc.rotate_bshd(x, orc.regroup_delta(p.view(1, -1), G), inv)
+        kg = regroup(k, pos)
+        expect, _ = orc.jetlong_prefill(q, regroup(q, pos[cached:]), k, kg, v, seqstart=cached, w0=w0)
+
+        def positions(n, pos0, blk, stride):
+            i = torch.arange(n)
+            return pos0 + i if blk <= 0 else pos0 + (i // blk) * stride + i % blk
+
+        calls = []
+
+        def rope_regroup(x, inv_freq, *, group_size, pos0=0, pos_block=0, pos_block_stride=0, out=None):
+            out.copy_(regroup(x, positions(x.shape[1], pos0, pos_block, pos_block_stride)))
+            return out
+
+        def posmap_prefill(q_ops, k_ops, value, *, pmap, q_pos0, k_pos0=0, q_block=0, q_block_stride=0, k_block=0,
+                           k_block_stride=0, softmax_scale=None, out=None, lse=None, stripes=None):
+            first, count, step = stripes if stripes is not None else (0, q_ops[0].shape[0], 0)
+            wrap = q_ops[0].shape[0]
+            calls.append((first, count))
+            pk = positions(k_ops[0].shape[1], k_pos0, k_block, k_block_stride).view(1, 1, -1)
+            for i in range(count):
+                e = (first + i) % wrap if stripes is not None else i
+                pq = positions(q_ops[0].shape[1], q_pos0 + e * step, q_block, q_block_stride).view(1, -1, 1)
+                near, far = (pk <= pq) & (pk >= pq - pmap), pk < pq - pmap
+                on, ln = orc.attention(q_ops[0][e:e + 1], k_ops[0], value, near, softmax_scale)
+                of, lf = orc.attention(q_ops[1][e:e + 1], k_ops[1], value, far, softmax_scale)
+                o, l = orc.merge2(on, ln, of, lf)
+                out[e:e + 1].copy_(o)
+                lse[e:e + 1].copy_(l)
+            return out, lse
+
+        def merge_partials(outs, lses, return_lse=True):
+            o, l = orc.merge_partials(torch.stack(list(outs)), torch.stack(list(lses)))
+            return (o, l) if return_lse else o
+
+        be.ops = types.SimpleNamespace(PositionMap=types.SimpleNamespace(jetlong=lambda w: w), rope_regroup=rope_regroup,
+                                       posmap_prefill=posmap_prefill, merge_partials=merge_partials)
+
+        def all_to_all(outs, ins, group=None, async_op=False):
+            works = [dist.isend(t.contiguous(), d) for d, t in enumerate(ins) if t.numel()]
+            works += [dist.irecv(t, s) for s, t in enumerate(outs) if t.numel()]
+            for w in works:
+                w.wait()
+            return types.SimpleNamespace(wait=lambda: None)
+
+        dist.all_to_all = all_to_all
+        shard = SequenceShard(rank, world, block=block)
+        be.configure_sequence_sharding(shard)
+        mine_q = shard.owned_rows(S)                            # rows of the chunk, relative to its start
+        mine_k = shard.owned_rows(Skv)
+        out = be.fused_jetlong_prefill_token_sharded(
+            q[:, mine_q].contiguous(), k[:, mine_k].contiguous(), kg[:, mine_k].contiguous(), v[:, mine_k].contiguous(),
+            q_start=cached, inv_freq=inv, group_size=G, window_size_left=w0, softmax_scale=D ** -0.5, mode="q_exchange")
+        d, cos = orc.compare(out, expect[:, mine_q])
+        # one batched launch for my own stripe and the first half of the others, one for the rest
+        first = (world - 1 + 1) // 2
+        want = [(rank, 1 + first)] + ([((rank + 1 + first) % world, world - 1 - first)] if world - 1 - first else [])
+        results[rank] = (d, cos, calls == want)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,block", [(2, 64), (3, 32)])
+def test_token_sharded_q_exchange_driver(world, block):
+    port = _free_port()
+    results = mp.Manager().dict()
+    mp.spawn(_q_exchange_worker, args=(world, port, block, results), nprocs=world, join=True)
+    assert len(results) == world
+    for r in range(world):
+        d, cos, launches_as_planned = results[r]
+        assert d <= 2e-5 and cos >= 0.99999, (r, d, cos)
+        assert launches_as_planned, r
