@@ -141,10 +141,11 @@ def test_token_sharded_prefill_picks_the_smaller_exchange(monkeypatch):
     assert mode(8, 1048576, 32768, 32, 8) == "kv_gather"
 
 
-def _q_exchange_worker(rank, world, port, block, results):
-    """The token-sharded Q-exchange driver (stripe batching, own stripe in the first launch, exchange, N-way merge)
-    with the CPU oracle standing in for the kernels and point-to-point sends standing in for the all-to-all (gloo
-    has none); symmetric memory does not exist on CPU ranks, so the driver takes its collective path."""
+def _token_sharded_worker(rank, world, port, block, mode, results):
+    """The token-sharded prefill drivers - "q_exchange" (stripe batching, own stripe in the first launch, exchange,
+    N-way merge) and "kv_gather" (all-gather, stripe interleave, local regroup, one launch) - with the CPU oracle
+    standing in for the kernels and point-to-point sends standing in for the all-to-all (gloo has none); symmetric
+    memory does not exist on CPU ranks, so the Q exchange takes its collective path."""
     sys.path[:0] = [PKG, os.path.join(ROOT, "oracle")]
     import types
     import jetlong_oracle as orc
@@ -174,11 +175,13 @@ def _q_exchange_worker(rank, world, port, block, results):
         calls = []
 
         def rope_regroup(x, inv_freq, *, group_size, pos0=0, pos_block=0, pos_block_stride=0, out=None):
-            out.copy_(regroup(x, positions(x.shape[1], pos0, pos_block, pos_block_stride)))
-            return out
+            r = regroup(x, positions(x.shape[1], pos0, pos_block, pos_block_stride))
+            return r if out is None else out.copy_(r)
 
         def posmap_prefill(q_ops, k_ops, value, *, pmap, q_pos0, k_pos0=0, q_block=0, q_block_stride=0, k_block=0,
-                           k_block_stride=0, softmax_scale=None, out=None, lse=None, stripes=None):
+                           k_block_stride=0, softmax_scale=None, out=None, lse=None, stripes=None, return_lse=True):
+            out = torch.empty_like(q_ops[0]) if out is None else out
+            lse = torch.empty(q_ops[0].shape[0], q_ops[0].shape[2], q_ops[0].shape[1]) if lse is None else lse
             first, count, step = stripes if stripes is not None else (0, q_ops[0].shape[0], 0)
             wrap = q_ops[0].shape[0]
             calls.append((first, count))
@@ -192,7 +195,7 @@ def _q_exchange_worker(rank, world, port, block, results):
                 o, l = orc.merge2(on, ln, of, lf)
                 out[e:e + 1].copy_(o)
                 lse[e:e + 1].copy_(l)
-            return out, lse
+            return (out, lse) if return_lse else out
 
         def merge_partials(outs, lses, return_lse=True):
             o, l = orc.merge_partials(torch.stack(list(outs)), torch.stack(list(lses)))
@@ -215,21 +218,24 @@ def _q_exchange_worker(rank, world, port, block, results):
         mine_k = shard.owned_rows(Skv)
         out = be.fused_jetlong_prefill_token_sharded(
             q[:, mine_q].contiguous(), k[:, mine_k].contiguous(), kg[:, mine_k].contiguous(), v[:, mine_k].contiguous(),
-            q_start=cached, inv_freq=inv, group_size=G, window_size_left=w0, softmax_scale=D ** -0.5, mode="q_exchange")
+            q_start=cached, inv_freq=inv, group_size=G, window_size_left=w0, softmax_scale=D ** -0.5, mode=mode)
         d, cos = orc.compare(out, expect[:, mine_q])
-        # one batched launch for my own stripe and the first half of the others, one for the rest
-        first = (world - 1 + 1) // 2
-        want = [(rank, 1 + first)] + ([((rank + 1 + first) % world, world - 1 - first)] if world - 1 - first else [])
+        if mode == "q_exchange":       # one batched launch for my own stripe and the first half of the others, one for the rest
+            first = (world - 1 + 1) // 2
+            want = [(rank, 1 + first)] + ([((rank + 1 + first) % world, world - 1 - first)] if world - 1 - first else [])
+        else:                           # one launch of my query stripe against all the gathered keys
+            want = [(0, 1)]
         results[rank] = (d, cos, calls == want)
     finally:
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("mode", ["q_exchange", "kv_gather"])
 @pytest.mark.parametrize("world,block", [(2, 64), (3, 32)])
-def test_token_sharded_q_exchange_driver(world, block):
+def test_token_sharded_prefill_drivers(world, block, mode):
     port = _free_port()
     results = mp.Manager().dict()
-    mp.spawn(_q_exchange_worker, args=(world, port, block, results), nprocs=world, join=True)
+    mp.spawn(_token_sharded_worker, args=(world, port, block, mode, results), nprocs=world, join=True)
     assert len(results) == world
     for r in range(world):
         d, cos, launches_as_planned = results[r]
