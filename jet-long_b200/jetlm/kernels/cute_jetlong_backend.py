@@ -196,17 +196,20 @@ def fused_jetlong_prefill_token_sharded(query_base, key_base, key_group, value, 
             q_all=torch.empty(N, B, S_loc, H, D, dtype=dt, device=dev),
             q_grp=torch.empty(N, B, S_loc, H, D, dtype=dt, device=dev),
             send_o=torch.empty(N, B, S_loc, H, D, dtype=dt, device=dev),
-            send_l=torch.empty(N, B, H, S_loc, dtype=torch.float32, device=dev),
-            recv_o=torch.empty(N, B, S_loc, H, D, dtype=dt, device=dev),
-            recv_l=torch.empty(N, B, H, S_loc, dtype=torch.float32, device=dev))
+            send_l=torch.empty(N, B, H, S_loc, dtype=torch.float32, device=dev))
     if "peer" not in bufs:
         from .sequence_parallel import make_stripe_exchange
         bufs["peer"] = make_stripe_exchange(sh, B, S_loc, H, D, dt, dev)       # None: the NCCL all-to-all below
     peer = bufs["peer"]
     q_all, q_grp = bufs["q_all"], bufs["q_grp"]
-    send_o, send_l, recv_o, recv_l = bufs["send_o"], bufs["send_l"], bufs["recv_o"], bufs["recv_l"]
+    send_o, send_l = bufs["send_o"], bufs["send_l"]
     if peer is not None:
-        recv_o, recv_l = peer.begin()
+        recv_o, recv_l = peer.begin()              # this call's receive buffer in symmetric memory
+    else:
+        if "recv_o" not in bufs:                   # receive buffers of the all-to-all
+            bufs["recv_o"] = torch.empty(N, B, S_loc, H, D, dtype=dt, device=dev)
+            bufs["recv_l"] = torch.empty(N, B, H, S_loc, dtype=torch.float32, device=dev)
+        recv_o, recv_l = bufs["recv_o"], bufs["recv_l"]
     pmap = ops.PositionMap.jetlong(int(window_size_left))
     stride = N * blk
     me = sh.rank
