@@ -746,8 +746,9 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_tc_kernel(const __grid_co
 //     S_a | S_b | O | P_a | P_b   =  128 + 128 + 128 + 64 + 64 = 512 columns
 // The two softmax warpgroups take alternate key tiles of the same 128 rows (warps 4-7: even tiles, buffers a;
 // warps 8-11: odd tiles, buffers b), one thread per row as in the single-CTA kernel.  A score buffer is handed
-// back as soon as its scores are in registers, and Q K^T runs three tiles ahead of P V, so neither the softmax
-// threads nor the tensor pipe wait for each other's full round trip.
+// back as soon as its scores are in registers, and Q K^T and P V are issued by two different warps (1 and 2 of
+// the even CTA): Q K^T of tile g + 2 starts when the scores of tile g have been read, whatever P V is waiting
+// for, so neither the softmax threads nor the tensor pipe wait for each other's full round trip.
 // Both threads of a row add into the same O, so they share the row's reference maximum: it lives in shared
 // memory, is decided in tile order (the thread of tile g waits until the decision of tile g-1 is posted, which
 // happens a tile earlier in time) and the thread that raises it rescales O once P V of the previous tile has
